@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-GEMV hot path on B200.
+
+Workload (`config.workload` = "gemv_sweep"): the batched decode GEMV sweep of the benchmark
+configuration list -- Q4_K / Q5_K / Q6_K weights of N x K in {4096x4096, 1024x4096, 12288x4096,
+4096x12288}, members M in {1, 4, 16, 64}, bf16 N(0,1) activations, f32 outputs -- 48 GEMVs per step.
+Synthetic seeded blocks stand in for model weights (no datasets or checkpoints are involved).
+
+metric  = algorithmic bytes moved per second over a whole step: for each GEMV the encoded weight
+          bytes + M*K*2 activation bytes + M*N*4 output bytes, counted once.
+L2      = every (format, shape) has a ring of distinct weight copies larger than 2x the 126 MB L2
+          and each launch uses the next copy, so no launch finds its weights in cache.
+value   = device-resident inputs, CUDA-event timed on the launching stream.
+e2e     = the same sweep through ribn_gemv_host: pinned host activations in, host outputs out,
+          copies inside the timed region.
+--impl reference = the CPU restatement of the reference's host path (dequantise a row, sequential
+          f32 dot; oracle/ribn_oracle.c) on all host threads, on a bounded sample of the sweep.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FORMATS = [12, 13, 14]
+SHAPES = [(4096, 4096), (1024, 4096), (12288, 4096), (4096, 12288)]  # (N, K)
+MEMBERS = [1, 4, 16, 64]
+L2_BYTES = 126 << 20
+NOMINAL_HBM_GBS = 6650.0  # fallback when MEASURED_PEAKS.json is absent
+
+
+def case_bytes(vt: int, n: int, k: int, m: int) -> int:
+    from engine_b200 import synth
+
+    return synth.encoded_bytes(vt, k, n) + m * k * 2 + m * n * 4
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return NOMINAL_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for parts in self.samples:
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference's host path for the same metric, on this box's cores."""
+    if rank != 0:
+        return
+    import oracle
+    from engine_b200 import synth
+
+    threads = os.cpu_count() or 1
+    sample_members = [1, 4]
+    cases = []
+    for vt in FORMATS:
+        for n, k in SHAPES:
+            w = synth.random_weight(vt, k, n, seed=vt * 100 + n // 1024 + k // 1024)
+            for m in sample_members:
+                x = oracle.oracle_np.bf16_bits_to_f32(oracle.oracle_np.f32_to_bf16_bits(synth.random_activations(m, k, seed=m)))
+                cases.append((vt, n, k, m, w, x))
+    step_bytes = sum(case_bytes(vt, n, k, m) for vt, n, k, m, _, _ in cases)
+
+    def step():
+        for vt, n, k, m, w, x in cases:
+            oracle.gemv_f32(vt, w, k, n, x, threads=threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    elapsed = time.perf_counter() - t0
+    value = step_bytes * args.steps / elapsed / 1e9
+    sample = f"members {sample_members} of the sweep (24 of 48 GEMVs per step), all {threads} host threads, rows split over threads"
+    line = {
+        "impl": "reference", "metric": "qgemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gemv_sweep", "formats": ["Q4_K", "Q5_K", "Q6_K"], "shapes_NxK": SHAPES,
+                   "members": sample_members, "activations": "bf16", "outputs": "f32"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline_leg():
+    """Bounded CPU sample for the main arm: the M=1 GEMV of every (format, shape), reference host
+    arithmetic, once single-threaded (the reference's host path is single-threaded) and once on all cores."""
+    import oracle
+    from engine_b200 import synth
+
+    threads = os.cpu_count() or 1
+    total = 0
+    t1 = tn = 0.0
+    for vt in FORMATS:
+        for n, k in SHAPES:
+            w = synth.random_weight(vt, k, n, seed=1)
+            x = synth.random_activations(1, k, seed=1)
+            total += case_bytes(vt, n, k, 1)
+            t0 = time.perf_counter()
+            oracle.gemv_f32(vt, w, k, n, x, threads=1)
+            t1 += time.perf_counter() - t0
+            t0 = time.perf_counter()
+            oracle.gemv_f32(vt, w, k, n, x, threads=threads)
+            tn += time.perf_counter() - t0
+    return {"value": total / tn / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "M=1 GEMV of all 12 (format, shape) pairs, one pass; rows split over all host threads",
+            "single_thread_value": total / t1 / 1e9}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--variant", type=int, default=0, help="GEMV tuning variant")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
+    parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
+    parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
+                        "a small run for profiler captures, not a benchmark line")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    global FORMATS, SHAPES, MEMBERS
+    if args.only:
+        fmt, shape, m = args.only.split(":")
+        FORMATS = [{"Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}[fmt]]
+        SHAPES = [tuple(int(v) for v in shape.split("x"))]
+        MEMBERS = [int(m)]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import engine_b200
+    from engine_b200 import synth
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    # The library launches on its context's stream; a dedicated stream lets the step be captured
+    # into a CUDA graph, so the timed region measures the GPU and not the Python launch loop.
+    stream = torch.cuda.Stream(device=device)
+    ctx = engine_b200.RibnContext(local_rank, stream=stream)
+    ctx.set_option("gemv_variant", args.variant)
+    kernels = {vt: engine_b200.QwenGemvKernel.from_value_type(vt, ctx) for vt in FORMATS}
+    store = engine_b200.CudaWeightStore(ctx)
+
+    # Rings of distinct weight copies, each ring larger than 2x L2.
+    rings = {}
+    for vt in FORMATS:
+        for n, k in SHAPES:
+            nbytes = synth.encoded_bytes(vt, k, n)
+            copies = (2 * L2_BYTES + nbytes - 1) // nbytes + 1
+            ring = []
+            for c in range(copies):
+                name = f"{synth.TYPE_NAMES[vt]}.{n}x{k}.{c}"
+                data = synth.random_weight_device(vt, k, n, seed=(rank * 1000003 + vt * 4099 + n + k + c) & 0x7FFFFFFF, device=device)
+                ring.append(store.adopt(engine_b200.WeightTensorSpec.new(name, [k, n]), vt, data))
+            rings[(vt, n, k)] = ring
+    acts = {(k, m): torch.randn(m, k, device=device).to(torch.bfloat16) for _, k in SHAPES for m in MEMBERS}
+    outs = {(n, m): torch.empty(m, n, dtype=torch.float32, device=device) for n, _ in SHAPES for m in MEMBERS}
+    cursor = {key: 0 for key in rings}
+    cases = [(vt, n, k, m) for vt in FORMATS for n, k in SHAPES for m in MEMBERS]
+    step_bytes = sum(case_bytes(*c) for c in cases)
+    launches_per_step = sum((m + 7) // 8 for _, _, _, m in cases)
+
+    def launch(vt, n, k, m):
+        ring = rings[(vt, n, k)]
+        weight = ring[cursor[(vt, n, k)] % len(ring)]
+        cursor[(vt, n, k)] += 1
+        kernels[vt].execute_warp_batch(weight, acts[(k, m)], outs[(n, m)], m)
+
+    def step():
+        for c in cases:
+            launch(*c)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def capture(fn):
+        """Record fn's launches into a CUDA graph on the library's stream; None if capture is refused."""
+        if args.no_graph:
+            return None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn()
+            return graph
+        except Exception as exc:  # fall back to plain launches, and say so in the output
+            sys.stderr.write(f"CUDA graph capture failed ({exc}); timing eager launches\n")
+            torch.cuda.synchronize()
+            return None
+
+    torch.cuda.synchronize()
+    step()  # first launches set per-kernel attributes, which must not happen inside a capture
+    torch.cuda.synchronize()
+    step_graph = capture(step)
+
+    def run_step():
+        if step_graph is not None:
+            with torch.cuda.stream(stream):
+                step_graph.replay()
+        else:
+            step()
+
+    for _ in range(args.warmup):
+        run_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(ctx.stream)
+    for _ in range(args.steps):
+        run_step()
+    stop.record(ctx.stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host activations in, host outputs out, through ribn_gemv_host
+    max_stage = max(m * k * 2 + 256 + m * n * 4 for _, n, k, m in cases)
+    ctx.reserve_staging(max_stage + 4096)
+    host_x = {key: t.cpu().pin_memory() for key, t in acts.items()}
+    host_y = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in outs.items()}
+
+    def e2e_step():
+        for vt, n, k, m in cases:
+            ring = rings[(vt, n, k)]
+            weight = ring[cursor[(vt, n, k)] % len(ring)]
+            cursor[(vt, n, k)] += 1
+            kernels[vt].inner.execute_host(weight, host_x[(k, m)], host_y[(n, m)], m)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
+    h2d = sum(m * k * 2 for _, _, k, m in cases)
+    d2h = sum(m * n * 4 for _, n, _, m in cases)
+
+    breakdown = None
+    if args.cases and rank == 0:
+        breakdown = {}
+        for c in cases:
+            reps = 2 * len(rings[(c[0], c[1], c[2])])  # two trips round the ring of cold copies
+
+            def burst(c=c, reps=reps):
+                for _ in range(reps):
+                    launch(*c)
+
+            graph = capture(burst)
+            replay = (lambda g=graph: g.replay()) if graph is not None else burst
+            with torch.cuda.stream(stream):
+                replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ctx.stream)
+                replay()
+                b.record(ctx.stream)
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) / reps * 1e3
+            vt, n, k, m = c
+            breakdown[f"{synth.TYPE_NAMES[vt]}_{n}x{k}_M{m}"] = {"us": round(us, 2), "GBps": round(case_bytes(*c) / us / 1e3, 1)}
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        line = {
+            "metric": "qgemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gemv_sweep" if not args.only else f"single case {args.only} (profiling run, not the benchmark)",
+                       "formats": [synth.TYPE_NAMES[v] for v in FORMATS], "shapes_NxK": SHAPES,
+                       "members": MEMBERS, "activations": "bf16", "outputs": "f32",
+                       "l2": "ring of distinct weight copies > 2x L2 per (format, shape); inputs larger than L2",
+                       "parallelism": "replicas" if world > 1 else "single", "gemv_variant": args.variant,
+                       "cuda_graph": step_graph is not None},
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s",
+                         "kernel": "gemv_kernel (all launches of the step)", "bytes_per_step": step_bytes},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if breakdown is not None:
+            line["cases"] = breakdown
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline_leg()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

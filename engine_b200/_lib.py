@@ -1,0 +1,88 @@
+"""ctypes binding of libribn_b200.so (the C ABI declared in include/ribn_b200.h).
+
+There is no fallback: if the shared library is missing or does not export a declared symbol,
+importing fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libribn_b200.so")
+
+RIBN_OK = 0
+RIBN_E_DRIVER = 1
+RIBN_E_INVALID_WEIGHT = 2
+RIBN_E_UNSUPPORTED_TYPE = 3
+RIBN_E_SHAPE_OVERFLOW = 4
+RIBN_E_INPUT_LENGTH = 5
+RIBN_E_OUTPUT_LENGTH = 6
+RIBN_E_CONTEXT_MISMATCH = 7
+RIBN_E_TIMEOUT = 8
+RIBN_E_INVALID_ARGUMENT = 9
+
+RIBN_F32 = 0
+RIBN_BF16 = 1
+MAX_GEMV_MEMBERS = 64
+
+
+class QWeight(ctypes.Structure):
+    """struct ribn_qweight"""
+
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("encoded_bytes", ctypes.c_uint64),
+        ("value_type", ctypes.c_uint32),
+        ("rank", ctypes.c_uint32),
+        ("dimensions", ctypes.c_uint64 * 4),
+    ]
+
+
+_u64p = ctypes.POINTER(ctypes.c_uint64)
+_vp = ctypes.c_void_p
+_qwp = ctypes.POINTER(QWeight)
+
+# name -> (restype, argtypes); one entry per declaration in include/ribn_b200.h
+SIGNATURES = {
+    "ribn_create": (ctypes.c_int, [ctypes.c_int, _vp, ctypes.POINTER(_vp)]),
+    "ribn_destroy": (None, [_vp]),
+    "ribn_synchronize": (ctypes.c_int, [_vp]),
+    "ribn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "ribn_last_error": (ctypes.c_char_p, [_vp]),
+    "ribn_last_error_detail": (None, [_vp, _u64p, _u64p]),
+    "ribn_set_option": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_int64]),
+    "ribn_tensor_layout": (ctypes.c_int, [ctypes.c_uint32, _u64p, _u64p]),
+    "ribn_validate_quantized_geometry": (ctypes.c_int, [_qwp, ctypes.c_uint32, _u64p, _u64p]),
+    "ribn_dequantize": (ctypes.c_int, [_vp, _qwp, _vp, ctypes.c_uint64]),
+    "ribn_gemv": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_int,
+                                 ctypes.c_uint64, ctypes.c_uint32]),
+    "ribn_reserve_staging": (ctypes.c_int, [_vp, ctypes.c_uint64]),
+    "ribn_gemv_host": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp,
+                                      ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
+    "ribn_rms_norm": (ctypes.c_int, [_vp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64, _vp, ctypes.c_int,
+                                     ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing. Build it with `python -m engine_b200.build` (needs nvcc; the library "
+            "targets sm_100a only and has no CPU or PyTorch fallback)."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild with `python -m engine_b200.build --force`") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib

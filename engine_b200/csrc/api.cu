@@ -1,0 +1,475 @@
+// C ABI of the library: context, validation, error reporting, dispatch.
+//
+// Host-side twin of the reference's kernel wrapper layer
+// (crates/nvidia/src/quantized.rs:143-488, :1755-1804 and
+// crates/nvidia/src/model_ops.rs:1714-1824 of the reference project): every
+// check that layer performs before a launch is performed here, in the same
+// order, with the same error classes and message wording.
+#include <cuda_runtime.h>
+
+#include <cinttypes>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <new>
+#include <string>
+
+#include "../../include/ribn_b200.h"
+#include "internal.h"
+
+struct ribn_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int* device_status = nullptr;   // one word, written by kernels whose bounded waits ran out
+    void* staging = nullptr;        // device scratch for the host-buffer entry points
+    uint64_t staging_bytes = 0;
+    int variant = 0;                // GEMV tuning variant (ribn_set_option)
+    std::string message;
+    uint64_t expected = 0, actual = 0;
+};
+
+namespace {
+
+using ribn::GemvArgs;
+
+struct Layout {
+    uint64_t elements, bytes;
+};
+
+// crates/gguf/src/lib.rs:1051-1083
+bool tensor_layout(uint32_t t, Layout* out) {
+    switch (t) {
+        case 0: case 26: *out = {1, 4}; return true;
+        case 1: case 25: case 30: *out = {1, 2}; return true;
+        case 2: case 20: *out = {32, 18}; return true;
+        case 3: *out = {32, 20}; return true;
+        case 6: *out = {32, 22}; return true;
+        case 7: *out = {32, 24}; return true;
+        case 8: *out = {32, 34}; return true;
+        case 9: *out = {32, 36}; return true;
+        case 10: *out = {256, 84}; return true;
+        case 11: case 21: *out = {256, 110}; return true;
+        case 12: *out = {256, 144}; return true;
+        case 13: *out = {256, 176}; return true;
+        case 14: *out = {256, 210}; return true;
+        case 15: *out = {256, 292}; return true;
+        case 16: case 35: *out = {256, 66}; return true;
+        case 17: *out = {256, 74}; return true;
+        case 18: *out = {256, 98}; return true;
+        case 19: *out = {256, 50}; return true;
+        case 22: *out = {256, 82}; return true;
+        case 23: *out = {256, 136}; return true;
+        case 24: *out = {1, 1}; return true;
+        case 27: case 28: *out = {1, 8}; return true;
+        case 29: *out = {256, 56}; return true;
+        case 34: *out = {256, 54}; return true;
+        case 39: *out = {32, 17}; return true;
+        case 40: *out = {64, 36}; return true;
+        case 41: *out = {128, 18}; return true;
+        case 42: *out = {64, 18}; return true;
+        default: return false;
+    }
+}
+
+const char* type_label(uint32_t t) {
+    switch (t) {
+        case RIBN_TYPE_Q8_0: return "Q8_0";
+        case RIBN_TYPE_Q4_K: return "Q4_K";
+        case RIBN_TYPE_Q5_K: return "Q5_K";
+        case RIBN_TYPE_Q6_K: return "Q6_K";
+        default: return "?";
+    }
+}
+
+bool supported_type(uint32_t t) {
+    return t == RIBN_TYPE_Q8_0 || t == RIBN_TYPE_Q4_K || t == RIBN_TYPE_Q5_K || t == RIBN_TYPE_Q6_K;
+}
+
+// A failed check: status + message + the two numbers some classes carry.
+struct Failure {
+    int status = RIBN_OK;
+    std::string message;
+    uint64_t expected = 0, actual = 0;
+};
+
+Failure fail(int status, std::string message, uint64_t expected = 0, uint64_t actual = 0) {
+    Failure f;
+    f.status = status;
+    f.message = std::move(message);
+    f.expected = expected;
+    f.actual = actual;
+    return f;
+}
+
+std::string fmt(const char* pattern, ...) {
+    char buffer[256];
+    va_list args;
+    va_start(args, pattern);
+    vsnprintf(buffer, sizeof buffer, pattern, args);
+    va_end(args);
+    return buffer;
+}
+
+bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) { return __builtin_mul_overflow(a, b, out); }
+
+// validate_quantized_geometry, crates/nvidia/src/quantized.rs:1755-1804, check for check.
+Failure validate_geometry(const ribn_qweight* w, uint32_t expected_type, uint64_t* k_out, uint64_t* n_out) {
+    if (w == nullptr) return fail(RIBN_E_INVALID_ARGUMENT, "null weight descriptor");
+    uint32_t type = expected_type;
+    if (type == 0) {
+        // QwenGemvKernel::from_value_type (staging.rs:108-140): the kernel follows the weight's type.
+        type = w->value_type;
+        if (!supported_type(type))
+            return fail(RIBN_E_INVALID_WEIGHT, fmt("no quantized GEMV kernel for GGML value type %u", type));
+    } else if (!supported_type(type)) {
+        return fail(RIBN_E_INVALID_WEIGHT, fmt("no quantized GEMV kernel for GGML value type %u", type));
+    }
+    if (w->value_type != type)
+        return fail(RIBN_E_UNSUPPORTED_TYPE,
+                    fmt("quantized GEMV requires GGML value type %u, got %u", type, w->value_type), type, w->value_type);
+    if (w->rank != 2) return fail(RIBN_E_INVALID_WEIGHT, fmt("invalid quantized weight: expected rank-2 tensor, got rank %u", w->rank));
+    Layout layout{};
+    tensor_layout(type, &layout);
+    const uint64_t k = w->dimensions[0], n = w->dimensions[1];
+    if (k == 0 || n == 0 || k % layout.elements != 0)
+        return fail(RIBN_E_INVALID_WEIGHT,
+                    fmt("invalid quantized weight: %s shape is %" PRIu64 "x%" PRIu64
+                        "; input size must be a positive multiple of %" PRIu64,
+                        type_label(type), k, n, layout.elements));
+    uint64_t blocks = 0, expected_bytes = 0;
+    if (mul_overflows(k / layout.elements, n, &blocks) || mul_overflows(blocks, layout.bytes, &expected_bytes))
+        return fail(RIBN_E_SHAPE_OVERFLOW, "quantized GEMV shape does not fit CUDA launch arguments");
+    if (w->encoded_bytes != expected_bytes)
+        return fail(RIBN_E_INVALID_WEIGHT,
+                    fmt("invalid quantized weight: encoded length is %" PRIu64 ", expected %" PRIu64, w->encoded_bytes,
+                        expected_bytes));
+    // The reference's kernels index with 32-bit ints, so it refuses blocks > i32::MAX / block_bytes
+    // and dims > i32::MAX.  These kernels index bytes with 64 bits; only the dimension limit is kept.
+    const uint64_t i32_max = static_cast<uint64_t>(std::numeric_limits<int32_t>::max());
+    if (k > i32_max || n > i32_max)
+        return fail(RIBN_E_SHAPE_OVERFLOW, "quantized GEMV shape does not fit CUDA launch arguments");
+    if (k_out) *k_out = k;
+    if (n_out) *n_out = n;
+    return Failure{};
+}
+
+int record(ribn_ctx* ctx, const Failure& f) {
+    if (ctx != nullptr) {
+        ctx->message = f.message;
+        ctx->expected = f.expected;
+        ctx->actual = f.actual;
+    }
+    return f.status;
+}
+
+int record_cuda(ribn_ctx* ctx, cudaError_t e, const char* what) {
+    return record(ctx, fail(RIBN_E_DRIVER, fmt("CUDA driver error: %s: %s", what, cudaGetErrorString(e))));
+}
+
+bool valid_dtype(int d) { return d == RIBN_F32 || d == RIBN_BF16; }
+uint64_t dtype_bytes(int d) { return d == RIBN_BF16 ? 2 : 4; }
+
+// ContextMismatch (quantized.rs:326-331): every buffer must be device memory of the context's GPU.
+Failure check_device_pointer(const ribn_ctx* ctx, const void* p, const char* what) {
+    if (p == nullptr) return fail(RIBN_E_INVALID_ARGUMENT, fmt("%s pointer is null", what));
+    if (reinterpret_cast<uintptr_t>(p) % 16 != 0)
+        return fail(RIBN_E_INVALID_ARGUMENT, fmt("%s pointer is not 16-byte aligned", what));
+    cudaPointerAttributes attr{};
+    const cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RIBN_E_CONTEXT_MISMATCH, "quantized GEMV buffers and stream belong to different CUDA contexts");
+    }
+    if ((attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) || attr.device != ctx->device)
+        return fail(RIBN_E_CONTEXT_MISMATCH, "quantized GEMV buffers and stream belong to different CUDA contexts");
+    return Failure{};
+}
+
+struct DeviceGuard {
+    int previous = -1;
+    explicit DeviceGuard(int device) {
+        cudaGetDevice(&previous);
+        if (previous != device) cudaSetDevice(device);
+    }
+    ~DeviceGuard() {
+        int now = -1;
+        cudaGetDevice(&now);
+        if (previous >= 0 && now != previous) cudaSetDevice(previous);
+    }
+};
+
+// Everything ribn_gemv checks before launching, shared with the host-buffer variant.
+Failure validate_gemv(const ribn_qweight* w, uint32_t expected_type, int x_dtype, uint64_t x_len, int y_dtype,
+                      uint64_t y_len, uint32_t members, uint64_t* k, uint64_t* n) {
+    if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return fail(RIBN_E_INVALID_ARGUMENT, "unknown activation dtype");
+    // quantized.rs:458-469: members == 0 and members over the cap are refused before geometry.
+    if (members == 0)
+        return fail(RIBN_E_INPUT_LENGTH, "quantized GEMV input has 0 values, expected 1", 1, 0);
+    if (members > RIBN_MAX_GEMV_MEMBERS)
+        return fail(RIBN_E_INVALID_WEIGHT,
+                    fmt("invalid quantized weight: batch variant supports at most %u members", RIBN_MAX_GEMV_MEMBERS));
+    Failure f = validate_geometry(w, expected_type, k, n);
+    if (f.status != RIBN_OK) return f;
+    uint64_t expected_in = 0, expected_out = 0;
+    if (mul_overflows(*k, members, &expected_in) || mul_overflows(*n, members, &expected_out))
+        return fail(RIBN_E_SHAPE_OVERFLOW, "quantized GEMV shape does not fit CUDA launch arguments");
+    if (x_len != expected_in)
+        return fail(RIBN_E_INPUT_LENGTH,
+                    fmt("quantized GEMV input has %" PRIu64 " values, expected %" PRIu64, x_len, expected_in), expected_in,
+                    x_len);
+    if (y_len != expected_out)
+        return fail(RIBN_E_OUTPUT_LENGTH,
+                    fmt("quantized GEMV output has %" PRIu64 " values, expected %" PRIu64, y_len, expected_out),
+                    expected_out, y_len);
+    return Failure{};
+}
+
+int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y,
+                 int y_dtype, uint32_t members) {
+    GemvArgs a{};
+    a.weights = static_cast<const uint8_t*>(w->data);
+    a.weight_bytes = w->encoded_bytes;
+    a.value_type = w->value_type;
+    a.k = static_cast<int>(k);
+    a.n = static_cast<int>(n);
+    a.x_bf16 = x_dtype == RIBN_BF16;
+    a.y_bf16 = y_dtype == RIBN_BF16;
+    a.device_status = ctx->device_status;
+    a.sm_count = ctx->sm_count;
+    a.variant = ctx->variant;
+    a.stream = ctx->stream;
+    // The CUDA-core kernel holds at most eight activation rows in registers; larger batches
+    // run as consecutive launches over member groups (the weights stay in L2 between them).
+    for (uint32_t m0 = 0; m0 < members; m0 += 8) {
+        a.members = static_cast<int>(members - m0 < 8 ? members - m0 : 8);
+        a.x = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(m0) * k * dtype_bytes(x_dtype);
+        a.y = static_cast<uint8_t*>(y) + static_cast<uint64_t>(m0) * n * dtype_bytes(y_dtype);
+        const cudaError_t e = ribn::launch_gemv(a);
+        if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+    }
+    return RIBN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ribn_create(int device, void* cuda_stream, ribn_ctx** out) {
+    if (out == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return RIBN_E_DRIVER;
+    }
+    DeviceGuard guard(device);
+    cudaDeviceProp prop{};
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return RIBN_E_DRIVER;
+    // The kernels are built for sm_100a only and there is no fallback path.
+    if (prop.major != 10) return RIBN_E_DRIVER;
+    ribn_ctx* ctx = new (std::nothrow) ribn_ctx();
+    if (ctx == nullptr) return RIBN_E_DRIVER;
+    ctx->device = device;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->sm_count = prop.multiProcessorCount;
+    e = cudaMalloc(&ctx->device_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->device_status, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        delete ctx;
+        return RIBN_E_DRIVER;
+    }
+    *out = ctx;
+    return RIBN_OK;
+}
+
+void ribn_destroy(ribn_ctx* ctx) {
+    if (ctx == nullptr) return;
+    DeviceGuard guard(ctx->device);
+    if (ctx->staging != nullptr) cudaFree(ctx->staging);
+    if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
+    delete ctx;
+}
+
+int ribn_synchronize(ribn_ctx* ctx) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
+    int status = 0;
+    e = cudaMemcpy(&status, ctx->device_status, sizeof status, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "status readback");
+    if (status != ribn::kDeviceOk) {
+        cudaMemset(ctx->device_status, 0, sizeof(int));
+        return record(ctx, fail(RIBN_E_TIMEOUT, "a bounded device-side wait ran out; results of this stream are invalid"));
+    }
+    return RIBN_OK;
+}
+
+const char* ribn_status_string(int status) {
+    switch (status) {
+        case RIBN_OK: return "ok";
+        case RIBN_E_DRIVER: return "CUDA driver error";
+        case RIBN_E_INVALID_WEIGHT: return "invalid quantized weight";
+        case RIBN_E_UNSUPPORTED_TYPE: return "unsupported GGML value type for this kernel";
+        case RIBN_E_SHAPE_OVERFLOW: return "quantized GEMV shape does not fit CUDA launch arguments";
+        case RIBN_E_INPUT_LENGTH: return "input length mismatch";
+        case RIBN_E_OUTPUT_LENGTH: return "output length mismatch";
+        case RIBN_E_CONTEXT_MISMATCH: return "quantized GEMV buffers and stream belong to different CUDA contexts";
+        case RIBN_E_TIMEOUT: return "bounded device wait timed out";
+        case RIBN_E_INVALID_ARGUMENT: return "invalid argument";
+        default: return "unknown status";
+    }
+}
+
+const char* ribn_last_error(const ribn_ctx* ctx) { return ctx == nullptr ? "" : ctx->message.c_str(); }
+
+void ribn_last_error_detail(const ribn_ctx* ctx, uint64_t* expected, uint64_t* actual) {
+    if (expected) *expected = ctx ? ctx->expected : 0;
+    if (actual) *actual = ctx ? ctx->actual : 0;
+}
+
+int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
+    if (ctx == nullptr || name == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (std::strcmp(name, "gemv_variant") == 0) {
+        ctx->variant = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, fmt("unknown option %s", name)));
+}
+
+int ribn_tensor_layout(uint32_t value_type, uint64_t* block_elements, uint64_t* block_bytes) {
+    Layout layout{};
+    if (!tensor_layout(value_type, &layout)) return RIBN_E_UNSUPPORTED_TYPE;
+    if (block_elements) *block_elements = layout.elements;
+    if (block_bytes) *block_bytes = layout.bytes;
+    return RIBN_OK;
+}
+
+int ribn_validate_quantized_geometry(const ribn_qweight* weight, uint32_t expected_type, uint64_t* input_size,
+                                     uint64_t* output_size) {
+    return validate_geometry(weight, expected_type, input_size, output_size).status;
+}
+
+int ribn_dequantize(ribn_ctx* ctx, const ribn_qweight* weight, float* out_device, uint64_t out_len) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    uint64_t k = 0, n = 0;
+    Failure f = validate_geometry(weight, 0, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    uint64_t expected = 0;
+    if (mul_overflows(k, n, &expected)) return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "tensor element count overflows"));
+    if (out_len != expected)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH,
+                                fmt("dequantize output has %" PRIu64 " values, expected %" PRIu64, out_len, expected),
+                                expected, out_len));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_dequantize(static_cast<const uint8_t*>(weight->data), weight->value_type, k, n,
+                                                  out_device, ctx->sm_count, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "dequantize launch");
+    return RIBN_OK;
+}
+
+int ribn_gemv(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_device, int x_dtype,
+              uint64_t x_len, void* y_device, int y_dtype, uint64_t y_len, uint32_t members) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    uint64_t k = 0, n = 0;
+    Failure f = validate_gemv(weight, expected_type, x_dtype, x_len, y_dtype, y_len, members, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    return enqueue_gemv(ctx, weight, k, n, x_device, x_dtype, y_device, y_dtype, members);
+}
+
+int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (bytes <= ctx->staging_bytes) return RIBN_OK;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
+    if (ctx->staging != nullptr) cudaFree(ctx->staging);
+    ctx->staging = nullptr;
+    ctx->staging_bytes = 0;
+    e = cudaMalloc(&ctx->staging, bytes);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "staging allocation");
+    ctx->staging_bytes = bytes;
+    return RIBN_OK;
+}
+
+int ribn_gemv_host(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_host, int x_dtype,
+                   uint64_t x_len, void* y_host, int y_dtype, uint64_t y_len, uint32_t members) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    uint64_t k = 0, n = 0;
+    Failure f = validate_gemv(weight, expected_type, x_dtype, x_len, y_dtype, y_len, members, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    if (x_host == nullptr || y_host == nullptr) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "host pointer is null"));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const uint64_t x_bytes = x_len * dtype_bytes(x_dtype);
+    const uint64_t y_bytes = y_len * dtype_bytes(y_dtype);
+    const uint64_t y_offset = (x_bytes + 255) & ~255ull;
+    if (y_offset + y_bytes > ctx->staging_bytes)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT,
+                                fmt("staging buffer holds %" PRIu64 " bytes, this call needs %" PRIu64
+                                    " (ribn_reserve_staging)",
+                                    ctx->staging_bytes, y_offset + y_bytes)));
+    uint8_t* x_dev = static_cast<uint8_t*>(ctx->staging);
+    uint8_t* y_dev = x_dev + y_offset;
+    cudaError_t e = cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "activation upload");
+    const int status = enqueue_gemv(ctx, weight, k, n, x_dev, x_dtype, y_dev, y_dtype, members);
+    if (status != RIBN_OK) return status;
+    e = cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "output download");
+    e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
+    return RIBN_OK;
+}
+
+int ribn_rms_norm(ribn_ctx* ctx, const void* x_device, int x_dtype, uint64_t x_len, const float* weight_device,
+                  uint64_t weight_len, void* y_device, int y_dtype, uint64_t y_len, uint32_t members, uint32_t length,
+                  float eps) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype))
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "unknown activation dtype"));
+    // CudaQwen35Ops::rms_norm_batch (model_ops.rs:1770-1824): zero-sized shapes and length
+    // mismatches are refused before the launch.
+    if (members == 0 || length == 0)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH, "RMSNorm needs at least one vector of at least one value", 1, 0));
+    const uint64_t expected = static_cast<uint64_t>(members) * length;
+    if (x_len != expected)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH,
+                                fmt("RMSNorm input has %" PRIu64 " values, expected %" PRIu64, x_len, expected), expected,
+                                x_len));
+    if (weight_len != length)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH,
+                                fmt("RMSNorm weight has %" PRIu64 " values, expected %u", weight_len, length), length,
+                                weight_len));
+    if (y_len != expected)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH,
+                                fmt("RMSNorm output has %" PRIu64 " values, expected %" PRIu64, y_len, expected), expected,
+                                y_len));
+    if (length > static_cast<uint32_t>(std::numeric_limits<int32_t>::max()))
+        return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "RMSNorm length does not fit CUDA launch arguments"));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, weight_device, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_rms_norm(x_device, x_dtype == RIBN_BF16, weight_device, y_device,
+                                                y_dtype == RIBN_BF16, static_cast<int>(members),
+                                                static_cast<int>(length), eps, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "RMSNorm launch");
+    return RIBN_OK;
+}
+
+}  // extern "C"

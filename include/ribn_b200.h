@@ -1,0 +1,149 @@
+/*
+ * ribn_b200 -- B200 (sm_100a) kernels for the GGUF block-quantized matmul path,
+ * behind a C ABI.
+ *
+ * The reference engine has no C ABI: its seam is the Rust API of its CUDA crate
+ * (kernel wrapper objects over a driver binding).  Each entry point below names
+ * the reference interface it replaces, by file:line inside the reference
+ * project, so a thin `extern "C"` block on the Rust side can swap the wrappers
+ * one for one.
+ *
+ * Conventions kept from the reference:
+ *   - the caller owns every buffer; a context owns only its stream handle;
+ *   - weights are immutable device bytes in GGUF block layout, GGML dimension
+ *     order [K (contiguous input), N (output rows)]      (cuda.rs:154-183,
+ *     quantized.rs:138-142);
+ *   - activations and outputs are batch-major [members][K] / [members][N]
+ *     (quantized.rs:265-267);
+ *   - a call validates, enqueues on the context's stream and returns; no
+ *     allocation and no host synchronisation on the device-pointer entry
+ *     points (quantized.rs:357-362);
+ *   - every error is raised before anything is launched and leaves the outputs
+ *     untouched (tests/q4_q8_1.rs:298-349);
+ *   - a context is not thread-safe: one caller at a time (adapter.rs:16).
+ *
+ * All pointers named *device* must be device memory of the context's GPU,
+ * 16-byte aligned.  There is no CPU fallback anywhere in this library.
+ */
+#ifndef RIBN_B200_H
+#define RIBN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RIBN_ABI_VERSION 1
+
+/* Mirrors CudaQuantizedKernelError one to one (quantized.rs:90-100); TIMEOUT is
+ * the status of a bounded device-side wait that ran out, INVALID_ARGUMENT covers
+ * null/misaligned pointers, which the reference's typed slices cannot express. */
+typedef enum ribn_status {
+    RIBN_OK = 0,
+    RIBN_E_DRIVER = 1,             /* Driver(String) */
+    RIBN_E_INVALID_WEIGHT = 2,     /* InvalidWeight(String) */
+    RIBN_E_UNSUPPORTED_TYPE = 3,   /* UnsupportedValueType { expected, actual } */
+    RIBN_E_SHAPE_OVERFLOW = 4,     /* ShapeOverflow */
+    RIBN_E_INPUT_LENGTH = 5,       /* InputLength { expected, actual } */
+    RIBN_E_OUTPUT_LENGTH = 6,      /* OutputLength { expected, actual } */
+    RIBN_E_CONTEXT_MISMATCH = 7,   /* ContextMismatch */
+    RIBN_E_TIMEOUT = 8,
+    RIBN_E_INVALID_ARGUMENT = 9
+} ribn_status;
+
+typedef enum ribn_dtype { RIBN_F32 = 0, RIBN_BF16 = 1 } ribn_dtype;
+
+/* GGML value types on the path (crates/gguf/src/lib.rs:1051-1083). */
+#define RIBN_TYPE_Q8_0 8u
+#define RIBN_TYPE_Q4_K 12u
+#define RIBN_TYPE_Q5_K 13u
+#define RIBN_TYPE_Q6_K 14u
+
+/* Largest `members` ribn_gemv accepts (the reference's cap is 8,
+ * quantized.rs:12; larger batches go through ribn_gemm). */
+#define RIBN_MAX_GEMV_MEMBERS 64u
+
+/* CudaQuantizedWeight (cuda.rs:157-183): opaque encoded bytes on the device +
+ * value type + WeightTensorSpec dimensions. */
+typedef struct ribn_qweight {
+    const void *data;        /* device pointer, GGUF-encoded blocks */
+    uint64_t encoded_bytes;  /* exact length of `data` */
+    uint32_t value_type;     /* GGML type id */
+    uint32_t rank;           /* number of valid entries in `dimensions` */
+    uint64_t dimensions[4];  /* GGML order: dimensions[0] = K, dimensions[1] = N */
+} ribn_qweight;
+
+typedef struct ribn_ctx ribn_ctx;
+
+/* One owner per (device, stream), like the reference's kernel objects that hold
+ * an Arc<CudaStream> (quantized.rs:143-160).  `cuda_stream` is a cudaStream_t /
+ * CUstream (NULL = the legacy default stream).  Nothing is compiled at run time:
+ * the kernels are built ahead of time for sm_100a (the reference NVRTC-compiles
+ * once per process, quantized.rs:76-88, :169-182). */
+int ribn_create(int device, void *cuda_stream, ribn_ctx **out);
+void ribn_destroy(ribn_ctx *ctx);
+
+/* Block until everything enqueued on the context's stream has finished and
+ * report any bounded device wait that timed out (RIBN_E_TIMEOUT). */
+int ribn_synchronize(ribn_ctx *ctx);
+
+const char *ribn_status_string(int status);
+/* Message of the last failing call on `ctx`, worded like the Display impl of
+ * the reference error (quantized.rs:102-137).  Valid until the next call. */
+const char *ribn_last_error(const ribn_ctx *ctx);
+/* UnsupportedValueType / InputLength / OutputLength carry two numbers. */
+void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *actual);
+
+/* Tuning knobs, the counterpart of the reference's plain option structs
+ * (GemvMode, decode.rs:298-307).  "gemv_variant": 0 = default tile geometry,
+ * 1..3 = alternatives kept for measurement. */
+int ribn_set_option(ribn_ctx *ctx, const char *name, int64_t value);
+
+/* tensor_layout (crates/gguf/src/lib.rs:1051-1083): GGML type -> (elements per
+ * block, bytes per block).  RIBN_E_UNSUPPORTED_TYPE for unknown ids. */
+int ribn_tensor_layout(uint32_t value_type, uint64_t *block_elements, uint64_t *block_bytes);
+
+/* validate_quantized_geometry (quantized.rs:1755-1804).  `expected_type` 0 means
+ * "whatever the weight says, if it is one of the four supported types".  Pure
+ * host code, no CUDA call. */
+int ribn_validate_quantized_geometry(const ribn_qweight *weight, uint32_t expected_type,
+                                     uint64_t *input_size, uint64_t *output_size);
+
+/* Device twin of dequantize_block applied to every block of a tensor
+ * (crates/gguf/src/lib.rs:520-547, :589-661): out[n*K + k] as f32, bit-exact
+ * with the reference decoder for every finite value.  out_len = N*K. */
+int ribn_dequantize(ribn_ctx *ctx, const ribn_qweight *weight, float *out_device, uint64_t out_len);
+
+/* Cuda{Q4K,Q5K,Q6K,Q8_0}Gemv::execute / execute_warp (members = 1) and
+ * execute_warp_batch (quantized.rs:1612-1650, :401-487), and
+ * QwenGemvKernel::execute* (staging.rs:108-216) when expected_type = 0.
+ *   y[m][n] = sum_k dequant(W[n][k]) * x[m][k],  f32 accumulation.
+ * x_len / y_len are element counts and must equal members*K / members*N.
+ * members = 0 -> RIBN_E_INPUT_LENGTH {expected 1, actual 0}; members >
+ * RIBN_MAX_GEMV_MEMBERS -> RIBN_E_INVALID_WEIGHT (quantized.rs:458-469). */
+int ribn_gemv(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
+              const void *x_device, int x_dtype, uint64_t x_len,
+              void *y_device, int y_dtype, uint64_t y_len, uint32_t members);
+
+/* Same operation with HOST activations and outputs: copies x to a staging
+ * buffer on the device, runs the GEMV, copies y back and waits.  The staging
+ * buffer must have been sized with ribn_reserve_staging first (that call is the
+ * only one that allocates). */
+int ribn_reserve_staging(ribn_ctx *ctx, uint64_t bytes);
+int ribn_gemv_host(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
+                   const void *x_host, int x_dtype, uint64_t x_len,
+                   void *y_host, int y_dtype, uint64_t y_len, uint32_t members);
+
+/* CudaQwen35Ops::rms_norm / rms_norm_batch (model_ops.rs:1714-1824, kernels
+ * :106-199): y[m][i] = x[m][i] * rsqrt(mean_i(x[m]^2) + eps) * weight[i].
+ * x_len and y_len must equal members*length, weight_len must equal length. */
+int ribn_rms_norm(ribn_ctx *ctx, const void *x_device, int x_dtype, uint64_t x_len,
+                  const float *weight_device, uint64_t weight_len,
+                  void *y_device, int y_dtype, uint64_t y_len,
+                  uint32_t members, uint32_t length, float eps);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RIBN_B200_H */
