@@ -26,6 +26,9 @@ struct ribn_ctx {
     void* staging = nullptr;        // device scratch for the host-buffer entry points
     uint64_t staging_bytes = 0;
     int variant = 0;                // GEMV tuning variant (ribn_set_option)
+    int gemv_path = 0;              // 0 = choose per shape, 1 = f32 CUDA-core kernel only, 2 = integer-dot kernel only
+    void* workspace = nullptr;      // device scratch owned by the context (fused-op intermediates)
+    uint64_t workspace_bytes = 0;
     std::string message;
     uint64_t expected = 0, actual = 0;
 };
@@ -227,7 +230,7 @@ Failure validate_gemv(const ribn_qweight* w, uint32_t expected_type, int x_dtype
 }
 
 int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y,
-                 int y_dtype, uint32_t members) {
+                 int y_dtype, uint32_t members, const float* norm_weight = nullptr, float eps = 0.0f) {
     GemvArgs a{};
     a.weights = static_cast<const uint8_t*>(w->data);
     a.weight_bytes = w->encoded_bytes;
@@ -240,11 +243,46 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.sm_count = ctx->sm_count;
     a.variant = ctx->variant;
     a.stream = ctx->stream;
-    // The CUDA-core kernel holds at most eight activation rows in registers; larger batches
-    // run as consecutive launches over member groups (the weights stay in L2 between them).
+    // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
+    // packed once into the context workspace, then consumed four member rows per launch (the
+    // weights stay in L2 between the launches of one call).
+    const int members_per_launch = members < 4 ? static_cast<int>(members) : 4;
+    const uint64_t stride = ribn::packed_activation_stride(ribn::padded_k(a.k));
+    if (ctx->gemv_path != 1 && ribn::gemv_dp4a_fits(a.value_type, a.k, members_per_launch) &&
+        stride * members <= ctx->workspace_bytes) {
+        cudaError_t e = ribn::launch_quantize_activations(x, a.x_bf16, norm_weight, eps, ctx->workspace,
+                                                          static_cast<int>(members), a.k, ctx->stream);
+        if (e != cudaSuccess) return record_cuda(ctx, e, "activation packing launch");
+        for (uint32_t m0 = 0; m0 < members; m0 += 4) {
+            a.members = static_cast<int>(members - m0 < 4 ? members - m0 : 4);
+            a.x = static_cast<const uint8_t*>(ctx->workspace) + static_cast<uint64_t>(m0) * stride;
+            a.y = static_cast<uint8_t*>(y) + static_cast<uint64_t>(m0) * n * dtype_bytes(y_dtype);
+            bool handled = false;
+            e = ribn::launch_gemv_dp4a(a, &handled);
+            if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+            if (!handled) return record(ctx, fail(RIBN_E_DRIVER, "integer-dot GEMV refused a shape it had accepted"));
+        }
+        return RIBN_OK;
+    }
+    if (ctx->gemv_path == 2)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "integer-dot GEMV cannot stage these activations in shared memory"));
+    // Path 2: f32 CUDA-core kernel, eight member rows per launch.
+    const void* x_in = x;
+    bool x_in_bf16 = a.x_bf16;
+    if (norm_weight != nullptr) {
+        const uint64_t need = static_cast<uint64_t>(members) * k * sizeof(float);
+        if (need > ctx->workspace_bytes)
+            return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "RMSNorm+GEMV intermediate does not fit the context workspace"));
+        const cudaError_t e = ribn::launch_rms_norm(x, a.x_bf16, norm_weight, ctx->workspace, false,
+                                                    static_cast<int>(members), a.k, eps, ctx->stream);
+        if (e != cudaSuccess) return record_cuda(ctx, e, "RMSNorm launch");
+        x_in = ctx->workspace;
+        x_in_bf16 = false;
+    }
+    a.x_bf16 = x_in_bf16;
     for (uint32_t m0 = 0; m0 < members; m0 += 8) {
         a.members = static_cast<int>(members - m0 < 8 ? members - m0 : 8);
-        a.x = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(m0) * k * dtype_bytes(x_dtype);
+        a.x = static_cast<const uint8_t*>(x_in) + static_cast<uint64_t>(m0) * k * (x_in_bf16 ? 2 : 4);
         a.y = static_cast<uint8_t*>(y) + static_cast<uint64_t>(m0) * n * dtype_bytes(y_dtype);
         const cudaError_t e = ribn::launch_gemv(a);
         if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
@@ -278,7 +316,11 @@ int ribn_create(int device, void* cuda_stream, ribn_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     e = cudaMalloc(&ctx->device_status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_status, 0, sizeof(int));
+    // Scratch for fused-op intermediates, allocated once here so that no later call allocates.
+    ctx->workspace_bytes = 32ull << 20;
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);
     if (e != cudaSuccess) {
+        if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
         delete ctx;
         return RIBN_E_DRIVER;
     }
@@ -290,6 +332,7 @@ void ribn_destroy(ribn_ctx* ctx) {
     if (ctx == nullptr) return;
     DeviceGuard guard(ctx->device);
     if (ctx->staging != nullptr) cudaFree(ctx->staging);
+    if (ctx->workspace != nullptr) cudaFree(ctx->workspace);
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
     delete ctx;
 }
@@ -336,6 +379,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     if (ctx == nullptr || name == nullptr) return RIBN_E_INVALID_ARGUMENT;
     if (std::strcmp(name, "gemv_variant") == 0) {
         ctx->variant = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "gemv_path") == 0 && value >= 0 && value <= 2) {
+        ctx->gemv_path = static_cast<int>(value);
         return RIBN_OK;
     }
     return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, fmt("unknown option %s", name)));
@@ -387,6 +434,26 @@ int ribn_gemv(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight,
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
     return enqueue_gemv(ctx, weight, k, n, x_device, x_dtype, y_device, y_dtype, members);
+}
+
+int ribn_rms_norm_gemv(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_device,
+                       int x_dtype, uint64_t x_len, const float* norm_weight_device, uint64_t norm_weight_len, float eps,
+                       void* y_device, int y_dtype, uint64_t y_len, uint32_t members) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    uint64_t k = 0, n = 0;
+    Failure f = validate_gemv(weight, expected_type, x_dtype, x_len, y_dtype, y_len, members, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    if (norm_weight_len != k)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH,
+                                fmt("RMSNorm weight has %" PRIu64 " values, expected %" PRIu64, norm_weight_len, k), k,
+                                norm_weight_len));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, norm_weight_device, "norm weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    return enqueue_gemv(ctx, weight, k, n, x_device, x_dtype, y_device, y_dtype, members, norm_weight_device, eps);
 }
 
 int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {

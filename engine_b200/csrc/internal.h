@@ -29,6 +29,26 @@ struct GemvArgs {
 
 cudaError_t launch_gemv(const GemvArgs& args);
 
+// Packed activations for the integer-dot GEMV.  Each member row of K values (padded with zeros to
+// kpad, a whole number of 256-element super-blocks) becomes, contiguously:
+//   q1[kpad] int8 | q2[kpad] int8 | dq[kpad/32] f32 | sum[kpad/32] f32
+// with x ~= dq * (256*q1 + q2) per block of 32 and sum the f32 sum of the block.
+__host__ __device__ inline unsigned long long packed_activation_stride(int kpad) {
+    return static_cast<unsigned long long>(kpad) * 2 + static_cast<unsigned long long>(kpad / 32) * 8;
+}
+inline int padded_k(int k) { return (k + 255) / 256 * 256; }
+
+// x [members][k] (f32 or bf16) -> packed rows; with norm_weight != nullptr the row is RMS-normalised
+// and scaled first (y = x * rsqrt(mean(x^2)+eps) * norm_weight), i.e. RMSNorm fused into the packer.
+cudaError_t launch_quantize_activations(const void* x, bool x_bf16, const float* norm_weight, float eps, void* packed,
+                                        int members, int k, cudaStream_t stream);
+
+// Integer-dot GEMV for 1..4 members over packed activations (args.x = packed rows).  *handled is
+// false when the shape does not fit (activations too large for shared memory); nothing was launched
+// then and the caller takes another path.
+cudaError_t launch_gemv_dp4a(const GemvArgs& args, bool* handled);
+bool gemv_dp4a_fits(uint32_t value_type, int k, int members);
+
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);
 

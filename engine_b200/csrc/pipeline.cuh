@@ -51,7 +51,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (spin > 64) __nanosleep(64);
+        if (spin > 4096) __nanosleep(64);
     }
     return false;
 }

@@ -213,6 +213,18 @@ class _CudaQuantizedGemv:
         """quantized.rs:1645: `members` activation rows [members][K] -> [members][N], weights read once."""
         self._run(weight, input, output, members)
 
+    def execute_rms_norm(self, weight: CudaQuantizedWeight, input: torch.Tensor, norm_weight: torch.Tensor, epsilon: float,
+                         output: torch.Tensor, members: int) -> None:
+        """rms_norm(_batch) followed by the GEMV (decode.rs:582-609) as one call: ribn_rms_norm_gemv."""
+        ctx = self.context
+        descriptor = weight.descriptor()
+        if norm_weight.dtype != torch.float32:
+            raise TypeError("RMSNorm weights are float32")
+        ctx.check(ctx._lib.ribn_rms_norm_gemv(ctx.handle, self.VALUE_TYPE, ctypes.byref(descriptor), input.data_ptr(),
+                                              _dtype_code(input), input.numel(), norm_weight.data_ptr(), norm_weight.numel(),
+                                              ctypes.c_float(epsilon), output.data_ptr(), _dtype_code(output), output.numel(),
+                                              members))
+
     def execute_host(self, weight: CudaQuantizedWeight, input: np.ndarray | torch.Tensor, output: np.ndarray | torch.Tensor,
                      members: int) -> None:
         """Host activations in, host outputs out (copies inside); needs context.reserve_staging()."""

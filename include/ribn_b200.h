@@ -96,8 +96,11 @@ const char *ribn_last_error(const ribn_ctx *ctx);
 void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *actual);
 
 /* Tuning knobs, the counterpart of the reference's plain option structs
- * (GemvMode, decode.rs:298-307).  "gemv_variant": 0 = default tile geometry,
- * 1..3 = alternatives kept for measurement. */
+ * (GemvMode, decode.rs:298-307).
+ *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
+ *                   2 = integer-dot kernel only (error if the shape does not fit);
+ *   "gemv_variant": tile geometry of the f32 kernel, 0 = default, 1..3 = alternatives
+ *                   kept for measurement. */
 int ribn_set_option(ribn_ctx *ctx, const char *name, int64_t value);
 
 /* tensor_layout (crates/gguf/src/lib.rs:1051-1083): GGML type -> (elements per
@@ -125,6 +128,17 @@ int ribn_dequantize(ribn_ctx *ctx, const ribn_qweight *weight, float *out_device
 int ribn_gemv(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
               const void *x_device, int x_dtype, uint64_t x_len,
               void *y_device, int y_dtype, uint64_t y_len, uint32_t members);
+
+/* The pair the reference's layer forward always issues back to back -- rms_norm
+ * (or rms_norm_batch) then gemv (decode.rs:582-609, :678-696) -- as one call:
+ *   y[m][n] = sum_k dequant(W[n][k]) * (x[m][k] * rsqrt(mean(x[m]^2)+eps) * norm_weight[k])
+ * Same result contract as ribn_rms_norm followed by ribn_gemv.  For members <= 4
+ * the normalisation runs in the GEMV kernel's prologue (no intermediate in
+ * memory); larger batches normalise into the context's workspace first. */
+int ribn_rms_norm_gemv(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
+                       const void *x_device, int x_dtype, uint64_t x_len,
+                       const float *norm_weight_device, uint64_t norm_weight_len, float eps,
+                       void *y_device, int y_dtype, uint64_t y_len, uint32_t members);
 
 /* Same operation with HOST activations and outputs: copies x to a staging
  * buffer on the device, runs the GEMV, copies y back and waits.  The staging

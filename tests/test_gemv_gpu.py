@@ -23,6 +23,15 @@ KERNELS = {8: engine_b200.CudaQ8_0Gemv, 12: engine_b200.CudaQ4KGemv, 13: engine_
 NAMES = {"q8_0": 8, "q4_k": 12, "q5_k": 13, "q6_k": 14}
 
 
+@pytest.fixture(params=[0, 1], ids=["auto", "f32-kernel"], autouse=True)
+def gemv_path(request, ctx):
+    """Every test runs twice: with the default kernel choice (integer-dot kernel for up to four
+    members per launch) and with the f32 CUDA-core kernel forced."""
+    ctx.set_option("gemv_path", request.param)
+    yield request.param
+    ctx.set_option("gemv_path", 0)
+
+
 def upload(ctx, vt, encoded, k, n, name="w"):
     store = engine_b200.CudaWeightStore(ctx)
     raw = np.ascontiguousarray(np.asarray(encoded).reshape(-1).view(np.uint8))
@@ -139,7 +148,9 @@ def test_q8_0_input_sizes_that_are_not_multiples_of_256(ctx, k, n):
         check(8, w, k, n, y, x_seen)
 
 
-def test_every_tuning_variant_agrees(ctx):
+def test_every_tuning_variant_agrees(ctx, gemv_path):
+    if gemv_path != 1:
+        pytest.skip("variants are tile geometries of the f32 kernel")
     k, n = 2048, 777
     try:
         for vt in (8, 12, 13, 14):
@@ -188,13 +199,18 @@ def test_host_buffers(ctx):
     weight = upload(ctx, 13, w, k, n)
     x = synth.random_activations(members, k, seed=3)
     y = np.full((members, n), np.nan, np.float32)
-    kernel = engine_b200.CudaQ5KGemv.from_context(ctx)
-    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
-        kernel.execute_host(weight, x, y, members)  # nothing reserved yet
-    assert e.value.kind == "InvalidArgument"
-    ctx.reserve_staging(1 << 20)
-    kernel.execute_host(weight, x, y, members)
-    check(13, w, k, n, y.astype(np.float64), x)
+    own = engine_b200.RibnContext(0)  # a context of its own: staging starts unreserved
+    try:
+        weight = upload(own, 13, w, k, n)
+        kernel = engine_b200.CudaQ5KGemv.from_context(own)
+        with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+            kernel.execute_host(weight, x, y, members)  # nothing reserved yet
+        assert e.value.kind == "InvalidArgument"
+        own.reserve_staging(1 << 20)
+        kernel.execute_host(weight, x, y, members)
+        check(13, w, k, n, y.astype(np.float64), x)
+    finally:
+        own.close()
 
 
 # ---- rejections happen before the launch and leave the output untouched (tests/q4_q8_1.rs:298-349)
@@ -248,3 +264,47 @@ def test_qwen_gemv_kernel_dispatches_on_value_type(ctx):
         check(vt, w, k, n, y.cpu().numpy()[None, :].astype(np.float64), x.cpu().numpy())
     with pytest.raises(engine_b200.CudaQuantizedKernelError):
         engine_b200.QwenGemvKernel.from_value_type(11, ctx)
+
+
+# ---- fused RMSNorm -> GEMV: same result contract as the two calls
+@pytest.mark.parametrize("vt", [8, 12, 13, 14])
+@pytest.mark.parametrize("members,x_dtype", [(1, torch.float32), (2, torch.bfloat16), (4, torch.float32), (7, torch.float32)])
+def test_fused_rms_norm_gemv(ctx, vt, members, x_dtype):
+    k, n = 4096, 513
+    w = synth.random_weight(vt, k, n, seed=vt + members)
+    weight = upload(ctx, vt, w, k, n)
+    rng = np.random.default_rng(members)
+    x = torch.from_numpy((rng.standard_normal((members, k)) * 2.5).astype(np.float32)).to(ctx.device).to(x_dtype)
+    gain_host = (1.0 + 0.02 * rng.standard_normal(k)).astype(np.float32)
+    gain = torch.from_numpy(gain_host).to(ctx.device)
+    y = torch.full((members, n), float("nan"), device=ctx.device)
+    KERNELS[vt].from_context(ctx).execute_rms_norm(weight, x, gain, 1e-6, y, members)
+    ctx.synchronize()
+    normed = oracle.rms_norm(x.float().cpu().numpy(), gain_host, 1e-6)
+    check(vt, w, k, n, y.cpu().numpy().astype(np.float64), normed)
+
+
+def test_fused_rejections(ctx):
+    k, n = 512, 4
+    w = synth.random_weight(12, k, n, seed=1)
+    weight = upload(ctx, 12, w, k, n)
+    x = torch.zeros(k, device=ctx.device)
+    y = torch.full((n,), 7.0, device=ctx.device)
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+        engine_b200.CudaQ4KGemv.from_context(ctx).execute_rms_norm(weight, x, torch.ones(k - 1, device=ctx.device), 1e-6, y, 1)
+    assert e.value.kind == "InputLength"
+    ctx.synchronize()
+    assert torch.all(y == 7.0)
+
+
+def test_non_finite_activations_reach_the_output(ctx):
+    k, n = 512, 8
+    w = synth.random_weight(12, k, n, seed=2)
+    weight = upload(ctx, 12, w, k, n)
+    x = synth.random_activations(1, k, seed=1)
+    x[0, 100] = np.inf
+    xd = torch.from_numpy(x).to(ctx.device)
+    yd = torch.zeros(n, device=ctx.device)
+    engine_b200.CudaQ4KGemv.from_context(ctx).execute_warp(weight, xd.reshape(-1), yd)
+    ctx.synchronize()
+    assert not torch.isfinite(yd).any()
