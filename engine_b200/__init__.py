@@ -17,6 +17,7 @@ from .quantized import (
     RibnContext,
     WeightTensorSpec,
     dequantize,
+    gemm,
     tensor_layout,
     validate_geometry_raw,
     validate_quantized_geometry,
@@ -25,6 +26,6 @@ from .quantized import (
 __all__ = [
     "CudaQ4KGemv", "CudaQ5KGemv", "CudaQ6KGemv", "CudaQ8_0Gemv", "CudaQuantizedKernelError",
     "CudaQuantizedWeight", "CudaQwen35Ops", "CudaWeightStore", "QwenGemvKernel", "RibnContext",
-    "WeightTensorSpec", "dequantize", "tensor_layout", "validate_geometry_raw",
+    "WeightTensorSpec", "dequantize", "gemm", "tensor_layout", "validate_geometry_raw",
     "validate_quantized_geometry",
 ]

@@ -27,8 +27,11 @@ struct ribn_ctx {
     uint64_t staging_bytes = 0;
     int variant = 0;                // GEMV tuning variant (ribn_set_option)
     int gemv_path = 0;              // 0 = choose per shape, 1 = f32 CUDA-core kernel only, 2 = integer-dot kernel only
-    void* workspace = nullptr;      // device scratch owned by the context (fused-op intermediates)
+    void* workspace = nullptr;      // device scratch owned by the context (packed activations, split-K partial tiles)
     uint64_t workspace_bytes = 0;
+    unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
+    int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
+    int tc_min_members = 5;         // batches of at least this many bf16 rows go to the tensor-core kernel
     std::string message;
     uint64_t expected = 0, actual = 0;
 };
@@ -36,6 +39,8 @@ struct ribn_ctx {
 namespace {
 
 using ribn::GemvArgs;
+
+constexpr int kTicketCount = 16384;
 
 struct Layout {
     uint64_t elements, bytes;
@@ -229,6 +234,31 @@ Failure validate_gemv(const ribn_qweight* w, uint32_t expected_type, int x_dtype
     return Failure{};
 }
 
+int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, void* y, int y_dtype,
+               uint64_t members) {
+    ribn::TcArgs t{};
+    t.weights = static_cast<const uint8_t*>(w->data);
+    t.weight_bytes = w->encoded_bytes;
+    t.value_type = w->value_type;
+    t.k = static_cast<int>(k);
+    t.n = static_cast<int>(n);
+    t.m = static_cast<int>(members);
+    t.x = x;
+    t.y = y;
+    t.y_bf16 = y_dtype == RIBN_BF16;
+    t.scratch = ctx->workspace;
+    t.scratch_bytes = ctx->workspace_bytes;
+    t.tickets = ctx->tickets;
+    t.ticket_count = kTicketCount;
+    t.force_ksplit = ctx->tc_ksplit;
+    t.device_status = ctx->device_status;
+    t.sm_count = ctx->sm_count;
+    t.stream = ctx->stream;
+    const cudaError_t e = ribn::launch_qgemm_tc(t);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "tensor-core GEMM launch");
+    return RIBN_OK;
+}
+
 int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y,
                  int y_dtype, uint32_t members, const float* norm_weight = nullptr, float eps = 0.0f) {
     GemvArgs a{};
@@ -243,6 +273,11 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.sm_count = ctx->sm_count;
     a.variant = ctx->variant;
     a.stream = ctx->stream;
+    // Path 0: tensor-core kernel for bf16 batches (no RMSNorm fused: normalised rows would have to be
+    // rounded to bf16 first, which the error bound of the path does not allow).
+    if (ctx->gemv_path == 0 && norm_weight == nullptr && a.x_bf16 && members >= static_cast<uint32_t>(ctx->tc_min_members) &&
+        ribn::qgemm_tc_supports(a.value_type, a.k))
+        return enqueue_tc(ctx, w, k, n, x, y, y_dtype, members);
     // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
     // packed once into the context workspace, then consumed four member rows per launch (the
     // weights stay in L2 between the launches of one call).
@@ -319,8 +354,12 @@ int ribn_create(int device, void* cuda_stream, ribn_ctx** out) {
     // Scratch for fused-op intermediates, allocated once here so that no later call allocates.
     ctx->workspace_bytes = 32ull << 20;
     if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->tickets, kTicketCount * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->tickets, 0, kTicketCount * sizeof(unsigned int));
     if (e != cudaSuccess) {
         if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
+        if (ctx->workspace != nullptr) cudaFree(ctx->workspace);
+        if (ctx->tickets != nullptr) cudaFree(ctx->tickets);
         delete ctx;
         return RIBN_E_DRIVER;
     }
@@ -333,6 +372,7 @@ void ribn_destroy(ribn_ctx* ctx) {
     DeviceGuard guard(ctx->device);
     if (ctx->staging != nullptr) cudaFree(ctx->staging);
     if (ctx->workspace != nullptr) cudaFree(ctx->workspace);
+    if (ctx->tickets != nullptr) cudaFree(ctx->tickets);
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
     delete ctx;
 }
@@ -379,6 +419,14 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     if (ctx == nullptr || name == nullptr) return RIBN_E_INVALID_ARGUMENT;
     if (std::strcmp(name, "gemv_variant") == 0) {
         ctx->variant = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tc_ksplit") == 0 && value >= 0 && value <= 64) {
+        ctx->tc_ksplit = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {
+        ctx->tc_min_members = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "gemv_path") == 0 && value >= 0 && value <= 2) {
@@ -454,6 +502,37 @@ int ribn_rms_norm_gemv(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
     return enqueue_gemv(ctx, weight, k, n, x_device, x_dtype, y_device, y_dtype, members, norm_weight_device, eps);
+}
+
+int ribn_gemm(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_device, uint64_t x_len,
+              void* y_device, int y_dtype, uint64_t y_len, uint64_t tokens) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (!valid_dtype(y_dtype)) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "unknown output dtype"));
+    if (tokens == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "quantized GEMM input has 0 values, expected 1", 1, 0));
+    uint64_t k = 0, n = 0;
+    Failure f = validate_geometry(weight, expected_type, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    uint64_t expected_in = 0, expected_out = 0;
+    if (tokens > static_cast<uint64_t>(std::numeric_limits<int32_t>::max()) || mul_overflows(k, tokens, &expected_in) ||
+        mul_overflows(n, tokens, &expected_out))
+        return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "quantized GEMM shape does not fit CUDA launch arguments"));
+    if (x_len != expected_in)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH,
+                                fmt("quantized GEMM input has %" PRIu64 " values, expected %" PRIu64, x_len, expected_in),
+                                expected_in, x_len));
+    if (y_len != expected_out)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH,
+                                fmt("quantized GEMM output has %" PRIu64 " values, expected %" PRIu64, y_len, expected_out),
+                                expected_out, y_len));
+    if (!ribn::qgemm_tc_supports(weight->value_type, static_cast<int>(k)))
+        return record(ctx, fail(RIBN_E_INVALID_WEIGHT,
+                                "invalid quantized weight: the tensor-core GEMM needs an input size that is a multiple of 256"));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    return enqueue_tc(ctx, weight, k, n, x_device, y_device, y_dtype, tokens);
 }
 
 int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {

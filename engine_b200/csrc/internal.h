@@ -49,6 +49,27 @@ cudaError_t launch_quantize_activations(const void* x, bool x_bf16, const float*
 cudaError_t launch_gemv_dp4a(const GemvArgs& args, bool* handled);
 bool gemv_dp4a_fits(uint32_t value_type, int k, int members);
 
+// Tensor-core GEMM (tcgen05): Y[m][n] = sum_k dequant(W[n][k]) * X[m][k], X bf16.
+struct TcArgs {
+    const uint8_t* weights;
+    uint64_t weight_bytes;
+    uint32_t value_type;
+    int k, n, m;
+    const void* x;            // bf16 [m][k], 16-byte aligned
+    void* y;                  // [m][n]
+    bool y_bf16;
+    void* scratch;            // split-K partial tiles
+    size_t scratch_bytes;
+    unsigned int* tickets;    // zero-initialised counters, one per output tile
+    int ticket_count;
+    int force_ksplit;         // 0 = choose
+    int* device_status;
+    int sm_count;
+    cudaStream_t stream;
+};
+bool qgemm_tc_supports(uint32_t value_type, int k);
+cudaError_t launch_qgemm_tc(const TcArgs& args);
+
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);
 

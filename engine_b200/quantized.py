@@ -320,6 +320,18 @@ class CudaQwen35Ops:
                                          output.numel(), members, length, ctypes.c_float(epsilon)))
 
 
+def gemm(context: RibnContext, weight: CudaQuantizedWeight, input: torch.Tensor, output: torch.Tensor,
+         expected_type: int = 0) -> None:
+    """Prefill GEMM on the tensor cores: input bf16 [tokens, K] -> output bf16/f32 [tokens, N] (ribn_gemm)."""
+    if input.dtype != torch.bfloat16:
+        raise TypeError("the tensor-core GEMM takes bfloat16 activations")
+    k = weight.spec().dimensions[0] if weight.spec().dimensions else 0
+    tokens = input.numel() // k if k else 0
+    descriptor = weight.descriptor()
+    context.check(context._lib.ribn_gemm(context.handle, expected_type, ctypes.byref(descriptor), input.data_ptr(),
+                                         input.numel(), output.data_ptr(), _dtype_code(output), output.numel(), tokens))
+
+
 def dequantize(context: RibnContext, weight: CudaQuantizedWeight, output: torch.Tensor) -> None:
     """Device twin of engine_gguf::dequantize_block over a whole tensor -> f32 [N, K]."""
     if output.dtype != torch.float32:

@@ -99,6 +99,8 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  * (GemvMode, decode.rs:298-307).
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
+ *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
+ *   "tc_ksplit":    split-K factor of the tensor-core kernel, 0 = choose per shape;
  *   "gemv_variant": tile geometry of the f32 kernel, 0 = default, 1..3 = alternatives
  *                   kept for measurement. */
 int ribn_set_option(ribn_ctx *ctx, const char *name, int64_t value);
@@ -139,6 +141,16 @@ int ribn_rms_norm_gemv(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight
                        const void *x_device, int x_dtype, uint64_t x_len,
                        const float *norm_weight_device, uint64_t norm_weight_len, float eps,
                        void *y_device, int y_dtype, uint64_t y_len, uint32_t members);
+
+/* Prefill: Y[t][n] = sum_k dequant(W[n][k]) * X[t][k] for any number of tokens,
+ * X bf16 [tokens][K], Y bf16 or f32 [tokens][N], on the tensor cores (tcgen05,
+ * dequantisation fused into the operand producer).  The reference has no GEMM:
+ * it serves prefill as chunks of eight tokens through execute_warp_batch
+ * (decode.rs:1953-1977, :2149-2267); this call replaces that loop.  K must be a
+ * multiple of 256.  ribn_gemv routes bf16 batches of five or more rows here. */
+int ribn_gemm(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
+              const void *x_device_bf16, uint64_t x_len,
+              void *y_device, int y_dtype, uint64_t y_len, uint64_t tokens);
 
 /* Same operation with HOST activations and outputs: copies x to a staging
  * buffer on the device, runs the GEMV, copies y back and waits.  The staging
