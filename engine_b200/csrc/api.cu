@@ -31,6 +31,7 @@ struct ribn_ctx {
     uint64_t workspace_bytes = 0;
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
+    int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int tc_min_members = 5;         // batches of at least this many bf16 rows go to the tensor-core kernel
     std::string message;
     uint64_t expected = 0, actual = 0;
@@ -251,6 +252,7 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.tickets = ctx->tickets;
     t.ticket_count = kTicketCount;
     t.force_ksplit = ctx->tc_ksplit;
+    t.force_row_copies = ctx->tc_row_copies;
     t.device_status = ctx->device_status;
     t.sm_count = ctx->sm_count;
     t.stream = ctx->stream;
@@ -423,6 +425,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_ksplit") == 0 && value >= 0 && value <= 64) {
         ctx->tc_ksplit = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {
+        ctx->tc_row_copies = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {

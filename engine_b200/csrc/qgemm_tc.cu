@@ -212,12 +212,20 @@ struct TcParams {
     int* status;
 };
 
-template <uint32_t FMT, int NT>
+// RAWTMA: the raw weight bytes of a stage (128 rows x one super-block) arrive as ONE tiled TMA box
+// instead of 128 bulk copies of 144..272 bytes (small bulk copies cost about as much per request
+// as large ones, and 128 of them per 18 KB starve the pipeline).  The box is 2-D over the tensor
+// viewed as [N rows][row_bytes] of 16-bit elements; it needs row_bytes to be a multiple of 16.
+// Q6_K super-blocks (210 bytes) start on 2-byte boundaries: the box starts at the 16-byte
+// boundary below and is 240 bytes wide, and the remainder is an offset in shared memory.
+template <uint32_t FMT, int NT, bool RAWTMA>
 struct TcGeometry {
     using F = Format<FMT>;
+    static constexpr int kBoxBytes = FMT == kQ6_K ? 240 : F::kBytes;
     static constexpr int kAbStages = NT >= 256 ? 2 : 3;
     static constexpr int kRawStages = 2;
-    static constexpr int kSlot = ((F::kBytes + 15) / 16) * 16 + 16;  // one row's super-block, copied from a 16-byte boundary
+    // bytes per row in a raw stage: the TMA box width, or a bulk copy from the 16-byte boundary below the block
+    static constexpr int kSlot = RAWTMA ? kBoxBytes : ((F::kBytes + 15) / 16) * 16 + 16;
     static constexpr int kRawStageBytes = kBM * kSlot;
     static constexpr int kAPartBytes = kBM * kBK * 2;        // one bf16 tile
     static constexpr int kATileBytes = 2 * kAPartBytes;      // high part, then low part
@@ -230,10 +238,10 @@ struct TcGeometry {
     static_assert(kSmemBytes <= 227 * 1024, "tile plan exceeds shared memory");
 };
 
-template <uint32_t FMT, int NT>
+template <uint32_t FMT, int NT, bool RAWTMA>
 __global__ void __launch_bounds__(kTcThreads, 1)
-qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
-    using G = TcGeometry<FMT, NT>;
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const TcParams p) {
+    using G = TcGeometry<FMT, NT, RAWTMA>;
     using F = Format<FMT>;
     using R = RowDequant<FMT>;
     extern __shared__ uint8_t smem_raw[];
@@ -262,7 +270,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < G::kRawStages; ++s) {
-            mbar_init(&raw_full[s], 32);
+            mbar_init(&raw_full[s], RAWTMA ? 1 : 32);
             mbar_init(&raw_empty[s], kDequantWarps);
         }
         for (int s = 0; s < G::kAbStages; ++s) {
@@ -272,6 +280,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
         mbar_init(acc_full, 1);
         mbar_fence_init();
         tma_prefetch_descriptor(&xmap);
+        if (RAWTMA) tma_prefetch_descriptor(&wmap);
     }
     if (warp == 1) tmem_alloc(tmem_holder, G::kTmemColumns);
     tcgen05_fence_before_sync();
@@ -290,6 +299,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
                 ok = false;
                 break;
             }
+            if (RAWTMA) {
+                if (lane == 0) {
+                    const unsigned long long byte_x = (static_cast<unsigned long long>(sb_begin + i) * F::kBytes) & ~15ull;
+                    mbar_arrive_expect_tx(&raw_full[rs], kBM * G::kBoxBytes);
+                    tma_load_2d(raw + rs * G::kRawStageBytes, &wmap, static_cast<int>(byte_x >> 1), n0, &raw_full[rs]);
+                }
+            } else {
             // Each lane brings four rows of the stage: one arrive with the byte total, then the copies.
             unsigned long long a0[4];
             uint32_t bytes[4];
@@ -326,6 +342,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
             for (int q = 0; q < 4; ++q) {
                 if (bytes[q] > 0)
                     bulk_copy_g2s(raw + rs * G::kRawStageBytes + (lane + 32 * q) * G::kSlot, p.w + a0[q], bytes[q], &raw_full[rs]);
+            }
             }
             // Activation tiles of the four K steps of this super-block.
             if (lane == 0) {
@@ -386,7 +403,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
                 ok = false;
                 break;
             }
-            const unsigned long long g0 = static_cast<unsigned long long>(row) * p.row_bytes +
+            // With the TMA box rows are 16-byte aligned, so only the block's offset inside its row counts.
+            const unsigned long long g0 = (RAWTMA ? 0ull : static_cast<unsigned long long>(row) * p.row_bytes) +
                                           static_cast<unsigned long long>(sb_begin + i) * F::kBytes;
             const uint8_t* blk = raw + rs * G::kRawStageBytes + r * G::kSlot + static_cast<uint32_t>(g0 & 15ull);
             typename R::Scales scales;
@@ -459,30 +477,47 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams p) {
                 }
             }
         }
-        if (split) {
-            // The CTA that draws the last ticket of its tile adds the partial tiles in K order.
+    }
+
+    // ---------------- split-K: the CTA that draws the last ticket of its tile adds the partial tiles ----------------
+    if (p.ksplit > 1 && warp >= 2) {
+        // All eight dequant warps take part (they are idle by now): 256 threads, two per weight row.
+        __threadfence();
+        named_barrier_sync(2, kDequantWarps * 32);
+        if (threadIdx.x == 64) {
+            unsigned int* ticket = p.tickets + blockIdx.y * gridDim.x + blockIdx.x;
+            const unsigned int drawn = atomicAdd(ticket, 1u);
+            const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
+            if (last) *ticket = 0;  // ready for the next launch
+            *last_flag = last ? 1u : 0u;
+        }
+        named_barrier_sync(2, kDequantWarps * 32);
+        const int t256 = threadIdx.x - 64;
+        const long long row = static_cast<long long>(n0) + (t256 & (kBM - 1));
+        if (*last_flag != 0 && row < p.n) {
             __threadfence();
-            named_barrier_sync(2, 128);
-            if (threadIdx.x == 64) {
-                unsigned int* ticket = p.tickets + blockIdx.y * gridDim.x + blockIdx.x;
-                const unsigned int drawn = atomicAdd(ticket, 1u);
-                const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
-                if (last) *ticket = 0;  // ready for the next launch
-                *last_flag = last ? 1u : 0u;
-            }
-            named_barrier_sync(2, 128);
-            if (*last_flag != 0 && row < p.n) {
-                __threadfence();
-                const size_t plane = static_cast<size_t>(p.m) * p.n;
-                const int m_end = min(m0 + NT, p.m);
-                for (int m = m0; m < m_end; ++m) {
-                    const size_t o = static_cast<size_t>(m) * p.n + row;
-                    float sum = __ldcg(p.partial + o);
-                    for (int z = 1; z < p.ksplit; ++z) sum += __ldcg(p.partial + z * plane + o);
-                    if (p.y_bf16) {
-                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(sum);
-                    } else {
-                        static_cast<float*>(p.y)[o] = sum;
+            const size_t plane = static_cast<size_t>(p.m) * p.n;
+            const int m_end = min(m0 + NT, p.m);
+            // Four tokens at a time, so that four independent loads per K slice are in flight;
+            // the slices are added in index order whatever the arrival order was.
+            for (int m = m0 + 4 * (t256 >> 7); m < m_end; m += 8) {
+                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                size_t o[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) o[u] = static_cast<size_t>(min(m + u, m_end - 1)) * p.n + row;
+#pragma unroll 4
+                for (int z = 0; z < p.ksplit; ++z) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) sum[u] += __ldcg(p.partial + z * plane + o[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (m + u < m_end) {
+                        if (p.y_bf16) {
+                            static_cast<__nv_bfloat16*>(p.y)[o[u]] = __float2bfloat16_rn(sum[u]);
+                        } else {
+                            static_cast<float*>(p.y)[o[u]] = sum[u];
+                        }
                     }
                 }
             }
@@ -532,10 +567,10 @@ int choose_ksplit(int tiles, int nsb, int sm_count, size_t plane_bytes, size_t s
     return best;
 }
 
-template <uint32_t FMT, int NT>
+template <uint32_t FMT, int NT, bool RAWTMA>
 cudaError_t launch_tile(const TcArgs& a) {
-    using G = TcGeometry<FMT, NT>;
-    auto kernel = qgemm_tc_kernel<FMT, NT>;
+    using G = TcGeometry<FMT, NT, RAWTMA>;
+    auto kernel = qgemm_tc_kernel<FMT, NT, RAWTMA>;
     static int configured_device = -1;
     int device = 0;
     cudaGetDevice(&device);
@@ -560,6 +595,16 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.w_bytes = a.weight_bytes;
     p.row_bytes = a.value_type == kQ8_0 ? static_cast<unsigned long long>(a.k / 32) * 34
                                         : static_cast<unsigned long long>(a.k / kSuperBlock) * Format<FMT>::kBytes;
+    CUtensorMap wmap = map;  // unused unless RAWTMA
+    if (RAWTMA) {
+        const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(p.row_bytes / 2), static_cast<cuuint64_t>(a.n)};
+        const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(p.row_bytes)};
+        const cuuint32_t wbox[2] = {G::kBoxBytes / 2, kBM};
+        if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t*>(a.weights), wdims, wstrides, wbox, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     p.y = a.y;
     p.partial = static_cast<float*>(a.scratch);
     p.tickets = a.tickets;
@@ -577,17 +622,26 @@ cudaError_t launch_tile(const TcArgs& a) {
         static_cast<size_t>(a.m) * a.n * sizeof(float) * a.force_ksplit <= a.scratch_bytes && n_tiles * m_tiles <= a.ticket_count)
         p.ksplit = a.force_ksplit;
     const dim3 grid(n_tiles, m_tiles, p.ksplit);
-    kernel<<<grid, kTcThreads, G::kSmemBytes, a.stream>>>(map, p);
+    kernel<<<grid, kTcThreads, G::kSmemBytes, a.stream>>>(map, wmap, p);
     return cudaGetLastError();
+}
+
+template <uint32_t FMT, bool RAWTMA>
+cudaError_t launch_tokens(const TcArgs& a) {
+    if (a.m <= 16) return launch_tile<FMT, 16, RAWTMA>(a);
+    if (a.m <= 32) return launch_tile<FMT, 32, RAWTMA>(a);
+    if (a.m <= 64) return launch_tile<FMT, 64, RAWTMA>(a);
+    if (a.m <= 128) return launch_tile<FMT, 128, RAWTMA>(a);
+    return launch_tile<FMT, 256, RAWTMA>(a);
 }
 
 template <uint32_t FMT>
 cudaError_t launch_format(const TcArgs& a) {
-    if (a.m <= 16) return launch_tile<FMT, 16>(a);
-    if (a.m <= 32) return launch_tile<FMT, 32>(a);
-    if (a.m <= 64) return launch_tile<FMT, 64>(a);
-    if (a.m <= 128) return launch_tile<FMT, 128>(a);
-    return launch_tile<FMT, 256>(a);
+    // The tiled box needs 16-byte aligned rows; only Q6_K rows can fail that (210-byte blocks).
+    const unsigned long long row_bytes = a.value_type == kQ8_0 ? static_cast<unsigned long long>(a.k / 32) * 34
+                                                               : static_cast<unsigned long long>(a.k / kSuperBlock) * Format<FMT>::kBytes;
+    if (row_bytes % 16 == 0 && a.force_row_copies == 0) return launch_tokens<FMT, true>(a);
+    return launch_tokens<FMT, false>(a);
 }
 
 }  // namespace

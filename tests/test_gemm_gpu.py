@@ -54,6 +54,33 @@ def test_small_shapes(ctx, vt, n, k, m):
     check(vt, w, k, n, y, x_seen)
 
 
+@pytest.mark.parametrize("vt", [12, 13, 14, 8])
+def test_per_row_copy_variant(ctx, vt):
+    """The kernel variant that fetches raw rows with bulk copies (used when rows are not 16-byte aligned)."""
+    k, n, m = 1024, 200, 24
+    w = synth.random_weight(vt, k, n, seed=vt)
+    weight = upload(ctx, vt, w, k, n)
+    x = synth.random_activations(m, k, seed=3)
+    try:
+        ctx.set_option("tc_row_copies", 1)
+        y, x_seen = run(ctx, weight, x, n)
+    finally:
+        ctx.set_option("tc_row_copies", 0)
+    check(vt, w, k, n, y, x_seen)
+
+
+@pytest.mark.parametrize("k", [256, 1280, 5120])
+def test_q6_k_rows_that_are_not_16_byte_aligned(ctx, k):
+    """210-byte blocks: K/256 not a multiple of 8 gives rows that start on 2-, 4- or 8-byte boundaries,
+    and a tensor whose byte length is not a multiple of 16."""
+    n, m = 131, 20
+    w = synth.random_weight(14, k, n, seed=k)
+    weight = upload(ctx, 14, w, k, n)
+    x = synth.random_activations(m, k, seed=5)
+    y, x_seen = run(ctx, weight, x, n)
+    check(14, w, k, n, y, x_seen)
+
+
 @pytest.mark.parametrize("ksplit", [1, 2, 3, 8])
 def test_split_k_factors_agree(ctx, ksplit):
     k, n, m = 4096, 640, 48
