@@ -172,6 +172,36 @@ int ribn_rms_norm(ribn_ctx *ctx, const void *x_device, int x_dtype, uint64_t x_l
                   void *y_device, int y_dtype, uint64_t y_len,
                   uint32_t members, uint32_t length, float eps);
 
+/* No counterpart in the reference (its wrappers allocate freely through their
+ * driver binding).  The one entry point that allocates nothing, for callers that
+ * must not: a serving loop that has given all device memory to its own pools and
+ * forbids cudaMalloc after start-up, a latency-critical section that cannot take
+ * the implicit synchronisation of an allocation, or a plug-in that may not touch
+ * its host's allocator.  It needs no ribn_ctx (ribn_create allocates).
+ *
+ * Same operation and result as ribn_gemv for members <= 4.  The scratch for the
+ * packed activations is a fixed device array inside the library image (about
+ * 144 KiB, held by every GPU that loads the library until the process exits),
+ * hence the limit: members * K (K rounded up to a multiple of 256) must not
+ * exceed RIBN_NOALLOC_MAX_ACTIVATIONS, and the activations must fit the kernel's
+ * shared memory; larger calls are refused with RIBN_E_SHAPE_OVERFLOW.
+ *
+ * The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress) and should therefore be made before any stream
+ * capture begins.  All calls share the array and it keeps the previous call's
+ * contents; the call clears the one word that must start at zero and rewrites
+ * the rest.  Calls whose kernels can overlap on the GPU (other streams, other
+ * host threads) race on the array: the caller serialises them.
+ *
+ * wait != 0: synchronise the stream before returning and report a bounded
+ * device wait that ran out as RIBN_E_TIMEOUT.  error_message (may be NULL)
+ * receives the text of a failure. */
+#define RIBN_NOALLOC_MAX_ACTIVATIONS 65536ull
+int ribn_gemv_noalloc(int device, void *cuda_stream, const ribn_qweight *weight,
+                      const void *x_device, int x_dtype, uint64_t x_len,
+                      void *y_device, int y_dtype, uint64_t y_len, uint32_t members, int wait,
+                      char *error_message, uint64_t error_capacity);
+
 #ifdef __cplusplus
 }
 #endif
