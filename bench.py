@@ -175,6 +175,8 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--variant", type=int, default=0, help="GEMV tuning variant")
+    parser.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                        help="library tuning option passed to ribn_set_option (measurement runs only)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
     parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
@@ -215,6 +217,9 @@ def main() -> None:
     stream = torch.cuda.Stream(device=device)
     ctx = engine_b200.RibnContext(local_rank, stream=stream)
     ctx.set_option("gemv_variant", args.variant)
+    for item in args.option:
+        name, value = item.split("=")
+        ctx.set_option(name, int(value))
     kernels = {vt: engine_b200.QwenGemvKernel.from_value_type(vt, ctx) for vt in FORMATS}
     store = engine_b200.CudaWeightStore(ctx)
 
@@ -363,7 +368,7 @@ def main() -> None:
                        "formats": [synth.TYPE_NAMES[v] for v in FORMATS], "shapes_NxK": SHAPES,
                        "members": MEMBERS, "activations": "bf16", "outputs": "f32",
                        "l2": "ring of distinct weight copies > 2x L2 per (format, shape); inputs larger than L2",
-                       "parallelism": "replicas" if world > 1 else "single", "gemv_variant": args.variant,
+                       "parallelism": "replicas" if world > 1 else "single", "gemv_variant": args.variant, "options": args.option,
                        "cuda_graph": step_graph is not None},
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                          "traffic": None, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s",

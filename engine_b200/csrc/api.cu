@@ -31,6 +31,7 @@ struct ribn_ctx {
     uint64_t workspace_bytes = 0;
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
+    int tc_split_operands = 0;      // 1 = batches <= 64 also use the split-operand GEMM instead of the group-scaled kernel
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int tc_min_members = 5;         // batches of at least this many bf16 rows go to the tensor-core kernel
     std::string message;
@@ -256,7 +257,9 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.device_status = ctx->device_status;
     t.sm_count = ctx->sm_count;
     t.stream = ctx->stream;
-    const cudaError_t e = ribn::launch_qgemm_tc(t);
+    // Decode batches: raw quants on the tensor core, scales applied per group.  Prefill: dequantised
+    // operands (the per-group epilogue would cost more than it saves once hundreds of tokens share a tile).
+    const cudaError_t e = (members <= 64 && ctx->tc_split_operands == 0) ? ribn::launch_qgemv_tc(t) : ribn::launch_qgemm_tc(t);
     if (e != cudaSuccess) return record_cuda(ctx, e, "tensor-core GEMM launch");
     return RIBN_OK;
 }
@@ -425,6 +428,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_ksplit") == 0 && value >= 0 && value <= 64) {
         ctx->tc_ksplit = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tc_split_operands") == 0 && (value == 0 || value == 1)) {
+        ctx->tc_split_operands = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {

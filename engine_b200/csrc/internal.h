@@ -70,6 +70,8 @@ struct TcArgs {
 };
 bool qgemm_tc_supports(uint32_t value_type, int k);
 cudaError_t launch_qgemm_tc(const TcArgs& args);
+// Group-scaled variant for decode batches (raw quants on the tensor core, scales applied per group).
+cudaError_t launch_qgemv_tc(const TcArgs& args);
 
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);

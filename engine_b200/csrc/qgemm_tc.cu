@@ -40,6 +40,7 @@
 
 #include "formats.cuh"
 #include "internal.h"
+#include "tc_host.h"
 #include "tcgen05.cuh"
 
 namespace ribn {
@@ -197,20 +198,6 @@ struct RowDequant<kQ8_0> {
     }
 };
 
-
-struct TcParams {
-    const uint8_t* w;
-    unsigned long long w_bytes;
-    unsigned long long row_bytes;
-    void* y;                 // [m][n] f32 or bf16
-    float* partial;          // split-K scratch: [ksplit][m][n] f32
-    unsigned int* tickets;   // one counter per (n tile, m tile), zero between launches
-    int k, n, m;
-    int nsb;                 // super-blocks per row
-    int ksplit;
-    int y_bf16;
-    int* status;
-};
 
 // RAWTMA: the raw weight bytes of a stage (128 rows x one super-block) arrive as ONE tiled TMA box
 // instead of 128 bulk copies of 144..272 bytes (small bulk copies cost about as much per request
@@ -528,43 +515,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, G::kTmemColumns);
-}
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-// Waves x (K work per CTA + a fixed cost of about one and a half super-blocks for pipeline fill,
-// TMEM allocation and the epilogue), minimised over the split factor.
-int choose_ksplit(int tiles, int nsb, int sm_count, size_t plane_bytes, size_t scratch_bytes, int max_tickets) {
-    if (tiles > max_tickets) return 1;
-    int best = 1;
-    double best_cost = 1e30;
-    const int limit = nsb < 16 ? nsb : 16;
-    for (int ks = 1; ks <= limit; ++ks) {
-        if (ks > 1 && plane_bytes * ks > scratch_bytes) break;
-        const int waves = (tiles * ks + sm_count - 1) / sm_count;
-        const double per_cta = static_cast<double>((nsb + ks - 1) / ks) + 1.5 + (ks > 1 ? 0.5 : 0.0);
-        const double cost = waves * per_cta;
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best = ks;
-        }
-    }
-    return best;
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>

@@ -1,0 +1,62 @@
+// Host-side helpers shared by the tensor-core kernels: kernel parameter block, tensor-map encoding
+// through the runtime's driver entry point, split-K choice.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ribn {
+
+struct TcParams {
+    const uint8_t* w;
+    unsigned long long w_bytes;
+    unsigned long long row_bytes;
+    void* y;                 // [m][n] f32 or bf16
+    float* partial;          // split-K scratch: [ksplit][m][n] f32
+    unsigned int* tickets;   // one counter per (n tile, m tile), zero between launches
+    int k, n, m;
+    int nsb;                 // super-blocks per row
+    int ksplit;
+    int y_bf16;
+    int* status;
+};
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// Waves x (K work per CTA + a fixed cost of about one and a half super-blocks for pipeline fill,
+// TMEM allocation and the epilogue), minimised over the split factor.
+inline int choose_ksplit(int tiles, int nsb, int sm_count, size_t plane_bytes, size_t scratch_bytes, int max_tickets) {
+    if (tiles > max_tickets) return 1;
+    int best = 1;
+    double best_cost = 1e30;
+    const int limit = nsb < 16 ? nsb : 16;
+    for (int ks = 1; ks <= limit; ++ks) {
+        if (ks > 1 && plane_bytes * ks > scratch_bytes) break;
+        const int waves = (tiles * ks + sm_count - 1) / sm_count;
+        const double per_cta = static_cast<double>((nsb + ks - 1) / ks) + 1.5 + (ks > 1 ? 0.5 : 0.0);
+        const double cost = waves * per_cta;
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = ks;
+        }
+    }
+    return best;
+}
+
+}  // namespace ribn

@@ -100,6 +100,8 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
  *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
+ *   "tc_split_operands": 1 = batches of up to 64 rows use the dequantised-operand GEMM (the prefill
+ *                   kernel) instead of the group-scaled decode kernel;
  *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
  *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not
  *                   16-byte aligned, and for tests);
