@@ -31,7 +31,8 @@ struct ribn_ctx {
     uint64_t workspace_bytes = 0;
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
-    int tc_split_operands = 0;      // 1 = batches <= 64 also use the split-operand GEMM instead of the group-scaled kernel
+    int tc_split_operands = 1;      // 1 = batches <= 64 use the split-operand GEMM (default, faster as measured); 0 = group-scaled kernel
+    int tc_trace = 0;               // 1 = the decode tensor-core kernel records pipeline clock stamps in the workspace tail
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int tc_min_members = 5;         // batches of at least this many bf16 rows go to the tensor-core kernel
     std::string message;
@@ -43,6 +44,7 @@ namespace {
 using ribn::GemvArgs;
 
 constexpr int kTicketCount = 16384;
+constexpr uint64_t kTraceBytes = 64 << 10;
 
 struct Layout {
     uint64_t elements, bytes;
@@ -254,6 +256,12 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.ticket_count = kTicketCount;
     t.force_ksplit = ctx->tc_ksplit;
     t.force_row_copies = ctx->tc_row_copies;
+    t.trace = nullptr;
+    if (ctx->tc_trace != 0) {
+        // the last 64 KiB of the workspace; split-K partial tiles use the front
+        t.trace = reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes);
+        t.scratch_bytes -= kTraceBytes;
+    }
     t.device_status = ctx->device_status;
     t.sm_count = ctx->sm_count;
     t.stream = ctx->stream;
@@ -434,6 +442,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
         ctx->tc_split_operands = static_cast<int>(value);
         return RIBN_OK;
     }
+    if (std::strcmp(name, "tc_trace") == 0 && (value == 0 || value == 1)) {
+        ctx->tc_trace = static_cast<int>(value);
+        return RIBN_OK;
+    }
     if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {
         ctx->tc_row_copies = static_cast<int>(value);
         return RIBN_OK;
@@ -546,6 +558,16 @@ int ribn_gemm(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight,
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
     return enqueue_tc(ctx, weight, k, n, x_device, y_device, y_dtype, tokens);
+}
+
+int ribn_debug_read_trace(ribn_ctx* ctx, void* host_dst, uint64_t bytes) {
+    if (ctx == nullptr || host_dst == nullptr || bytes > kTraceBytes) return RIBN_E_INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy(host_dst, static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "trace readback");
+    return RIBN_OK;
 }
 
 int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {

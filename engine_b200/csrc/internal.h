@@ -63,6 +63,7 @@ struct TcArgs {
     unsigned int* tickets;    // zero-initialised counters, one per output tile
     int ticket_count;
     int force_ksplit;         // 0 = choose
+    long long* trace;         // diagnostics buffer of the decode kernel (see TcParams), or null
     int force_row_copies;     // 1 = per-row bulk copies even where one tiled TMA box per stage would do
     int* device_status;
     int sm_count;

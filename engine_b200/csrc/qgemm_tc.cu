@@ -564,6 +564,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.nsb = a.k / kSuperBlock;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
     p.status = a.device_status;
+    p.trace = nullptr;
     const int n_tiles = (a.n + kBM - 1) / kBM;
     const int m_tiles = (a.m + NT - 1) / NT;
     p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, static_cast<size_t>(a.m) * a.n * sizeof(float),

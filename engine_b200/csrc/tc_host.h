@@ -20,6 +20,9 @@ struct TcParams {
     int ksplit;
     int y_bf16;
     int* status;
+    // Diagnostics: when non-null, CTA (0,0,0) of the decode kernel records SM clock stamps of its
+    // pipeline events here: trace[(role * 64 + step) * 8 + event], 4 roles x 64 steps x 8 events.
+    long long* trace;
 };
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).

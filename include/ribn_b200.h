@@ -100,8 +100,10 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
  *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
- *   "tc_split_operands": 1 = batches of up to 64 rows use the dequantised-operand GEMM (the prefill
- *                   kernel) instead of the group-scaled decode kernel;
+ *   "tc_split_operands": 1 (default) = batches of up to 64 rows use the dequantised-operand GEMM (the
+ *                   prefill kernel); 0 = the group-scaled decode kernel (raw quants on the tensor
+ *                   cores, block scales applied from TMEM; same results within the parity bound);
+ *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);
  *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
  *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not
  *                   16-byte aligned, and for tests);
@@ -109,6 +111,13 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "gemv_variant": tile geometry of the f32 kernel, 0 = default, 1..3 = alternatives
  *                   kept for measurement. */
 int ribn_set_option(ribn_ctx *ctx, const char *name, int64_t value);
+
+/* Diagnostics, no counterpart in the reference: with option "tc_trace" = 1 the decode tensor-core
+ * kernel records SM clock stamps of its pipeline events (first CTA, first 64 K steps) in the last
+ * 64 KiB of the context workspace; this call waits for the stream and copies them out
+ * (int64 trace[(role*64 + step)*8 + event]; roles: 0 MMA issuer, 1 unpack warp, 2 accumulate warp,
+ * 3 weight producer). */
+int ribn_debug_read_trace(ribn_ctx *ctx, void *host_dst, uint64_t bytes);
 
 /* tensor_layout (crates/gguf/src/lib.rs:1051-1083): GGML type -> (elements per
  * block, bytes per block).  RIBN_E_UNSUPPORTED_TYPE for unknown ids. */

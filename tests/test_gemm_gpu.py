@@ -24,7 +24,7 @@ def tc_kernel(request, ctx):
     dequantised split operands); every test runs with each.  Larger batches always use the second."""
     ctx.set_option("tc_split_operands", request.param)
     yield request.param
-    ctx.set_option("tc_split_operands", 0)
+    ctx.set_option("tc_split_operands", 1)
 
 
 def upload(ctx, vt, encoded, k, n):
