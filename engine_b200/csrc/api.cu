@@ -31,10 +31,11 @@ struct ribn_ctx {
     uint64_t workspace_bytes = 0;
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
-    int tc_split_operands = 1;      // 1 = batches <= 64 use the split-operand GEMM (default, faster as measured); 0 = group-scaled kernel
+    int tc_split_operands = 0;      // 1 = bf16 batches <= 64 use the split-operand GEMM (the prefill kernel) instead of the f16 decode kernel
     int tc_trace = 0;               // 1 = the decode tensor-core kernel records pipeline clock stamps in the workspace tail
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
-    int tc_min_members = 5;         // batches of at least this many bf16 rows go to the tensor-core kernel
+    int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
+    int tc_min_members = 5;         // batches of at least this many rows go to the tensor-core kernel
     std::string message;
     uint64_t expected = 0, actual = 0;
 };
@@ -238,8 +239,8 @@ Failure validate_gemv(const ribn_qweight* w, uint32_t expected_type, int x_dtype
     return Failure{};
 }
 
-int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, void* y, int y_dtype,
-               uint64_t members) {
+int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y, int y_dtype,
+               uint64_t members, const float* norm_weight = nullptr, float eps = 0.0f) {
     ribn::TcArgs t{};
     t.weights = static_cast<const uint8_t*>(w->data);
     t.weight_bytes = w->encoded_bytes;
@@ -248,6 +249,9 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.n = static_cast<int>(n);
     t.m = static_cast<int>(members);
     t.x = x;
+    t.x_bf16 = x_dtype == RIBN_BF16;
+    t.norm_weight = norm_weight;
+    t.eps = eps;
     t.y = y;
     t.y_bf16 = y_dtype == RIBN_BF16;
     t.scratch = ctx->workspace;
@@ -265,9 +269,11 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.device_status = ctx->device_status;
     t.sm_count = ctx->sm_count;
     t.stream = ctx->stream;
-    // Decode batches: raw quants on the tensor core, scales applied per group.  Prefill: dequantised
-    // operands (the per-group epilogue would cost more than it saves once hundreds of tokens share a tile).
-    const cudaError_t e = (members <= 64 && ctx->tc_split_operands == 0) ? ribn::launch_qgemv_tc(t) : ribn::launch_qgemm_tc(t);
+    // Decode batches: one f16 tile per step, normalised per super-block, accumulated in registers.  Prefill:
+    // split bf16 operands accumulated in TMEM over the whole K range (hundreds of tokens per tile do not
+    // fit the registers of the accumulate warps).
+    const bool decode = members <= 64 && (ctx->tc_split_operands == 0 || !t.x_bf16 || norm_weight != nullptr);
+    const cudaError_t e = decode ? ribn::launch_qgemv_tc(t) : ribn::launch_qgemm_tc(t);
     if (e != cudaSuccess) return record_cuda(ctx, e, "tensor-core GEMM launch");
     return RIBN_OK;
 }
@@ -286,11 +292,13 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.sm_count = ctx->sm_count;
     a.variant = ctx->variant;
     a.stream = ctx->stream;
-    // Path 0: tensor-core kernel for bf16 batches (no RMSNorm fused: normalised rows would have to be
-    // rounded to bf16 first, which the error bound of the path does not allow).
-    if (ctx->gemv_path == 0 && norm_weight == nullptr && a.x_bf16 && members >= static_cast<uint32_t>(ctx->tc_min_members) &&
-        ribn::qgemm_tc_supports(a.value_type, a.k))
-        return enqueue_tc(ctx, w, k, n, x, y, y_dtype, members);
+    // Path 0: tensor-core decode kernel for batches (RMSNorm, when asked for, is applied in f32 by its
+    // activation pre-pass).  Its operands are f16: bf16 activations convert exactly and the weights'
+    // rounding (2^-12) is below the one the caller applied to the activations (2^-9); f32 activations
+    // would lose 13 bits, so they take it only on request.  Its scratch is the f16 copy of the activations.
+    if (ctx->gemv_path == 0 && (a.x_bf16 || ctx->tc_f32_activations != 0) && members >= static_cast<uint32_t>(ctx->tc_min_members) && ribn::qgemm_tc_supports(a.value_type, a.k) &&
+        members * k * 2 + (1u << 20) <= ctx->workspace_bytes)
+        return enqueue_tc(ctx, w, k, n, x, x_dtype, y, y_dtype, members, norm_weight, eps);
     // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
     // packed once into the context workspace, then consumed four member rows per launch (the
     // weights stay in L2 between the launches of one call).
@@ -450,6 +458,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
         ctx->tc_row_copies = static_cast<int>(value);
         return RIBN_OK;
     }
+    if (std::strcmp(name, "tc_f32_activations") == 0 && (value == 0 || value == 1)) {
+        ctx->tc_f32_activations = static_cast<int>(value);
+        return RIBN_OK;
+    }
     if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {
         ctx->tc_min_members = static_cast<int>(value);
         return RIBN_OK;
@@ -557,7 +569,7 @@ int ribn_gemm(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight,
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "input");
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
-    return enqueue_tc(ctx, weight, k, n, x_device, y_device, y_dtype, tokens);
+    return enqueue_tc(ctx, weight, k, n, x_device, RIBN_BF16, y_device, y_dtype, tokens);
 }
 
 int ribn_debug_read_trace(ribn_ctx* ctx, void* host_dst, uint64_t bytes) {

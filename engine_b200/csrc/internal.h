@@ -55,7 +55,10 @@ struct TcArgs {
     uint64_t weight_bytes;
     uint32_t value_type;
     int k, n, m;
-    const void* x;            // bf16 [m][k], 16-byte aligned
+    const void* x;            // [m][k], 16-byte aligned; bf16 for launch_qgemm_tc, bf16 or f32 (x_bf16) for launch_qgemv_tc
+    bool x_bf16;
+    const float* norm_weight; // launch_qgemv_tc only: RMSNorm weight applied to x first, or null
+    float eps;
     void* y;                  // [m][n]
     bool y_bf16;
     void* scratch;            // split-K partial tiles
@@ -71,7 +74,8 @@ struct TcArgs {
 };
 bool qgemm_tc_supports(uint32_t value_type, int k);
 cudaError_t launch_qgemm_tc(const TcArgs& args);
-// Group-scaled variant for decode batches (raw quants on the tensor core, scales applied per group).
+// Decode batches (1..64 members): one f16 operand tile per step, normalised per super-block; takes
+// f32 or bf16 activations and can apply RMSNorm to them in its conversion pre-pass.
 cudaError_t launch_qgemv_tc(const TcArgs& args);
 
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,

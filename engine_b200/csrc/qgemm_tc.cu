@@ -40,6 +40,7 @@
 
 #include "formats.cuh"
 #include "internal.h"
+#include "row_dequant.cuh"
 #include "tc_host.h"
 #include "tcgen05.cuh"
 
@@ -49,154 +50,11 @@ namespace {
 constexpr int kBM = 128;            // weight rows per CTA
 constexpr int kBK = 64;             // K elements per UMMA stage (one 128-byte swizzled row)
 constexpr int kSub = kSuperBlock / kBK;  // stages per super-block
-constexpr float kPreScale = 1.0f;   // weights are not pre-scaled: bf16 has the f32 exponent range
-constexpr int kDequantWarps = 8;
-constexpr int kTcThreads = (2 + kDequantWarps) * 32;
-
-__device__ __forceinline__ uint4 raw16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ uint4 raw16_a2(const uint8_t* p) {
-    uint4 v;
-    v.x = ld_u32_a2(p);
-    v.y = ld_u32_a2(p + 4);
-    v.z = ld_u32_a2(p + 8);
-    v.w = ld_u32_a2(p + 12);
-    return v;
-}
-
-// Two f32 weights -> a word of their bf16 high parts and a word of the bf16 remainders.
-__device__ __forceinline__ void split_pair(float w0, float w1, uint32_t& high, uint32_t& low) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(w0, w1);
-    high = *reinterpret_cast<const uint32_t*>(&h);
-    const float h0 = __uint_as_float(high << 16);
-    const float h1 = __uint_as_float(high & 0xffff0000u);
-    const __nv_bfloat162 l = __floats2bfloat162_rn(w0 - h0, w1 - h1);
-    low = *reinterpret_cast<const uint32_t*>(&l);
-}
-
-// A 16-byte chunk (eight weights) of the high tile and the matching chunk of the low tile.
-struct ChunkPair {
-    uint4 high, low;
-};
-
-// Eight weights (two packed words of four byte-sized quants) -> one chunk pair.
-__device__ __forceinline__ ChunkPair chunk_from_bytes(uint32_t q0, uint32_t q1, float bias, float scale, float minimum) {
-    float a[4], b[4];
-    bytes_to_float4(q0, bias, a);
-    bytes_to_float4(q1, bias, b);
-    ChunkPair out;
-    split_pair(dequant_value(scale, a[0], minimum), dequant_value(scale, a[1], minimum), out.high.x, out.low.x);
-    split_pair(dequant_value(scale, a[2], minimum), dequant_value(scale, a[3], minimum), out.high.y, out.low.y);
-    split_pair(dequant_value(scale, b[0], minimum), dequant_value(scale, b[1], minimum), out.high.z, out.low.z);
-    split_pair(dequant_value(scale, b[2], minimum), dequant_value(scale, b[3], minimum), out.high.w, out.low.w);
-    return out;
-}
-
-// One thread owns one weight row and one half (h = 0/1) of every 64-wide K step.  Per step it
-// produces four 16-byte chunks (32 weights); chunk c of a row covers K offsets 8c .. 8c+7.
-//   K-quants: chunks 2h, 2h+1 (first group of the step) and 4+2h, 4+2h+1 (second group)
-//   Q8_0:     chunks 4h .. 4h+3 (block 2t+h of the super-block)
-template <uint32_t FMT>
-struct RowDequant;
-
-template <>
-struct RowDequant<kQ4_K> {
-    struct Scales { float a[8], b[8]; };
-    __device__ static void load_scales(const uint8_t* blk, Scales& s) {
-        const uint4 h = raw16(blk);
-        const float d = f16_bits_to_f32(h.x & 0xffffu) * kPreScale;
-        const float dmin = f16_bits_to_f32(h.x >> 16) * kPreScale;
-        uint32_t sc_lo, sc_hi, m_lo, m_hi;
-        unpack_k_scales(h.y, h.z, h.w, sc_lo, sc_hi, m_lo, m_hi);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            s.a[g] = d * byte_of(g < 4 ? sc_lo : sc_hi, g & 3);
-            s.b[g] = dmin * byte_of(g < 4 ? m_lo : m_hi, g & 3);
-        }
-    }
-    __device__ static int chunk_index(int h, int c) { return (c >> 1) * 4 + 2 * h + (c & 1); }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, ChunkPair (&out)[4]) {
-        const uint4 w = raw16(blk + 16 + 32 * t + 16 * h);
-        out[0] = chunk_from_bytes(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, 0.0f, s.a[2 * t], s.b[2 * t]);
-        out[1] = chunk_from_bytes(w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu, 0.0f, s.a[2 * t], s.b[2 * t]);
-        out[2] = chunk_from_bytes((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, 0.0f, s.a[2 * t + 1], s.b[2 * t + 1]);
-        out[3] = chunk_from_bytes((w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu, 0.0f, s.a[2 * t + 1], s.b[2 * t + 1]);
-    }
-};
-
-template <>
-struct RowDequant<kQ5_K> {
-    using Scales = RowDequant<kQ4_K>::Scales;
-    __device__ static void load_scales(const uint8_t* blk, Scales& s) { RowDequant<kQ4_K>::load_scales(blk, s); }
-    __device__ static int chunk_index(int h, int c) { return RowDequant<kQ4_K>::chunk_index(h, c); }
-    __device__ static uint32_t lo5(uint32_t w, uint32_t hb, int g) { return (w & 0x0f0f0f0fu) | (((hb >> g) & 0x01010101u) << 4); }
-    __device__ static uint32_t hi5(uint32_t w, uint32_t hb, int g) {
-        return ((w >> 4) & 0x0f0f0f0fu) | (((hb >> g) & 0x01010101u) << 4);
-    }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, ChunkPair (&out)[4]) {
-        const uint4 w = raw16(blk + 48 + 32 * t + 16 * h);
-        const uint4 hb = raw16(blk + 16 + 16 * h);
-        const int g = 2 * t;
-        out[0] = chunk_from_bytes(lo5(w.x, hb.x, g), lo5(w.y, hb.y, g), 0.0f, s.a[g], s.b[g]);
-        out[1] = chunk_from_bytes(lo5(w.z, hb.z, g), lo5(w.w, hb.w, g), 0.0f, s.a[g], s.b[g]);
-        out[2] = chunk_from_bytes(hi5(w.x, hb.x, g + 1), hi5(w.y, hb.y, g + 1), 0.0f, s.a[g + 1], s.b[g + 1]);
-        out[3] = chunk_from_bytes(hi5(w.z, hb.z, g + 1), hi5(w.w, hb.w, g + 1), 0.0f, s.a[g + 1], s.b[g + 1]);
-    }
-};
-
-template <>
-struct RowDequant<kQ6_K> {
-    struct Scales { float a[16]; };
-    __device__ static void load_scales(const uint8_t* blk, Scales& s) {
-        const float d = f16_bits_to_f32(ld_u16(blk + 208)) * kPreScale;
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            const uint32_t pair = ld_u16(blk + 192 + i);
-            s.a[i] = d * static_cast<float>(static_cast<int8_t>(pair & 0xffu));
-            s.a[i + 1] = d * static_cast<float>(static_cast<int8_t>(pair >> 8));
-        }
-    }
-    __device__ static int chunk_index(int h, int c) { return RowDequant<kQ4_K>::chunk_index(h, c); }
-    // Step t covers groups 2t and 2t+1 = variants v, v+1 of chunk c = t/2 with v = 2*(t%2):
-    // group 2t reads ql[c*64 + p], group 2t+1 reads ql[c*64 + 32 + p], low nibble when t is even,
-    // high nibble when odd; both take two bits of qh[c*32 + p], at shifts 2v and 2v+2.
-    __device__ static uint32_t q6(uint32_t l, uint32_t hb, int nib, int shift) {
-        return ((l >> nib) & 0x0f0f0f0fu) | (((hb >> shift) & 0x03030303u) << 4);
-    }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, ChunkPair (&out)[4]) {
-        const int c = t >> 1;
-        const int nib = (t & 1) * 4;
-        const int v2 = (t & 1) * 4;  // 2 * variant of the first group
-        const uint4 l0 = raw16_a2(blk + c * 64 + 16 * h);
-        const uint4 l1 = raw16_a2(blk + c * 64 + 32 + 16 * h);
-        const uint4 hb = raw16_a2(blk + 128 + c * 32 + 16 * h);
-        const float s0 = h ? s.a[4 * t + 1] : s.a[4 * t];      // scale index 2*group + position/16
-        const float s1 = h ? s.a[4 * t + 3] : s.a[4 * t + 2];
-        out[0] = chunk_from_bytes(q6(l0.x, hb.x, nib, v2), q6(l0.y, hb.y, nib, v2), 32.0f, s0, 0.0f);
-        out[1] = chunk_from_bytes(q6(l0.z, hb.z, nib, v2), q6(l0.w, hb.w, nib, v2), 32.0f, s0, 0.0f);
-        out[2] = chunk_from_bytes(q6(l1.x, hb.x, nib, v2 + 2), q6(l1.y, hb.y, nib, v2 + 2), 32.0f, s1, 0.0f);
-        out[3] = chunk_from_bytes(q6(l1.z, hb.z, nib, v2 + 2), q6(l1.w, hb.w, nib, v2 + 2), 32.0f, s1, 0.0f);
-    }
-};
-
-template <>
-struct RowDequant<kQ8_0> {
-    struct Scales { float d[8]; };
-    __device__ static void load_scales(const uint8_t* blk, Scales& s) {
-#pragma unroll
-        for (int b = 0; b < 8; ++b) s.d[b] = f16_bits_to_f32(ld_u16(blk + 34 * b)) * kPreScale;
-    }
-    __device__ static int chunk_index(int h, int c) { return 4 * h + c; }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, ChunkPair (&out)[4]) {
-        const uint8_t* q = blk + 34 * (2 * t + h) + 2;
-        const uint4 w0 = raw16_a2(q);
-        const uint4 w1 = raw16_a2(q + 16);
-        const float d = h ? s.d[2 * t + 1] : s.d[2 * t];
-        out[0] = chunk_from_bytes(w0.x ^ 0x80808080u, w0.y ^ 0x80808080u, 128.0f, d, 0.0f);
-        out[1] = chunk_from_bytes(w0.z ^ 0x80808080u, w0.w ^ 0x80808080u, 128.0f, d, 0.0f);
-        out[2] = chunk_from_bytes(w1.x ^ 0x80808080u, w1.y ^ 0x80808080u, 128.0f, d, 0.0f);
-        out[3] = chunk_from_bytes(w1.z ^ 0x80808080u, w1.w ^ 0x80808080u, 128.0f, d, 0.0f);
-    }
-};
+constexpr int kSlots = 4;            // K steps being dequantised at once: slot s fills tile s of the ring
+constexpr int kDequantWarps = 4 * kSlots;   // one thread per (weight row, slot)
+constexpr int kSecondIssuerWarp = 2 + kDequantWarps;
+constexpr int kActivationWarp = 3 + kDequantWarps;
+constexpr int kTcThreads = (4 + kDequantWarps) * 32;
 
 
 // RAWTMA: the raw weight bytes of a stage (128 rows x one super-block) arrive as ONE tiled TMA box
@@ -205,12 +63,18 @@ struct RowDequant<kQ8_0> {
 // viewed as [N rows][row_bytes] of 16-bit elements; it needs row_bytes to be a multiple of 16.
 // Q6_K super-blocks (210 bytes) start on 2-byte boundaries: the box starts at the 16-byte
 // boundary below and is 240 bytes wide, and the remainder is an offset in shared memory.
+// Diagnostics (see TcParams::trace): one stamp per (role, step, event) from CTA (0,0,0).
+__device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int event) {
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && step < 64)
+        p.trace[(role * 64 + step) * 8 + event] = clock64();
+}
+
 template <uint32_t FMT, int NT, bool RAWTMA>
 struct TcGeometry {
     using F = Format<FMT>;
     static constexpr int kBoxBytes = FMT == kQ6_K ? 240 : F::kBytes;
-    static constexpr int kAbStages = NT >= 256 ? 2 : 3;
-    static constexpr int kRawStages = 2;
+    // Four stages keep all four slots busy; the widest tiles leave room for fewer (Q8_0 super-blocks are 272 bytes).
+    static constexpr int kAbStages = NT >= 256 ? 2 : (NT >= 128 || (NT >= 64 && FMT == kQ8_0)) ? 3 : 4;
     // bytes per row in a raw stage: the TMA box width, or a bulk copy from the 16-byte boundary below the block
     static constexpr int kSlot = RAWTMA ? kBoxBytes : ((F::kBytes + 15) / 16) * 16 + 16;
     static constexpr int kRawStageBytes = kBM * kSlot;
@@ -218,10 +82,18 @@ struct TcGeometry {
     static constexpr int kATileBytes = 2 * kAPartBytes;      // high part, then low part
     static constexpr int kBTileBytes = NT * kBK * 2;
     static constexpr int kTilesBytes = kAbStages * (kATileBytes + kBTileBytes);
-    static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kBarrierBytes = 256;
+    // Raw stages fill what is left of shared memory, between two and six.
+    static constexpr int kRawFit = (227 * 1024 - 1024 - kTilesBytes - kBarrierBytes) / kRawStageBytes;
+    static constexpr int kRawStages = kRawFit > 6 ? 6 : kRawFit;
+    static_assert(kRawStages >= 2, "tile plan exceeds shared memory");
+    static_assert(kAbStages <= kSlots, "every tile of the ring needs a slot");
+    static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kSmemBytes = 1024 + kTilesBytes + kRawBytes + kBarrierBytes;  // 1024: alignment slack
-    static constexpr int kTmemColumns = NT < 32 ? 32 : NT;
+    // Two accumulators: even K steps are issued by one thread into the first, odd steps by another
+    // into the second (an issue costs its thread far longer than the tensor pipe needs for so few
+    // tokens); the epilogue adds them.
+    static constexpr int kTmemColumns = 2 * NT < 32 ? 32 : 2 * NT;
     static_assert(kSmemBytes <= 227 * 1024, "tile plan exceeds shared memory");
 };
 
@@ -230,7 +102,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     using G = TcGeometry<FMT, NT, RAWTMA>;
     using F = Format<FMT>;
-    using R = RowDequant<FMT>;
+    using R = RowDequant<FMT, SplitBf16>;
     extern __shared__ uint8_t smem_raw[];
     // The swizzled tiles need a 1024-byte aligned base.
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
@@ -261,10 +133,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             mbar_init(&raw_empty[s], kDequantWarps);
         }
         for (int s = 0; s < G::kAbStages; ++s) {
-            mbar_init(&ab_full[s], kDequantWarps + 1);
+            mbar_init(&ab_full[s], 4 + 1);   // the four warps of the step's slot + the activation tile
             mbar_init(&ab_empty[s], 1);
         }
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 2);
         mbar_fence_init();
         tma_prefetch_descriptor(&xmap);
         if (RAWTMA) tma_prefetch_descriptor(&wmap);
@@ -286,6 +158,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 ok = false;
                 break;
             }
+            if (lane == 0) stamp(p, 3, i, 0);
             if (RAWTMA) {
                 if (lane == 0) {
                     const unsigned long long byte_x = (static_cast<unsigned long long>(sb_begin + i) * F::kBytes) & ~15ull;
@@ -331,32 +204,35 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                     bulk_copy_g2s(raw + rs * G::kRawStageBytes + (lane + 32 * q) * G::kSlot, p.w + a0[q], bytes[q], &raw_full[rs]);
             }
             }
-            // Activation tiles of the four K steps of this super-block.
-            if (lane == 0) {
-                for (int t = 0; t < kSub; ++t) {
-                    const int j = i * kSub + t;
-                    const int as = j % G::kAbStages;
-                    if (j >= G::kAbStages && !mbar_wait_bounded(&ab_empty[as], ((j / G::kAbStages) - 1) & 1)) {
-                        atomicExch(p.status, kDeviceWaitTimeout);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(&ab_full[as], G::kBTileBytes);
-                    tma_load_2d(b_tiles + as * G::kBTileBytes, &xmap, (sb_begin + i) * kSuperBlock + t * kBK, m0, &ab_full[as]);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: one thread ----------------
+    } else if (warp == kActivationWarp) {
+        // ---------------- activation tiles (TMA), one per K step; a warp of its own so that waiting for a
+        // free tile never delays the raw weight stream ----------------
+        if (lane == 0) {
+            for (int j = 0; j < steps; ++j) {
+                const int as = j % G::kAbStages;
+                if (j >= G::kAbStages && !mbar_wait_bounded(&ab_empty[as], ((j / G::kAbStages) - 1) & 1)) {
+                    atomicExch(p.status, kDeviceWaitTimeout);
+                    break;
+                }
+                mbar_arrive_expect_tx(&ab_full[as], G::kBTileBytes);
+                tma_load_2d(b_tiles + as * G::kBTileBytes, &xmap, sb_begin * kSuperBlock + j * kBK, m0, &ab_full[as]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1 || warp == kSecondIssuerWarp) {
+        // ---------------- MMA issuers: one thread for the even steps, one for the odd ones ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_instr_desc(kBM, NT, /*A bf16*/ 1, /*B bf16*/ 1);
-            for (int j = 0; j < steps; ++j) {
+            const int first = warp == 1 ? 0 : 1;
+            const uint32_t acc = tmem_base + first * NT;
+            for (int j = first; j < steps; j += 2) {
                 const int as = j % G::kAbStages;
                 if (!mbar_wait_bounded(&ab_full[as], (j / G::kAbStages) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     break;
                 }
+                stamp(p, 0, j, 0);
                 tcgen05_fence_after_sync();
                 const uint64_t desc_high = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes));
                 const uint64_t desc_low = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes + G::kAPartBytes));
@@ -364,19 +240,20 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk) {
                     // 16 K elements = 32 bytes further along the swizzled row: +2 in the address field
-                    umma_f16(tmem_base, desc_high + 2 * kk, desc_b + 2 * kk, idesc, j > 0 || kk > 0);
-                    umma_f16(tmem_base, desc_low + 2 * kk, desc_b + 2 * kk, idesc, true);
+                    umma_f16(acc, desc_high + 2 * kk, desc_b + 2 * kk, idesc, j > first || kk > 0);
+                    umma_f16(acc, desc_low + 2 * kk, desc_b + 2 * kk, idesc, true);
                 }
                 umma_commit(&ab_empty[as]);
+                stamp(p, 0, j, 1);
             }
             umma_commit(acc_full);
         }
         __syncwarp();
     } else {
         // ---------------- dequant warps: raw bytes -> f16 A tiles ----------------
-        const int t256 = threadIdx.x - 64;
-        const int r = t256 & (kBM - 1);
-        const int h = t256 >> 7;
+        const int worker = threadIdx.x - 64;
+        const int r = worker & (kBM - 1);
+        const int slot = worker >> 7;
         const long long row = static_cast<long long>(n0) + r;
         const bool row_ok = row < p.n;
         // Swizzled position of chunk c of row r: (r/8)*1024 + (r%8)*128 + ((c ^ (r%8)) * 16)
@@ -394,34 +271,44 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             const unsigned long long g0 = (RAWTMA ? 0ull : static_cast<unsigned long long>(row) * p.row_bytes) +
                                           static_cast<unsigned long long>(sb_begin + i) * F::kBytes;
             const uint8_t* blk = raw + rs * G::kRawStageBytes + r * G::kSlot + static_cast<uint32_t>(g0 & 15ull);
+            if (r == 0 && slot == 0) stamp(p, 3, i, 1);
             typename R::Scales scales;
-            if (row_ok) R::load_scales(blk, scales);
+            if (row_ok) R::load_scales(blk, scales, 1.0f);
 #pragma unroll
             for (int t = 0; t < kSub; ++t) {
+                // A slot owns one tile of the ring (slots beyond the ring idle): its waits on that tile's
+                // barriers then follow one another phase by phase, which the one-bit parity needs.
                 const int j = i * kSub + t;
                 const int as = j % G::kAbStages;
+                if (as != slot) continue;
                 if (j >= G::kAbStages && !mbar_wait_bounded(&ab_empty[as], ((j / G::kAbStages) - 1) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
                     break;
                 }
+                if (r == 0) stamp(p, 1, j, 0);
                 uint8_t* tile = a_tiles + as * G::kATileBytes + row_off;
-                ChunkPair out[4];
-                if (row_ok) {
-                    R::step(blk, scales, t, h, out);
-                } else {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) out[c].high = out[c].low = make_uint4(0, 0, 0, 0);
-                }
+                for (int h = 0; h < 2; ++h) {
+                    typename R::Chunk out[4];
+                    if (row_ok) {
+                        R::step(blk, scales, t, h, out);
+                    } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t chunk_off = (static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4;
-                    *reinterpret_cast<uint4*>(tile + chunk_off) = out[c].high;
-                    *reinterpret_cast<uint4*>(tile + G::kAPartBytes + chunk_off) = out[c].low;
+                        for (int c = 0; c < 4; ++c) out[c] = SplitBf16::zero();
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t chunk_off = (static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4;
+                        *reinterpret_cast<uint4*>(tile + chunk_off) = out[c].high;
+                        *reinterpret_cast<uint4*>(tile + G::kAPartBytes + chunk_off) = out[c].low;
+                    }
                 }
+                if (r == 0) stamp(p, 1, j, 1);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ab_full[as]);
+                if (r == 0) stamp(p, 1, j, 2);
             }
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(&raw_empty[rs]);
@@ -442,15 +329,18 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 16) {
                 if (m0 + c0 >= p.m) break;
-                uint32_t v[16];
+                uint32_t v[16], odd[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + NT + c0, odd);
                 tmem_ld_wait();
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) + __uint_as_float(odd[jj]));
                 if (row < p.n) {
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj) {
                         const int m = m0 + c0 + jj;
                         if (m < p.m) {
-                            const float value = __uint_as_float(v[jj]) * (1.0f / kPreScale);
+                            const float value = __uint_as_float(v[jj]);
                             const size_t o = static_cast<size_t>(m) * p.n + row;
                             if (split) {
                                 part[o] = value;
@@ -467,8 +357,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     }
 
     // ---------------- split-K: the CTA that draws the last ticket of its tile adds the partial tiles ----------------
-    if (p.ksplit > 1 && warp >= 2) {
-        // All eight dequant warps take part (they are idle by now): 256 threads, two per weight row.
+    if (p.ksplit > 1 && warp >= 2 && warp < 2 + kDequantWarps) {
+        // All dequant warps take part (they are idle by now): four threads per weight row.
         __threadfence();
         named_barrier_sync(2, kDequantWarps * 32);
         if (threadIdx.x == 64) {
@@ -479,15 +369,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             *last_flag = last ? 1u : 0u;
         }
         named_barrier_sync(2, kDequantWarps * 32);
-        const int t256 = threadIdx.x - 64;
-        const long long row = static_cast<long long>(n0) + (t256 & (kBM - 1));
+        const int worker = threadIdx.x - 64;
+        const long long row = static_cast<long long>(n0) + (worker & (kBM - 1));
         if (*last_flag != 0 && row < p.n) {
             __threadfence();
             const size_t plane = static_cast<size_t>(p.m) * p.n;
             const int m_end = min(m0 + NT, p.m);
             // Four tokens at a time, so that four independent loads per K slice are in flight;
             // the slices are added in index order whatever the arrival order was.
-            for (int m = m0 + 4 * (t256 >> 7); m < m_end; m += 8) {
+            for (int m = m0 + 4 * (worker >> 7); m < m_end; m += 4 * kSlots) {
                 float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 size_t o[4];
 #pragma unroll
@@ -564,7 +454,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.nsb = a.k / kSuperBlock;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
     p.status = a.device_status;
-    p.trace = nullptr;
+    p.trace = a.trace;
     const int n_tiles = (a.n + kBM - 1) / kBM;
     const int m_tiles = (a.m + NT - 1) / NT;
     p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, static_cast<size_t>(a.m) * a.n * sizeof(float),

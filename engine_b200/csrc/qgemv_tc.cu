@@ -1,242 +1,66 @@
-// Decode-batch quantized GEMV on the tensor cores with the block scales applied AFTER the
-// contraction ("group-scaled"): members 1..64, bf16 activations.
+// Quantized GEMV for decode batches (5..64 member rows) on the 5th-generation tensor cores:
+// one f16 operand tile per K step, normalised per super-block.
 //
-//   y[m][n] = sum_g  a[n][g] * ( sum_{k in g} q[n][k] * x[m][k] )  -  c[n][g] * ( sum_{k in g} x[m][k] )
+//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]
 //
-// where g runs over the quantisation groups of a row (32 weights; 16 for Q6_K), q are the raw
-// integer quants and a, c come from the block scales.  The reference computes the same sum one
-// weight at a time on CUDA cores (crates/nvidia/src/kernels/quantized/q4_k.cu:103-258 and twins).
+// The reference serves batches of up to eight members with its CUDA-core GEMV
+// (crates/nvidia/src/quantized.rs:445-487 over q4_k.cu:161-258 and twins).  Here a batch shares one
+// pass over the weights, and the tensor pipe does the multiply-adds.
 //
-// Why this shape.  Dequantising every weight to a float before the product costs ~6-11 issued
-// instructions per weight on B200, several times what the weight stream allows.  The quants
-// themselves are small integers, exactly representable in bf16, and turning a nibble into the bf16
-// number 128+q is one byte permute and one logic op per PAIR of weights.  So the tensor core
-// contracts raw quants with the activations group by group,
-//     D_g[n][m] = sum_{k in g} (128 + q[n][k]) * x[m][k]        (exact products, f32 accumulate)
-//     S_g[m]    = sum_{k in g} x[m][k]                            (CUDA cores, from the activation tile)
-// into a ring of TMEM buffers (one buffer = the groups of a 64-wide K step, one tcgen05.commit per
-// step), and the accumulate warps (thread = weight row) read each finished group with tcgen05.ld and apply  acc[m] += a_g * D_g[m] - c_g * S_g[m],  c_g = min_g + 128 a_g
-// (the 128 and Q6_K's -32 are folded into c).  Per weight that is ~1.2 instructions of unpacking
-// plus 2M/32 FMAs, against one conversion, one FMA and a bf16 split per weight before.
-// Precision is that of an f32-accumulate dot product of the exact weights: nothing is rounded to
-// bf16 except the activations, which already are bf16.
+// A tcgen05.mma of 128 rows x 16 K costs the pipe about 54 cycles however few tokens it has (measured
+// for N <= 64), so the number of MMAs per weight decides the ceiling: this kernel issues one per 16 K
+// elements (the dequantised-operand GEMM of qgemm_tc.cu, which splits every weight into two bf16
+// parts, needs two), and it keeps the per-weight ALU work to the dequantisation itself.
 //
-// Structure of a CTA (896 threads): 128 weight rows x NT tokens (NT in {16, 32, 64}) x a K range.
-//   warp 0        weight producer: one tiled TMA box of raw weight bytes per super-block (or per-row
-//                 bulk copies when rows are not 16-byte aligned)
-//   warp 26       activation producer: one tiled TMA box of activations per 64-wide K step (128-byte
-//                 swizzle, rows past M read as zero) into a ring of its own, deep enough that the
-//                 L2 latency of these small loads never sits on the critical path
-//   warps 1, 27   issue tcgen05.mma (M=128, N=NT, K=16), one thread each, alternate K steps (issuing
-//                 costs ~70 clocks per instruction and thread, more than these small MMAs take to run);
-//                 tcgen05.commit per step
-//   warps 2..     accumulate warps, two or four per TMEM lane quadrant (8 or 16 of the 24 worker warps): work items (group, 16-token chunk)
-//                 are dealt round-robin to the four, so that several tcgen05.ld round trips are in
-//                 flight per quadrant; group scales from the raw block headers, FMAs, then a
-//                 fixed-order sum of the four partial accumulators through shared memory
-//   ..25          unpack warps, four or two per group of 32 rows taking K steps in turn: raw bytes ->
-//                 bf16 quants in the K-major 128-byte-swizzle A tile
-// Every mbarrier wait is bounded; on expiry the status word is set and all warps still reach the
-// teardown that frees TMEM.
+// Operand encoding.  f16 has 11 significant bits (2^-12 relative rounding, inside the 2e-3 bound of
+// the path; a bf16 tile would not be) but only five exponent bits.  Range is handled exactly:
+//   * every (row, super-block) is multiplied by a power of two that brings the largest magnitude its
+//     header allows (e.g. |d|*63*15 + |dmin|*63 for Q4_K) to at most 1024; the MMAs of one
+//     super-block accumulate into a TMEM buffer of their own, and four accumulate warps add
+//     s * D_superblock to f32 registers (s = the inverse power of two), once per 256 K elements;
+//   * every activation row is multiplied by a power of two that brings its largest magnitude to at most
+//     2^14 when it is converted to f16 (a pre-pass, convert_activations_f16 below, which can also
+//     apply RMSNorm first); the epilogue multiplies the result by the inverse.
+// Both scalings are exact, so the only roundings are the one of each weight and each activation to f16.
+//
+// Shape of one CTA: 128 weight rows x NT tokens (16, 32 or 64) x a range of K; 23 warps:
+//   warp 0        raw weight bytes of one super-block x 128 rows per stage (one tiled TMA box, or
+//                 per-row bulk copies for rows that are not 16-byte aligned);
+//   warp 1        MMA issuer (one thread): four tcgen05.mma per 64-wide K step, one tcgen05.commit to free
+//                 a group of steps, one to publish the super-block's TMEM buffer after its last step;
+//   warps 2..17   dequantisation: four slots of 128 threads (one per row); slot s converts K step s of
+//                 every super-block into the swizzled K-major A tile, so four steps are in flight;
+//   warps 18..21  accumulate: thread = weight row (TMEM lane), registers = tokens;
+//   warp 22       activation tiles (tiled TMA, 128-byte swizzle), one per K step.
+// The ring of A/B tiles is deeper than the four slots, so dequantising step j+4 overlaps the MMAs of
+// step j.  Split-K as in qgemm_tc.cu: partial tiles and an atomic ticket, the last CTA of a tile adds
+// them in index order.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets the status word, and every warp
+// still reaches the common teardown that frees TMEM.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "formats.cuh"
 #include "internal.h"
+#include "row_dequant.cuh"
 #include "tc_host.h"
 #include "tcgen05.cuh"
 
 namespace ribn {
 namespace {
 
-constexpr int kBM = 128;
-constexpr int kBK = 64;
-constexpr int kSub = kSuperBlock / kBK;
-// 24 worker warps, split between accumulate and unpack warps by the token tile (see GsGeometry),
-// + weight producer, two MMA issuers, activation producer.
-constexpr int kWorkerWarps = 24;
-constexpr int kGsThreads = (4 + kWorkerWarps) * 32;
-constexpr int kActivationWarp = 2 + kWorkerWarps;
-constexpr int kSecondMmaWarp = kActivationWarp + 1;
-
-__device__ __forceinline__ uint4 raw16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ uint4 raw16_a2(const uint8_t* p) {
-    uint4 v;
-    v.x = ld_u32_a2(p);
-    v.y = ld_u32_a2(p + 4);
-    v.z = ld_u32_a2(p + 8);
-    v.w = ld_u32_a2(p + 12);
-    return v;
-}
-
-// Bytes b0 b1 b2 b3 of `w` spread to the low bytes of 16-bit lanes: [b0,0,b1,0] and [b2,0,b3,0].
-__device__ __forceinline__ uint32_t spread01(uint32_t w) { return __byte_perm(w, 0u, 0x4140u); }
-__device__ __forceinline__ uint32_t spread23(uint32_t w) { return __byte_perm(w, 0u, 0x4342u); }
-
-// A 7-bit unsigned integer v in the low bits of each 16-bit lane -> bf16x2 of (128 + v):
-// 0x4300 is 128.0 in bf16 and its seven mantissa bits count in steps of one.
-constexpr uint32_t kMagic128 = 0x43004300u;
-
-// Eight 4-bit quants (low nibbles of the bytes of u0 and u1) -> one 16-byte chunk of bf16 (128+q).
-__device__ __forceinline__ uint4 chunk_low_nibbles(uint32_t u0, uint32_t u1) {
-    uint4 c;
-    c.x = (spread01(u0) & 0x000f000fu) | kMagic128;
-    c.y = (spread23(u0) & 0x000f000fu) | kMagic128;
-    c.z = (spread01(u1) & 0x000f000fu) | kMagic128;
-    c.w = (spread23(u1) & 0x000f000fu) | kMagic128;
-    return c;
-}
-
-// Per format:
-//   kGroup        weights per scale group (the contraction length of one TMEM buffer)
-//   kUsesSum      whether the epilogue needs S_g (an offset or a minimum to remove)
-//   step()        one thread's 32 weights of a 64-wide K step as four 16-byte chunks of bf16 integers;
-//                 chunk_index(h, c) says which of the row's eight chunks each is
-//   group_scales  a[g], c[g] of one super-block for the accumulate warps
-template <uint32_t FMT>
-struct Quants;
-
-template <>
-struct Quants<kQ4_K> {
-    static constexpr int kGroup = 32;
-    static constexpr bool kUsesSum = true;
-    static constexpr int kGroupsPerSb = 8;
-    static constexpr bool kStoresCoef = true;   // c_g depends on the block minimum
-    __device__ static int chunk_index(int h, int c) { return (c >> 1) * 4 + 2 * h + (c & 1); }
-    __device__ static void step(const uint8_t* blk, int t, int h, uint4 (&out)[4]) {
-        const uint4 w = raw16(blk + 16 + 32 * t + 16 * h);
-        out[0] = chunk_low_nibbles(w.x, w.y);
-        out[1] = chunk_low_nibbles(w.z, w.w);
-        out[2] = chunk_low_nibbles(w.x >> 4, w.y >> 4);
-        out[3] = chunk_low_nibbles(w.z >> 4, w.w >> 4);
-    }
-    __device__ static void group_scales(const uint8_t* blk, float (&a)[8], float (&c)[8]) {
-        const uint4 h = raw16(blk);
-        const float d = f16_bits_to_f32(h.x & 0xffffu);
-        const float dmin = f16_bits_to_f32(h.x >> 16);
-        uint32_t sc_lo, sc_hi, m_lo, m_hi;
-        unpack_k_scales(h.y, h.z, h.w, sc_lo, sc_hi, m_lo, m_hi);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            a[g] = d * byte_of(g < 4 ? sc_lo : sc_hi, g & 3);
-            c[g] = fmaf(128.0f, a[g], dmin * byte_of(g < 4 ? m_lo : m_hi, g & 3));
-        }
-    }
-};
-
-template <>
-struct Quants<kQ5_K> {
-    static constexpr int kGroup = 32;
-    static constexpr bool kUsesSum = true;
-    static constexpr int kGroupsPerSb = 8;
-    static constexpr bool kStoresCoef = true;   // c_g depends on the block minimum
-    __device__ static int chunk_index(int h, int c) { return Quants<kQ4_K>::chunk_index(h, c); }
-    // Low nibbles of u plus the fifth bit (bit `bit` of the matching byte of hb), as bf16 (128+q).
-    __device__ static uint32_t pair(uint32_t u_spread, uint32_t hb_spread, int bit) {
-        return ((u_spread & 0x000f000fu) | (((hb_spread >> bit) & 0x00010001u) << 4)) | kMagic128;
-    }
-    __device__ static uint4 chunk(uint32_t u0, uint32_t u1, uint32_t h0, uint32_t h1, int bit) {
-        uint4 c;
-        c.x = pair(spread01(u0), spread01(h0), bit);
-        c.y = pair(spread23(u0), spread23(h0), bit);
-        c.z = pair(spread01(u1), spread01(h1), bit);
-        c.w = pair(spread23(u1), spread23(h1), bit);
-        return c;
-    }
-    __device__ static void step(const uint8_t* blk, int t, int h, uint4 (&out)[4]) {
-        const uint4 w = raw16(blk + 48 + 32 * t + 16 * h);
-        const uint4 hb = raw16(blk + 16 + 16 * h);
-        out[0] = chunk(w.x, w.y, hb.x, hb.y, 2 * t);
-        out[1] = chunk(w.z, w.w, hb.z, hb.w, 2 * t);
-        out[2] = chunk(w.x >> 4, w.y >> 4, hb.x, hb.y, 2 * t + 1);
-        out[3] = chunk(w.z >> 4, w.w >> 4, hb.z, hb.w, 2 * t + 1);
-    }
-    __device__ static void group_scales(const uint8_t* blk, float (&a)[8], float (&c)[8]) {
-        Quants<kQ4_K>::group_scales(blk, a, c);
-    }
-};
-
-template <>
-struct Quants<kQ6_K> {
-    static constexpr int kGroup = 16;   // one int8 scale per 16 weights
-    static constexpr bool kUsesSum = true;
-    static constexpr int kGroupsPerSb = 16;
-    static constexpr bool kStoresCoef = false;  // c_g = 160 a_g
-    __device__ static int chunk_index(int h, int c) { return Quants<kQ4_K>::chunk_index(h, c); }
-    // 4 low bits from ql (nibble `nib`), 2 high bits from qh (at `shift`): 0..63, as bf16 (128+q).
-    __device__ static uint32_t pair(uint32_t l_spread, uint32_t h_spread, int nib, int shift) {
-        return (((l_spread >> nib) & 0x000f000fu) | (((h_spread >> shift) & 0x00030003u) << 4)) | kMagic128;
-    }
-    __device__ static uint4 chunk(uint32_t l0, uint32_t l1, uint32_t h0, uint32_t h1, int nib, int shift) {
-        uint4 c;
-        c.x = pair(spread01(l0), spread01(h0), nib, shift);
-        c.y = pair(spread23(l0), spread23(h0), nib, shift);
-        c.z = pair(spread01(l1), spread01(h1), nib, shift);
-        c.w = pair(spread23(l1), spread23(h1), nib, shift);
-        return c;
-    }
-    // Step t = groups-of-32 2t and 2t+1 (see qgemm_tc.cu): ql chunk c = t/2, low nibble for even t,
-    // qh shifts 4*(t%2) and 4*(t%2)+2.
-    __device__ static void step(const uint8_t* blk, int t, int h, uint4 (&out)[4]) {
-        const int c = t >> 1;
-        const int nib = (t & 1) * 4;
-        const int v2 = (t & 1) * 4;
-        const uint4 l0 = raw16_a2(blk + c * 64 + 16 * h);
-        const uint4 l1 = raw16_a2(blk + c * 64 + 32 + 16 * h);
-        const uint4 hb = raw16_a2(blk + 128 + c * 32 + 16 * h);
-        out[0] = chunk(l0.x, l0.y, hb.x, hb.y, nib, v2);
-        out[1] = chunk(l0.z, l0.w, hb.z, hb.w, nib, v2);
-        out[2] = chunk(l1.x, l1.y, hb.x, hb.y, nib, v2 + 2);
-        out[3] = chunk(l1.z, l1.w, hb.z, hb.w, nib, v2 + 2);
-    }
-    // w = a * (q6 - 32) and the tile holds 128 + q6: c = 160 a.
-    __device__ static void group_scales(const uint8_t* blk, float (&a)[16], float (&c)[16]) {
-        const float d = f16_bits_to_f32(ld_u16(blk + 208));
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            const uint32_t pair = ld_u16(blk + 192 + i);
-            a[i] = d * static_cast<float>(static_cast<int8_t>(pair & 0xffu));
-            a[i + 1] = d * static_cast<float>(static_cast<int8_t>(pair >> 8));
-            c[i] = 160.0f * a[i];
-            c[i + 1] = 160.0f * a[i + 1];
-        }
-    }
-};
-
-template <>
-struct Quants<kQ8_0> {
-    static constexpr int kGroup = 32;
-    static constexpr bool kUsesSum = false;  // int8 quants convert exactly, no offset to remove
-    static constexpr int kGroupsPerSb = 8;
-    static constexpr bool kStoresCoef = false;  // no offset
-    __device__ static int chunk_index(int h, int c) { return 4 * h + c; }
-    __device__ static uint32_t pair(float lo, float hi) {
-        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // |q| <= 128: exact in bf16
-        return *reinterpret_cast<const uint32_t*>(&v);
-    }
-    __device__ static uint4 chunk(uint32_t u0, uint32_t u1) {
-        float a[4], b[4];
-        bytes_to_float4(u0 ^ 0x80808080u, 128.0f, a);
-        bytes_to_float4(u1 ^ 0x80808080u, 128.0f, b);
-        return make_uint4(pair(a[0], a[1]), pair(a[2], a[3]), pair(b[0], b[1]), pair(b[2], b[3]));
-    }
-    __device__ static void step(const uint8_t* blk, int t, int h, uint4 (&out)[4]) {
-        const uint8_t* q = blk + 34 * (2 * t + h) + 2;
-        const uint4 w0 = raw16_a2(q);
-        const uint4 w1 = raw16_a2(q + 16);
-        out[0] = chunk(w0.x, w0.y);
-        out[1] = chunk(w0.z, w0.w);
-        out[2] = chunk(w1.x, w1.y);
-        out[3] = chunk(w1.z, w1.w);
-    }
-    __device__ static void group_scales(const uint8_t* blk, float (&a)[8], float (&c)[8]) {
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-            a[b] = f16_bits_to_f32(ld_u16(blk + 34 * b));
-            c[b] = 0.0f;
-        }
-    }
-};
-
+constexpr int kBM = 128;                 // weight rows per CTA
+constexpr int kBK = 64;                  // K elements per step (one 128-byte swizzled row of f16)
+constexpr int kSub = kSuperBlock / kBK;  // steps per super-block
+constexpr int kSlots = 4;                // K steps being dequantised at once
+constexpr int kDequantWarps = 4 * kSlots;
+constexpr int kFirstAccWarp = 2 + kDequantWarps;
+constexpr int kAccWarps = 4;
+constexpr int kActivationWarp = kFirstAccWarp + kAccWarps;
+constexpr int kThreads = (kActivationWarp + 1) * 32;
+constexpr int kAccBuffers = 4;           // super-blocks whose products may wait in TMEM
+static_assert(kSlots == kSub, "slot s owns K step s of every super-block");
 
 // Diagnostics (see TcParams::trace): one stamp per (role, step, event) from CTA (0,0,0).
 __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int event) {
@@ -245,74 +69,66 @@ __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>
-struct GsGeometry {
+struct Geometry {
     using F = Format<FMT>;
-    using Q = Quants<FMT>;
-    static constexpr int kAbStages = 4;
-    // 64 tokens make eight work items per K step for the accumulate warps: four of them per TMEM lane
-    // quadrant and two unpack slots; smaller tiles need the warps on the unpack side instead.
-    static constexpr int kAccSlots = NT >= 64 ? 4 : 2;             // accumulate warps per TMEM lane quadrant
-    static constexpr int kAccWarps = 4 * kAccSlots;
-    static constexpr int kUnpackSlots = (kWorkerWarps - kAccWarps) / 4;   // K steps in flight per group of 32 rows
-    static constexpr int kUnpackWarps = 4 * kUnpackSlots;          // one thread per weight row and slot
-    static constexpr int kFirstUnpackThread = (2 + kAccWarps) * 32;
-    static_assert(kUnpackSlots == 2 || kUnpackSlots == 4, "unpack slots take K steps modulo a power of two");
-    static constexpr int kGroupsPerStep = kBK / Q::kGroup;      // 2, or 4 for Q6_K
-    static constexpr int kMmasPerGroup = Q::kGroup / 16;        // 2, or 1 for Q6_K
-    static constexpr int kChunks = NT / 16;                     // 16-token chunks
-    // TMEM: a ring of step buffers, each holding the D_g of the groups of one 64-wide K step.
-    static constexpr int kStepCols = kGroupsPerStep * NT;
-    static constexpr int kStepBuffers = 512 / kStepCols < 4 ? 512 / kStepCols : 4;
-    static constexpr int kTmemColumns = kStepBuffers * kStepCols < 32 ? 32 : kStepBuffers * kStepCols;
     static constexpr int kBoxBytes = FMT == kQ6_K ? 240 : F::kBytes;
     static constexpr int kSlot = RAWTMA ? kBoxBytes : ((F::kBytes + 15) / 16) * 16 + 16;
     static constexpr int kRawStageBytes = kBM * kSlot;
     static constexpr int kATileBytes = kBM * kBK * 2;
     static constexpr int kBTileBytes = NT * kBK * 2;
-    static constexpr int kSumBytes = kStepBuffers * kGroupsPerStep * NT * 4;   // S_g[m] ring, f32
-    static constexpr int kScaleStages = 2;                       // super-blocks of decoded group scales kept
-    static constexpr int kScaleRow = (Q::kStoresCoef ? 2 : 1) * Q::kGroupsPerSb;   // floats per row: a[g], then c[g] if stored
-    static constexpr int kScaleBytes = kScaleStages * kBM * kScaleRow * 4;
-    static constexpr int kBGroups = NT >= 64 ? 2 : 3;           // activation tiles are recycled a super-block (4 tiles) at a time
-    static constexpr int kBStages = kBGroups * kSub;
-    static constexpr int kTilesBytes = kAbStages * kATileBytes + kBStages * kBTileBytes;
+    // The tiles form two groups of consecutive K steps.  A group is handed to the MMA issuer, and handed
+    // back, as a whole: one wait, 4 MMAs per step back to back, one commit -- a wait or a commit costs the
+    // issuing thread as much as several MMAs.  While the tensor pipe reads one group the slots fill the other.
+    static constexpr int kGroupSteps = (NT >= 64 || FMT == kQ8_0) ? 3 : 4;   // as many as shared memory holds
+    static constexpr int kGroups = 2;
+    static constexpr int kStages = kGroups * kGroupSteps;
+    static constexpr int kTilesBytes = kStages * (kATileBytes + kBTileBytes);
+    static constexpr int kScaleBytes = kAccBuffers * kBM * 4;   // s per (buffer, row)
     static constexpr int kBarrierBytes = 512;
-    static constexpr int kFixedBytes = 1024 + kTilesBytes + kSumBytes + kScaleBytes + kBarrierBytes;
-    // Raw stages fill what is left of shared memory (at most 8): the bytes in flight per SM must
-    // cover the DRAM latency, about 100 KB at 43 GB/s per SM and ~2 us.
+    static constexpr int kFixedBytes = 1024 + kTilesBytes + kScaleBytes + kBarrierBytes;   // 1024: alignment slack
     static constexpr int kRawFit = (227 * 1024 - kFixedBytes) / kRawStageBytes;
-    static constexpr int kRawStages = kRawFit > 8 ? 8 : kRawFit;
+    static constexpr int kRawStages = kRawFit > 6 ? 6 : kRawFit;
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kSmemBytes = kFixedBytes + kRawBytes;
-    static_assert(kAccSlots % kChunks == 0, "a slot must always see the same token chunk");
-    static_assert(kAccSlots * kBM * 16 * 4 <= kAbStages * kATileBytes, "the final partial sums reuse the A tiles");
+    static constexpr int kTmemColumns = kAccBuffers * NT < 32 ? 32 : kAccBuffers * NT;
     static_assert(kRawStages >= 2, "tile plan exceeds shared memory");
-    static_assert(kTmemColumns <= 512 && (kTmemColumns & (kTmemColumns - 1)) == 0, "TMEM columns must be a power of two <= 512");
+    static_assert(kStages >= kSlots, "a waiter may be at most one barrier phase behind");
+    static constexpr int kGroupArrivals = kGroupSteps * (4 + 1);   // per step: the slot's four warps + the activation tile
+    static_assert((kTmemColumns & (kTmemColumns - 1)) == 0 && kTmemColumns <= 512, "TMEM columns: a power of two <= 512");
+    static_assert((2 * kRawStages + 2 * kGroups + 2 * kAccBuffers) * 8 + 16 <= kBarrierBytes, "barrier block too small");
 };
 
+// s = 2^e with bound * 2^-e in (512, 1024]; inverse = 2^-e.  A zero bound (all-zero block) gives 0, 0.
+__device__ __forceinline__ void normaliser(float bound, float& inverse, float& s) {
+    const uint32_t bits = __float_as_uint(bound);
+    const int exponent = static_cast<int>(bits >> 23) - 127;    // bound in [2^exponent, 2^(exponent+1))
+    int e = exponent + 1 - 10;                                   // bound * 2^-e < 1024
+    e = max(-100, min(100, e));
+    const bool usable = bound > 0.0f && bound < 3.0e38f;
+    inverse = usable ? __uint_as_float(static_cast<uint32_t>(127 - e) << 23) : 0.0f;
+    s = usable ? __uint_as_float(static_cast<uint32_t>(127 + e) << 23) : 0.0f;
+}
+
 template <uint32_t FMT, int NT, bool RAWTMA>
-__global__ void __launch_bounds__(kGsThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const TcParams p) {
-    using G = GsGeometry<FMT, NT, RAWTMA>;
+    using G = Geometry<FMT, NT, RAWTMA>;
     using F = Format<FMT>;
-    using Q = Quants<FMT>;
+    using R = RowDequant<FMT, SingleF16>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint8_t* a_tiles = smem;
-    uint8_t* b_tiles = a_tiles + G::kAbStages * G::kATileBytes;
-    float* s_ring = reinterpret_cast<float*>(b_tiles + G::kBStages * G::kBTileBytes);   // [step buffer][group][token]
-    float* scale_ring = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_ring) + G::kSumBytes);   // [stage][row][a.., c..]
+    uint8_t* b_tiles = a_tiles + G::kStages * G::kATileBytes;
+    float* scale_ring = reinterpret_cast<float*>(b_tiles + G::kStages * G::kBTileBytes);   // [buffer][row]
     uint8_t* raw = reinterpret_cast<uint8_t*>(scale_ring) + G::kScaleBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + G::kRawBytes);
-    uint64_t* raw_full = bars;                        // [kRawStages]
-    uint64_t* raw_empty = raw_full + 8;               // [kRawStages], every warp that reads the raw stage
-    uint64_t* b_full = raw_empty + 8;                 // [kBStages], activation tile landed (TMA bytes)
-    uint64_t* b_empty = b_full + 12;                  // [kBGroups], one tcgen05.commit from each MMA issuer
-    uint64_t* ab_full = b_empty + 12;                 // [kAbStages], the four unpack warps of the step
-    uint64_t* ab_empty = ab_full + G::kAbStages;      // [kAbStages], tcgen05.commit
-    uint64_t* d_full = ab_empty + G::kAbStages;       // [kStepBuffers], tcgen05.commit
-    uint64_t* d_empty = d_full + 4;                   // [kStepBuffers], all accumulate warps
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + 4);
+    uint64_t* raw_full = bars;                        // [kRawStages]  TMA bytes (or 32 producer lanes)
+    uint64_t* raw_empty = raw_full + G::kRawStages;   // [kRawStages]  16 dequant warps
+    uint64_t* g_full = raw_empty + G::kRawStages;     // [kGroups]     per step of the group: the slot's 4 warps + the activation tile
+    uint64_t* g_empty = g_full + G::kGroups;          // [kGroups]     tcgen05.commit
+    uint64_t* d_full = g_empty + G::kGroups;          // [kAccBuffers] tcgen05.commit after a super-block's last MMA
+    uint64_t* d_empty = d_full + kAccBuffers;         // [kAccBuffers] 4 accumulate warps
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + kAccBuffers);
     uint32_t* last_flag = tmem_holder + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -327,17 +143,15 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < G::kRawStages; ++s) {
             mbar_init(&raw_full[s], RAWTMA ? 1 : 32);
-            mbar_init(&raw_empty[s], G::kUnpackWarps);
+            mbar_init(&raw_empty[s], kDequantWarps);
         }
-        for (int s = 0; s < G::kAbStages; ++s) {
-            mbar_init(&ab_full[s], 4);
-            mbar_init(&ab_empty[s], 1);
+        for (int s = 0; s < G::kGroups; ++s) {
+            mbar_init(&g_full[s], G::kGroupArrivals);
+            mbar_init(&g_empty[s], 1);
         }
-        for (int s = 0; s < G::kBStages; ++s) mbar_init(&b_full[s], 1);
-        for (int s = 0; s < G::kBGroups; ++s) mbar_init(&b_empty[s], 2);
-        for (int s = 0; s < G::kStepBuffers; ++s) {
+        for (int s = 0; s < kAccBuffers; ++s) {
             mbar_init(&d_full[s], 1);
-            mbar_init(&d_empty[s], G::kAccWarps);
+            mbar_init(&d_empty[s], kAccWarps);
         }
         mbar_fence_init();
         tma_prefetch_descriptor(&xmap);
@@ -350,26 +164,23 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     const uint32_t tmem_base = *tmem_holder;
 
     if (warp == 0) {
-        // ---------------- producer ----------------
+        // ---------------- raw weight bytes ----------------
         const unsigned long long safe_end = p.w_bytes & ~15ull;
-        bool ok = true;
-        for (int i = 0; i < nsb_local && ok; ++i) {
+        for (int i = 0; i < nsb_local; ++i) {
             const int rs = i % G::kRawStages;
             if (i >= G::kRawStages && !mbar_wait_bounded(&raw_empty[rs], ((i / G::kRawStages) - 1) & 1)) {
                 atomicExch(p.status, kDeviceWaitTimeout);
-                ok = false;
                 break;
             }
+            if (lane == 0) stamp(p, 3, i, 0);
             if (RAWTMA) {
                 if (lane == 0) {
                     const unsigned long long byte_x = (static_cast<unsigned long long>(sb_begin + i) * F::kBytes) & ~15ull;
                     mbar_arrive_expect_tx(&raw_full[rs], kBM * G::kBoxBytes);
                     tma_load_2d(raw + rs * G::kRawStageBytes, &wmap, static_cast<int>(byte_x >> 1), n0, &raw_full[rs]);
-                    stamp(p, 3, i, 0);
                 }
             } else {
-                // Rows that do not start on 16-byte boundaries: four bulk copies per lane, each from
-                // the boundary below its block; the last bytes of the tensor by plain loads.
+                // Each lane brings four rows of the stage: one arrive with the byte total, then the copies.
                 unsigned long long a0[4];
                 uint32_t bytes[4];
                 uint32_t total = 0;
@@ -386,6 +197,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                         a0[q] = g0 & ~15ull;
                         unsigned long long a1 = (g1 + 15ull) & ~15ull;
                         if (a1 > safe_end) {
+                            // Last bytes of a tensor whose length is not a multiple of 16: plain loads.
                             const unsigned long long bulk_end = safe_end > a0[q] ? safe_end : a0[q];
                             uint8_t* dst = raw + rs * G::kRawStageBytes + r * G::kSlot;
                             for (unsigned long long o = bulk_end; o < g1; ++o) dst[o - a0[q]] = p.w[o];
@@ -406,68 +218,75 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                         bulk_copy_g2s(raw + rs * G::kRawStageBytes + (lane + 32 * q) * G::kSlot, p.w + a0[q], bytes[q], &raw_full[rs]);
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
     } else if (warp == kActivationWarp) {
-        // ---------------- activation producer ----------------
+        // ---------------- activation tiles ----------------
         if (lane == 0) {
-            for (int i = 0; i < nsb_local; ++i) {
-                const int g = i % G::kBGroups;
-                if (i >= G::kBGroups && !mbar_wait_bounded(&b_empty[g], ((i / G::kBGroups) - 1) & 1)) {
+            for (int j = 0; j < steps; ++j) {
+                const int as = j % G::kStages;
+                const int g = as / G::kGroupSteps;
+                if (j >= G::kStages && !mbar_wait_bounded(&g_empty[g], ((j / G::kStages) - 1) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     break;
                 }
-                for (int t = 0; t < kSub; ++t) {
-                    const int bs = g * kSub + t;
-                    mbar_arrive_expect_tx(&b_full[bs], G::kBTileBytes);
-                    tma_load_2d(b_tiles + bs * G::kBTileBytes, &xmap, (sb_begin + i) * kSuperBlock + t * kBK, m0, &b_full[bs]);
-                }
+                mbar_arrive_expect_tx(&g_full[g], G::kBTileBytes);
+                tma_load_2d(b_tiles + as * G::kBTileBytes, &xmap, sb_begin * kSuperBlock + j * kBK, m0, &g_full[g]);
             }
         }
         __syncwarp();
-    } else if (warp == 1 || warp == kSecondMmaWarp) {
-        // ---------------- MMA issuers: all groups of a K step, then the commits ----------------
-        // The unpack warps have already waited for the activation tile and for the TMEM step buffer
-        // before they arrive on ab_full, so one wait covers all three conditions.
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_instr_desc(kBM, NT, /*A bf16*/ 1, /*B bf16*/ 1);
-            const int first = warp == 1 ? 0 : 1;
-            for (int j = first; j < steps; j += 2) {
-                const int as = j % G::kAbStages;
-                const int bs = j % G::kBStages;
-                const int sbuf = j % G::kStepBuffers;
-                if (!mbar_wait_bounded(&ab_full[as], (j / G::kAbStages) & 1)) {
-                    atomicExch(p.status, kDeviceWaitTimeout);
-                    break;
-                }
-                tcgen05_fence_after_sync();
-                stamp(p, 0, j, 0);
-                const uint64_t desc_a = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes));
-                const uint64_t desc_b = umma_smem_desc_sw128(smem_addr(b_tiles + bs * G::kBTileBytes));
-#pragma unroll
-                for (int gg = 0; gg < G::kGroupsPerStep; ++gg) {
-                    const uint32_t d_addr = tmem_base + sbuf * G::kStepCols + gg * NT;
-#pragma unroll
-                    for (int kk = 0; kk < G::kMmasPerGroup; ++kk) {
-                        const int k16 = gg * G::kMmasPerGroup + kk;  // 32 bytes along the swizzled row per K=16
-                        umma_f16(d_addr, desc_a + 2 * k16, desc_b + 2 * k16, idesc, kk > 0);
-                    }
-                }
-                umma_commit(&d_full[sbuf]);
-                umma_commit(&ab_empty[as]);
-                // the last two steps of a super-block (one per issuer) release its four activation tiles
-                if ((j & (kSub - 1)) >= kSub - 2) umma_commit(&b_empty[(j / kSub) % G::kBGroups]);
-                stamp(p, 0, j, 1);
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the whole warp runs this loop converged, an elected lane issues ----------------
+        constexpr uint32_t idesc = umma_instr_desc(kBM, NT, /*A f16*/ 0, /*B f16*/ 0);
+        const uint64_t desc_a0 = umma_smem_desc_sw128(smem_addr(a_tiles));
+        const uint64_t desc_b0 = umma_smem_desc_sw128(smem_addr(b_tiles));
+        const int groups = (steps + G::kGroupSteps - 1) / G::kGroupSteps;
+        const int missing = groups * G::kGroupSteps - steps;
+        bool ok = true;
+        for (int gi = 0; gi < groups && ok; ++gi) {
+            const int g = gi % G::kGroups;
+            if (gi == groups - 1 && lane == 0) {
+                // The last group may be short: the issuer stands in for the arrivals of the steps it lacks
+                // (now, when the barrier's earlier phases are over).
+                for (int u = 0; u < missing * (4 + 1); ++u) mbar_arrive(&g_full[g]);
             }
+            __syncwarp();
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&g_full[g], (gi / G::kGroups) & 1));
+            if (!ok) break;
+            if (lane == 0) stamp(p, 0, gi, 0);
+            __syncwarp();
+            tcgen05_fence_after_sync();
+#pragma unroll
+            for (int u = 0; u < G::kGroupSteps; ++u) {
+                const int j = gi * G::kGroupSteps + u;
+                if (j >= steps) break;
+                const int i = j / kSub;
+                const int t = j % kSub;
+                const int buf = i % kAccBuffers;
+                if (t == 0 && i >= kAccBuffers) {
+                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(&d_empty[buf], ((i / kAccBuffers) - 1) & 1));
+                    if (!ok) break;
+                    tcgen05_fence_after_sync();
+                }
+                const int as = g * G::kGroupSteps + u;
+                umma_f16_step4_elected(tmem_base + buf * NT, desc_a0 + static_cast<uint64_t>(as * (G::kATileBytes >> 4)),
+                                       desc_b0 + static_cast<uint64_t>(as * (G::kBTileBytes >> 4)), idesc, t > 0 ? 1u : 0u);
+                if (t == kSub - 1) umma_commit_elected(&d_full[buf]);
+            }
+            if (!ok) break;
+            umma_commit_elected(&g_empty[g]);
+            if (lane == 0) stamp(p, 0, gi, 1);
+            __syncwarp();
         }
+        if (!ok && lane == 0) atomicExch(p.status, kDeviceWaitTimeout);
         __syncwarp();
-    }
-    else if (warp >= 2 + G::kAccWarps && warp < kActivationWarp) {
-        // ---------------- unpack warps: raw bytes -> bf16 quants; group sums of the activations ----------------
-        const int r = (threadIdx.x - G::kFirstUnpackThread) & (kBM - 1);    // one thread per weight row and slot
-        const int unpack_slot = (threadIdx.x - G::kFirstUnpackThread) >> 7;  // this warp takes K steps j with j % slots == slot
+    } else if (warp < kFirstAccWarp) {
+        // ---------------- dequantisation: raw bytes -> f16 A tiles ----------------
+        const int worker = threadIdx.x - 64;
+        const int r = worker & (kBM - 1);
+        const int slot = worker >> 7;
         const long long row = static_cast<long long>(n0) + r;
         const bool row_ok = row < p.n;
+        // Swizzled position of chunk c of row r: (r/8)*1024 + (r%8)*128 + ((c ^ (r%8)) * 16)
         const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128;
         const uint32_t sw = r & 7;
         bool ok = true;
@@ -478,223 +297,166 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 ok = false;
                 break;
             }
+            if (r == 0 && slot == 0) stamp(p, 3, i, 1);
+            // With the TMA box rows are 16-byte aligned, so only the block's offset inside its row counts.
             const unsigned long long g0 = (RAWTMA ? 0ull : static_cast<unsigned long long>(row) * p.row_bytes) +
                                           static_cast<unsigned long long>(sb_begin + i) * F::kBytes;
             const uint8_t* blk = raw + rs * G::kRawStageBytes + r * G::kSlot + static_cast<uint32_t>(g0 & 15ull);
-            if (r == 0 && unpack_slot == 0) stamp(p, 3, i, 1);
+            float inverse = 0.0f, s = 0.0f;
+            typename R::Scales scales;
+            if (row_ok) {
+                normaliser(R::magnitude_bound(blk), inverse, s);
+                R::load_scales(blk, scales, inverse);
+            }
+            const int j = i * kSub + slot;
+            const int as = j % G::kStages;
+            const int g = as / G::kGroupSteps;
+            if (j >= G::kStages && !mbar_wait_bounded(&g_empty[g], ((j / G::kStages) - 1) & 1)) {
+                atomicExch(p.status, kDeviceWaitTimeout);
+                ok = false;
+                break;
+            }
+            if (r == 0) stamp(p, 1, j, 0);
+            uint8_t* tile = a_tiles + as * G::kATileBytes + row_off;
 #pragma unroll
             for (int t = 0; t < kSub; ++t) {
-                if ((t & (G::kUnpackSlots - 1)) != unpack_slot) continue;
-                const int j = i * kSub + t;
-                const int as = j % G::kAbStages;
-                const int sbuf = j % G::kStepBuffers;
-                if (j >= G::kAbStages && !mbar_wait_bounded(&ab_empty[as], ((j / G::kAbStages) - 1) & 1)) {
-                    atomicExch(p.status, kDeviceWaitTimeout);
-                    ok = false;
-                    break;
-                }
-                if (r == 0) stamp(p, 1, j, 0);
-                uint8_t* tile = a_tiles + as * G::kATileBytes + row_off;
+                if (t != slot) continue;   // compile-time step index for the format's tables
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    uint4 out[4];
+                    typename R::Chunk out[4];
                     if (row_ok) {
-                        Q::step(blk, t, h, out);
+                        R::step(blk, scales, t, h, out);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+                        for (int c = 0; c < 4; ++c) out[c] = SingleF16::zero();
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4*>(tile + ((static_cast<uint32_t>(Q::chunk_index(h, c)) ^ sw) << 4)) = out[c];
+                        *reinterpret_cast<uint4*>(tile + ((static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4)) = out[c].high;
                 }
-                if (r == 0) stamp(p, 1, j, 1);
-                // The MMA of this step needs the activation tile and a free TMEM step buffer as well; waiting
-                // for both here lets the issuer wait on ab_full alone.
-                const int bs = j % G::kBStages;
-                if (!mbar_wait_bounded(&b_full[bs], (j / G::kBStages) & 1) ||
-                    (j >= G::kStepBuffers && !mbar_wait_bounded(&d_empty[sbuf], ((j / G::kStepBuffers) - 1) & 1))) {
+            }
+            if (r == 0) stamp(p, 1, j, 1);
+            if (slot == 0) {
+                // The super-block's factor for the accumulate warps.  Entry i % 4 was last read for super-block
+                // i - 4; waiting for that TMEM buffer's release covers the entry too.
+                const int buf = i % kAccBuffers;
+                if (i >= kAccBuffers && !mbar_wait_bounded(&d_empty[buf], ((i / kAccBuffers) - 1) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
                     break;
                 }
-                if (t == 0 && unpack_slot == 0) {
-                    // Group scales of this row for the accumulate warps.  Entry i % 2 was last read for super-block
-                    // i - 2, which the accumulate warps finished before this warp could get here: its wait for the
-                    // TMEM buffer of this step follows the accumulation of step 4(i-1), the first of super-block i-1.
-                    float ga[Q::kGroupsPerSb], gcoef[Q::kGroupsPerSb];
-                    if (row_ok) {
-                        Q::group_scales(blk, ga, gcoef);
-                    } else {
-#pragma unroll
-                        for (int g = 0; g < Q::kGroupsPerSb; ++g) ga[g] = gcoef[g] = 0.0f;
-                    }
-                    float* dst = scale_ring + ((i % G::kScaleStages) * kBM + r) * G::kScaleRow;
-#pragma unroll
-                    for (int g = 0; g < Q::kGroupsPerSb; g += 4) {
-                        *reinterpret_cast<float4*>(dst + g) = make_float4(ga[g], ga[g + 1], ga[g + 2], ga[g + 3]);
-                        if (Q::kStoresCoef)
-                            *reinterpret_cast<float4*>(dst + Q::kGroupsPerSb + g) = make_float4(gcoef[g], gcoef[g + 1], gcoef[g + 2], gcoef[g + 3]);
-                    }
-                }
-                if (Q::kUsesSum) {
-                    // S_g[m] = sum over the group's K range of x[m][k], from the activation tile: a thread sums
-                    // one 16-byte chunk (8 values), the chunks of a group are combined across neighbouring lanes.
-                    if (r == 0) stamp(p, 1, j, 2);
-                    const uint8_t* btile = b_tiles + bs * G::kBTileBytes;
-                    float* sums = s_ring + sbuf * G::kGroupsPerStep * NT;
-                    constexpr int kChunksPerGroup = Q::kGroup / 8;   // 4, or 2 for Q6_K
-#pragma unroll
-                    for (int task = r; task < NT * 8; task += kBM) {
-                        const int m = task >> 3;
-                        const int ck = task & 7;
-                        const uint4 v = *reinterpret_cast<const uint4*>(btile + (m >> 3) * 1024 + (m & 7) * 128 + ((ck ^ (m & 7)) << 4));
-                        float part = ((__uint_as_float(v.x << 16) + __uint_as_float(v.x & 0xffff0000u)) +
-                                      (__uint_as_float(v.y << 16) + __uint_as_float(v.y & 0xffff0000u))) +
-                                     ((__uint_as_float(v.z << 16) + __uint_as_float(v.z & 0xffff0000u)) +
-                                      (__uint_as_float(v.w << 16) + __uint_as_float(v.w & 0xffff0000u)));
-                        part += __shfl_xor_sync(0xffffffffu, part, 1);
-                        if (kChunksPerGroup == 4) part += __shfl_xor_sync(0xffffffffu, part, 2);
-                        if ((ck & (kChunksPerGroup - 1)) == 0) sums[(ck / kChunksPerGroup) * NT + m] = part;
-                    }
-                }
-                if (r == 0) stamp(p, 1, j, 3);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&ab_full[as]);
-                if (r == 0) stamp(p, 1, j, 4);
+                scale_ring[buf * kBM + r] = s;
             }
+            fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0 && ok) mbar_arrive(&raw_empty[rs]);
+            if (lane == 0) {
+                mbar_arrive(&g_full[g]);
+                mbar_arrive(&raw_empty[rs]);
+            }
+            if (r == 0) stamp(p, 1, j, 2);
             ok = __all_sync(0xffffffffu, ok);
         }
-    } else {
-        // ---------------- accumulate warps: acc[m] += a_g * D_g[m] - c_g * S_g[m] ----------------
-        // Work item = (group, chunk of 16 tokens), numbered group-major; item `it` belongs to slot
-        // it % 4 of each quadrant.  kChunks divides 4, so a slot always holds the same token chunk.
-        const int q = warp & 3;                        // TMEM lanes 32*(warp % 4) .. +31
-        const int slot = (warp - 2) >> 2;
-        const int chunk = slot % G::kChunks;
+    }
+
+    // ---------------- accumulate warps: acc[m] += s * D_superblock[m]; then the epilogue ----------------
+    if (warp >= kFirstAccWarp && warp < kActivationWarp) {
+        const int q = warp & 3;                 // a warp may only read TMEM lanes 32*(warp%4) .. +31
         const int rrow = q * 32 + lane;
         const long long row = static_cast<long long>(n0) + rrow;
-        const bool row_ok = row < p.n;
-        float acc[16];
+        float acc[NT];
 #pragma unroll
-        for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
+        for (int m = 0; m < NT; ++m) acc[m] = 0.0f;
         bool ok = true;
         for (int i = 0; i < nsb_local && ok; ++i) {
-            const float* scales = scale_ring + ((i % G::kScaleStages) * kBM + rrow) * G::kScaleRow;
-#pragma unroll
-            for (int t = 0; t < kSub; ++t) {
-                const int j = i * kSub + t;
-                const int sbuf = j % G::kStepBuffers;
-                if (!mbar_wait_bounded(&d_full[sbuf], (j / G::kStepBuffers) & 1)) {
-                    atomicExch(p.status, kDeviceWaitTimeout);
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after_sync();
-                if (warp == 2 && lane == 0) stamp(p, 2, j, 0);
-#pragma unroll
-                for (int gg = 0; gg < G::kGroupsPerStep; ++gg) {
-                    const int item = (j * G::kGroupsPerStep + gg) * G::kChunks + chunk;
-                    if ((item & (G::kAccSlots - 1)) != slot) continue;
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sbuf * G::kStepCols + gg * NT + chunk * 16;
-                    uint32_t dv[16];
-                    tmem_ld16(taddr, dv);
-                    float sv[16];
-                    if (Q::kUsesSum) {
-                        const float4* sp = reinterpret_cast<const float4*>(s_ring + (sbuf * G::kGroupsPerStep + gg) * NT + chunk * 16);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float4 f = sp[u];
-                            sv[4 * u] = f.x; sv[4 * u + 1] = f.y; sv[4 * u + 2] = f.z; sv[4 * u + 3] = f.w;
-                        }
-                    }
-                    tmem_ld_wait();
-                    const float a_g = scales[t * G::kGroupsPerStep + gg];
-                    const float c_g = Q::kStoresCoef ? -scales[Q::kGroupsPerSb + t * G::kGroupsPerStep + gg] : -160.0f * a_g;
-#pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        float v = fmaf(a_g, __uint_as_float(dv[jj]), acc[jj]);
-                        if (Q::kUsesSum) v = fmaf(c_g, sv[jj], v);
-                        acc[jj] = v;
-                    }
-                }
-                // this warp is done with the step buffer (TMEM columns and the S ring entry)
-                tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&d_empty[sbuf]);
-                if (warp == 2 && lane == 0) stamp(p, 2, j, 1);
+            const int buf = i % kAccBuffers;
+            if (!mbar_wait_bounded(&d_full[buf], (i / kAccBuffers) & 1)) {
+                atomicExch(p.status, kDeviceWaitTimeout);
+                ok = false;
             }
             ok = __all_sync(0xffffffffu, ok);
-        }
-        if (!ok) atomicExch(p.status, kDeviceWaitTimeout);
-
-        // ---------------- sum the four slots of each quadrant in a fixed order ----------------
-        // Every MMA has been consumed once all accumulate warps are here, so the A tiles are free.
-        named_barrier_sync(2, G::kAccWarps * 32);
-        float* red = reinterpret_cast<float*>(a_tiles);   // [slot][row][16]
+            if (!ok) break;
+            if (rrow == 0) stamp(p, 2, i, 0);
+            tcgen05_fence_after_sync();
+            const float s = scale_ring[buf * kBM + rrow];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NT;
 #pragma unroll
-        for (int jj = 0; jj < 16; jj += 4)
-            *reinterpret_cast<float4*>(red + (slot * kBM + rrow) * 16 + jj) = make_float4(acc[jj], acc[jj + 1], acc[jj + 2], acc[jj + 3]);
-        named_barrier_sync(2, G::kAccWarps * 32);
-        const bool owner = slot < G::kChunks;             // this thread finishes (row, token chunk `slot`)
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t v0[16], v1[16];
+                tmem_ld16(taddr + c0, v0);
+                if (NT > 16) tmem_ld16(taddr + c0 + 16, v1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) acc[c0 + jj] = fmaf(s, __uint_as_float(v0[jj]), acc[c0 + jj]);
+                if (NT > 16) {
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) acc[c0 + 16 + jj] = fmaf(s, __uint_as_float(v1[jj]), acc[c0 + 16 + jj]);
+                }
+            }
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_empty[buf]);
+            if (rrow == 0) stamp(p, 2, i, 1);
+        }
         const bool split = p.ksplit > 1;
         float* part = split ? p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n : nullptr;
-        if (owner && row_ok) {
+        if (ok && row < p.n) {
 #pragma unroll
-            for (int jj = 0; jj < 16; ++jj) {
-                float total = acc[jj];
-                for (int s2 = slot + G::kChunks; s2 < G::kAccSlots; s2 += G::kChunks) total += red[(s2 * kBM + rrow) * 16 + jj];
-                const int m = m0 + slot * 16 + jj;
+            for (int jj = 0; jj < NT; ++jj) {
+                const int m = m0 + jj;
                 if (m < p.m) {
+                    const float value = acc[jj] * __ldg(p.x_scale + m);
                     const size_t o = static_cast<size_t>(m) * p.n + row;
                     if (split) {
-                        part[o] = total;
+                        part[o] = value;
                     } else if (p.y_bf16) {
-                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(total);
+                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value);
                     } else {
-                        static_cast<float*>(p.y)[o] = total;
+                        static_cast<float*>(p.y)[o] = value;
                     }
                 }
             }
         }
-        if (split) {
-            // The CTA that draws the last ticket of its tile adds the partial tiles in K order.
+    }
+
+    // ---------------- split-K: the CTA that draws the last ticket of its tile adds the partial tiles ----------------
+    if (p.ksplit > 1 && warp >= 2 && warp < kActivationWarp) {
+        // Dequant and accumulate warps take part (all idle by now): five threads per weight row.
+        constexpr int kReducers = (kDequantWarps + kAccWarps) * 32;
+        __threadfence();
+        named_barrier_sync(2, kReducers);
+        if (threadIdx.x == 64) {
+            unsigned int* ticket = p.tickets + blockIdx.y * gridDim.x + blockIdx.x;
+            const unsigned int drawn = atomicAdd(ticket, 1u);
+            const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
+            if (last) *ticket = 0;  // ready for the next launch
+            *last_flag = last ? 1u : 0u;
+        }
+        named_barrier_sync(2, kReducers);
+        const int worker = threadIdx.x - 64;
+        const long long row = static_cast<long long>(n0) + (worker & (kBM - 1));
+        if (*last_flag != 0 && row < p.n) {
             __threadfence();
-            named_barrier_sync(2, G::kAccWarps * 32);
-            if (threadIdx.x == 64) {
-                unsigned int* ticket = p.tickets + blockIdx.y * gridDim.x + blockIdx.x;
-                const unsigned int drawn = atomicAdd(ticket, 1u);
-                const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
-                if (last) *ticket = 0;  // ready for the next launch
-                *last_flag = last ? 1u : 0u;
-            }
-            named_barrier_sync(2, G::kAccWarps * 32);
-            if (*last_flag != 0 && row_ok) {
-                __threadfence();
-                // all sixteen warps share the tile: slot s takes tokens m0 + 4s .. +3, then strides of 16
-                const size_t plane = static_cast<size_t>(p.m) * p.n;
-                const int m_end = min(m0 + NT, p.m);
-                for (int m = m0 + 4 * slot; m < m_end; m += 4 * G::kAccSlots) {
-                    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    size_t o[4];
+            const size_t plane = static_cast<size_t>(p.m) * p.n;
+            const int m_end = min(m0 + NT, p.m);
+            // Four tokens at a time, so that four independent loads per K slice are in flight;
+            // the slices are added in index order whatever the arrival order was.
+            for (int m = m0 + 4 * (worker >> 7); m < m_end; m += 4 * (kReducers / kBM)) {
+                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                size_t o[4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) o[u] = static_cast<size_t>(min(m + u, m_end - 1)) * p.n + row;
+                for (int u = 0; u < 4; ++u) o[u] = static_cast<size_t>(min(m + u, m_end - 1)) * p.n + row;
 #pragma unroll 4
-                    for (int z = 0; z < p.ksplit; ++z) {
+                for (int z = 0; z < p.ksplit; ++z) {
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) sum[u] += __ldcg(p.partial + z * plane + o[u]);
-                    }
+                    for (int u = 0; u < 4; ++u) sum[u] += __ldcg(p.partial + z * plane + o[u]);
+                }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (m + u < m_end) {
-                            if (p.y_bf16) {
-                                static_cast<__nv_bfloat16*>(p.y)[o[u]] = __float2bfloat16_rn(sum[u]);
-                            } else {
-                                static_cast<float*>(p.y)[o[u]] = sum[u];
-                            }
+                for (int u = 0; u < 4; ++u) {
+                    if (m + u < m_end) {
+                        if (p.y_bf16) {
+                            static_cast<__nv_bfloat16*>(p.y)[o[u]] = __float2bfloat16_rn(sum[u]);
+                        } else {
+                            static_cast<float*>(p.y)[o[u]] = sum[u];
                         }
                     }
                 }
@@ -702,15 +464,79 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         }
     }
 
-    // ---------------- teardown ----------------
+    // ---------------- teardown: every warp arrives here, then TMEM is released ----------------
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, G::kTmemColumns);
 }
 
+// ---------------- activation pre-pass: x (f32 or bf16) -> f16 rows with a power-of-two factor per row ----------------
+// One CTA per member row.  With norm_weight the row is RMS-normalised first (model_ops.cu rms_norm:
+// y = x * rsqrt(mean(x^2) + eps) * weight, f32 arithmetic).  The row is then multiplied by 2^-e, e chosen so
+// that its largest magnitude lands in (2^13, 2^14], and rounded to f16; factor[m] = 2^e.
+constexpr int kConvertThreads = 512;
+
+__device__ __forceinline__ float load_activation(const void* x, bool bf16, size_t i) {
+    return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]) : static_cast<const float*>(x)[i];
+}
+
+__global__ void __launch_bounds__(kConvertThreads)
+convert_activations_f16(const void* x, int x_bf16, const float* norm_weight, float eps, __half* out, float* factor, int k) {
+    __shared__ float red_sum[kConvertThreads / 32];
+    __shared__ float red_max[kConvertThreads / 32];
+    __shared__ float broadcast[2];
+    const size_t base = static_cast<size_t>(blockIdx.x) * k;
+    float sum = 0.0f, biggest = 0.0f;
+    for (int i = threadIdx.x; i < k; i += kConvertThreads) {
+        const float v = load_activation(x, x_bf16 != 0, base + i);
+        sum = fmaf(v, v, sum);
+        biggest = fmaxf(biggest, fabsf(norm_weight != nullptr ? v * norm_weight[i] : v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        red_sum[threadIdx.x >> 5] = sum;
+        red_max[threadIdx.x >> 5] = biggest;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        sum = threadIdx.x < kConvertThreads / 32 ? red_sum[threadIdx.x] : 0.0f;
+        biggest = threadIdx.x < kConvertThreads / 32 ? red_max[threadIdx.x] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+        }
+        if (threadIdx.x == 0) {
+            const float inv_rms = norm_weight != nullptr ? rsqrtf(sum / static_cast<float>(k) + eps) : 1.0f;
+            broadcast[0] = inv_rms;
+            broadcast[1] = biggest * inv_rms;
+        }
+    }
+    __syncthreads();
+    const float inv_rms = broadcast[0];
+    const float amax = broadcast[1];
+    float down = 1.0f, up = 1.0f;   // 2^-e, 2^e
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int e = static_cast<int>(__float_as_uint(amax) >> 23) - 127 + 1 - 14;   // amax * 2^-e in [2^13, 2^14)
+        e = max(-100, min(100, e));
+        down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+        up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
+    }
+    if (threadIdx.x == 0) factor[blockIdx.x] = up;
+    for (int i = threadIdx.x; i < k; i += kConvertThreads) {
+        float v = load_activation(x, x_bf16 != 0, base + i);
+        if (norm_weight != nullptr) v = v * inv_rms * norm_weight[i];
+        out[base + i] = __float2half_rn(v * down);
+    }
+}
+
 template <uint32_t FMT, int NT, bool RAWTMA>
 cudaError_t launch_tile(const TcArgs& a) {
-    using G = GsGeometry<FMT, NT, RAWTMA>;
+    using G = Geometry<FMT, NT, RAWTMA>;
     auto kernel = qgemv_tc_kernel<FMT, NT, RAWTMA>;
     static int configured_device = -1;
     int device = 0;
@@ -722,14 +548,27 @@ cudaError_t launch_tile(const TcArgs& a) {
     }
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return cudaErrorNotSupported;
+
+    // Scratch: [f16 activations][one factor per member row][split-K partial tiles].
+    const size_t x16_bytes = (static_cast<size_t>(a.m) * a.k * sizeof(__half) + 1023) & ~static_cast<size_t>(1023);
+    const size_t factor_bytes = (static_cast<size_t>(a.m) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+    if (x16_bytes + factor_bytes > a.scratch_bytes) return cudaErrorMemoryAllocation;
+    __half* x16 = static_cast<__half*>(a.scratch);
+    float* factor = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + x16_bytes);
+    float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + x16_bytes + factor_bytes);
+    const size_t partial_bytes = a.scratch_bytes - x16_bytes - factor_bytes;
+
+    convert_activations_f16<<<a.m, kConvertThreads, 0, a.stream>>>(a.x, a.x_bf16 ? 1 : 0, a.norm_weight, a.eps, x16, factor, a.k);
+    cudaError_t launched = cudaGetLastError();
+    if (launched != cudaSuccess) return launched;
+
     CUtensorMap map;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k) * 2};
     const cuuint32_t box[2] = {kBK, NT};
     const cuuint32_t elem[2] = {1, 1};
-    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x16, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     TcParams p;
     p.w = a.weights;
@@ -747,7 +586,8 @@ cudaError_t launch_tile(const TcArgs& a) {
             return cudaErrorInvalidValue;
     }
     p.y = a.y;
-    p.partial = static_cast<float*>(a.scratch);
+    p.partial = partial;
+    p.x_scale = factor;
     p.tickets = a.tickets;
     p.k = a.k;
     p.n = a.n;
@@ -758,13 +598,12 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.trace = a.trace;
     const int n_tiles = (a.n + kBM - 1) / kBM;
     const int m_tiles = (a.m + NT - 1) / NT;
-    p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, static_cast<size_t>(a.m) * a.n * sizeof(float),
-                             a.scratch_bytes, a.ticket_count);
-    if (a.force_ksplit > 0 && a.force_ksplit <= p.nsb &&
-        static_cast<size_t>(a.m) * a.n * sizeof(float) * a.force_ksplit <= a.scratch_bytes && n_tiles * m_tiles <= a.ticket_count)
+    const size_t plane_bytes = static_cast<size_t>(a.m) * a.n * sizeof(float);
+    p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, plane_bytes, partial_bytes, a.ticket_count);
+    if (a.force_ksplit > 0 && a.force_ksplit <= p.nsb && plane_bytes * a.force_ksplit <= partial_bytes && n_tiles * m_tiles <= a.ticket_count)
         p.ksplit = a.force_ksplit;
     const dim3 grid(n_tiles, m_tiles, p.ksplit);
-    kernel<<<grid, kGsThreads, G::kSmemBytes, a.stream>>>(map, wmap, p);
+    kernel<<<grid, kThreads, G::kSmemBytes, a.stream>>>(map, wmap, p);
     return cudaGetLastError();
 }
 
@@ -777,6 +616,7 @@ cudaError_t launch_tokens(const TcArgs& a) {
 
 template <uint32_t FMT>
 cudaError_t launch_format(const TcArgs& a) {
+    // The tiled box needs 16-byte aligned rows; only Q6_K rows can fail that (210-byte blocks).
     const unsigned long long row_bytes = a.value_type == kQ8_0 ? static_cast<unsigned long long>(a.k / 32) * 34
                                                                : static_cast<unsigned long long>(a.k / kSuperBlock) * Format<FMT>::kBytes;
     if (row_bytes % 16 == 0 && a.force_row_copies == 0) return launch_tokens<FMT, true>(a);
@@ -785,8 +625,8 @@ cudaError_t launch_format(const TcArgs& a) {
 
 }  // namespace
 
-// Members 1..64 (larger batches tile over blockIdx.y in steps of 64), bf16 activations, K a multiple of 256.
 cudaError_t launch_qgemv_tc(const TcArgs& a) {
+    if (a.m < 1 || a.m > 64) return cudaErrorInvalidValue;
     switch (a.value_type) {
         case kQ4_K: return launch_format<kQ4_K>(a);
         case kQ5_K: return launch_format<kQ5_K>(a);

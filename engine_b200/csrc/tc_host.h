@@ -14,6 +14,7 @@ struct TcParams {
     unsigned long long row_bytes;
     void* y;                 // [m][n] f32 or bf16
     float* partial;          // split-K scratch: [ksplit][m][n] f32
+    const float* x_scale;    // decode kernel: power-of-two factor per member row (activations were divided by it)
     unsigned int* tickets;   // one counter per (n tile, m tile), zero between launches
     int k, n, m;
     int nsb;                 // super-blocks per row

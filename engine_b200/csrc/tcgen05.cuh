@@ -53,6 +53,49 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
+// The MMAs of one 64-wide K step (four K slices of 16 elements, 32 bytes apart along the swizzled rows,
+// i.e. +2 in the descriptors' address field), issued by the elected lane of a CONVERGED warp: every lane
+// executes this, so that the operands stay warp-uniform; issued from inside a one-lane branch instead,
+// each tcgen05.mma costs its thread about twice as long (measured: ~80 cycles against ~40, and up to 125
+// when other warps keep the ALUs busy).  `accumulate_first` = 0 makes the first slice overwrite D.
+__device__ __forceinline__ void umma_f16_step4_elected(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                       uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pf, pt, pe;\n\t"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        ".reg .b32 leader;\n\t"
+        "elect.sync leader|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pf, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "add.s64 a1, %1, 2;\n\t"
+        "add.s64 a2, %1, 4;\n\t"
+        "add.s64 a3, %1, 6;\n\t"
+        "add.s64 b1, %2, 2;\n\t"
+        "add.s64 b2, %2, 4;\n\t"
+        "add.s64 b3, %2, 6;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+
+// tcgen05.commit by the elected lane of a converged warp (the lane that issued the MMAs above).
+__device__ __forceinline__ void umma_commit_elected(uint64_t* bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pe;\n\t"
+        ".reg .b32 leader;\n\t"
+        "elect.sync leader|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}" ::"r"(smem_addr(bar))
+        : "memory");
+}
+
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))

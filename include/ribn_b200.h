@@ -100,9 +100,9 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
  *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
- *   "tc_split_operands": 1 (default) = batches of up to 64 rows use the dequantised-operand GEMM (the
- *                   prefill kernel); 0 = the group-scaled decode kernel (raw quants on the tensor
- *                   cores, block scales applied from TMEM; same results within the parity bound);
+ *   "tc_f32_activations": 1 = f32 batches may use it too (they are rounded to f16; default 0);
+ *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
+ *                   kernel) instead of the f16 decode kernel (default 0);
  *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);
  *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
  *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not

@@ -268,7 +268,8 @@ def test_qwen_gemv_kernel_dispatches_on_value_type(ctx):
 
 # ---- fused RMSNorm -> GEMV: same result contract as the two calls
 @pytest.mark.parametrize("vt", [8, 12, 13, 14])
-@pytest.mark.parametrize("members,x_dtype", [(1, torch.float32), (2, torch.bfloat16), (4, torch.float32), (7, torch.float32)])
+@pytest.mark.parametrize("members,x_dtype", [(1, torch.float32), (2, torch.bfloat16), (4, torch.float32), (7, torch.float32),
+                                             (8, torch.bfloat16), (33, torch.bfloat16)])
 def test_fused_rms_norm_gemv(ctx, vt, members, x_dtype):
     k, n = 4096, 513
     w = synth.random_weight(vt, k, n, seed=vt + members)
@@ -282,6 +283,33 @@ def test_fused_rms_norm_gemv(ctx, vt, members, x_dtype):
     ctx.synchronize()
     normed = oracle.rms_norm(x.float().cpu().numpy(), gain_host, 1e-6)
     check(vt, w, k, n, y.cpu().numpy().astype(np.float64), normed)
+
+
+# ---- f32 batches reach the tensor-core kernel only on request (its operands are f16)
+@pytest.mark.parametrize("vt", [8, 12, 13, 14])
+@pytest.mark.parametrize("fused", [False, True])
+def test_f32_batches_on_the_tensor_core_kernel(ctx, vt, fused):
+    k, n, members = 2048, 300, 9
+    w = synth.random_weight(vt, k, n, seed=vt)
+    weight = upload(ctx, vt, w, k, n)
+    rng = np.random.default_rng(vt)
+    x_host = (rng.standard_normal((members, k)) * np.float32(3.0)).astype(np.float32)
+    x_host[3] *= np.float32(1e-6)     # rows far apart in magnitude: every row has its own power-of-two factor
+    x_host[5] *= np.float32(3e5)
+    gain_host = (1.0 + 0.02 * rng.standard_normal(k)).astype(np.float32)
+    x = torch.from_numpy(x_host).to(ctx.device)
+    y = torch.full((members, n), float("nan"), device=ctx.device)
+    ctx.set_option("tc_f32_activations", 1)
+    try:
+        if fused:
+            KERNELS[vt].from_context(ctx).execute_rms_norm(weight, x, torch.from_numpy(gain_host).to(ctx.device), 1e-6, y, members)
+        else:
+            KERNELS[vt].from_context(ctx).execute_warp_batch(weight, x, y, members)
+        ctx.synchronize()
+    finally:
+        ctx.set_option("tc_f32_activations", 0)
+    seen = oracle.rms_norm(x_host, gain_host, 1e-6) if fused else x_host
+    check(vt, w, k, n, y.cpu().numpy().astype(np.float64), seen)
 
 
 def test_fused_rejections(ctx):
