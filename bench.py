@@ -106,6 +106,7 @@ def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     import oracle
+    from oracle import oracle_np
     from engine_b200 import synth
 
     threads = os.cpu_count() or 1
@@ -115,7 +116,7 @@ def run_reference(args, rank: int, world: int) -> None:
         for n, k in SHAPES:
             w = synth.random_weight(vt, k, n, seed=vt * 100 + n // 1024 + k // 1024)
             for m in sample_members:
-                x = oracle.oracle_np.bf16_bits_to_f32(oracle.oracle_np.f32_to_bf16_bits(synth.random_activations(m, k, seed=m)))
+                x = oracle_np.bf16_bits_to_f32(oracle_np.f32_to_bf16_bits(synth.random_activations(m, k, seed=m)))
                 cases.append((vt, n, k, m, w, x))
     step_bytes = sum(case_bytes(vt, n, k, m) for vt, n, k, m, _, _ in cases)
 
@@ -141,6 +142,70 @@ def run_reference(args, rank: int, world: int) -> None:
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+# DRAM bytes moved per algorithmic byte by the tensor-core decode kernel, from an ncu capture of one launch
+# (dram__bytes_read.sum + dram__bytes_write.sum over the encoded weight bytes + activations + outputs;
+# the summary of that capture is committed under profiles/).  None until a capture exists.
+TC_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+
+
+def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
+    source = f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s"
+    if dominant is None:   # a run restricted to calls of 1..4 member rows
+        return {"bound": "hbm", "achieved": step_gbps, "peak": peak, "unit": "GB/s", "frac": step_gbps / peak, "traffic": None,
+                "peak_source": source, "kernel": "gemv_dp4a_kernel + activation pre-pass (all calls of the step)",
+                "bytes_per_step": step_bytes}
+    achieved, us_per_call, bytes_per_call = dominant
+    traffic = None if TC_TRAFFIC_PER_ALGORITHMIC_BYTE is None else TC_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_call
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+            "peak_source": source, "kernel": "qgemv_tc_kernel + its activation pre-pass (calls of 16 and 64 member rows)",
+            "us_per_call": us_per_call, "algorithmic_bytes_per_call": bytes_per_call,
+            "whole_step": {"achieved": step_gbps, "frac": step_gbps / peak, "bytes_per_step": step_bytes}}
+
+
+def time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, reps):
+    """GB/s of the sweep when the reference project's own GEMV kernels serve it (cubins from oracle/build_ref.py)."""
+    import torch
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        return {"unavailable": "reference cubins not built here (oracle/build_ref.py needs the reference tree)"}
+    try:
+        kernels = ref_cuda.ReferenceKernels()
+        x32 = {key: t.float() for key, t in acts.items()}
+        cursor = {key: 0 for key in rings}
+
+        def step():
+            for vt, n, k, m in cases:
+                ring = rings[(vt, n, k)]
+                weight = ring[cursor[(vt, n, k)] % len(ring)]
+                cursor[(vt, n, k)] += 1
+                kernels.gemv(vt, weight.encoded_data(), x32[(k, m)], outs[(n, m)], k, n, m)
+
+        with torch.cuda.stream(stream):
+            step()
+        torch.cuda.synchronize()
+        graph = capture(step)
+        with torch.cuda.stream(stream):
+            replay = (lambda: graph.replay()) if graph is not None else step
+            for _ in range(3):
+                replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(reps):
+                replay()
+            b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        launches = sum(ref_cuda.launches_for(m) for _, _, _, m in cases)
+        return {"value": step_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "launches_per_step": launches,
+                "kernels": "q{4,5,6}_k_gemv_warp (1 member row), q{4,5,6}_k_gemv_warp_batch (8 member rows per launch)",
+                "activations": "f32 (the reference has no bf16 input)", "cuda_graph": graph is not None,
+                "source": "the reference's .cu files compiled with nvcc for sm_100a, launched with the reference's geometry"}
+    except Exception as exc:  # the comparison is optional; the benchmark line must still be printed
+        return {"unavailable": f"{type(exc).__name__}: {exc}"}
 
 
 def cpu_baseline_leg():
@@ -171,13 +236,14 @@ def cpu_baseline_leg():
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=300)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--variant", type=int, default=0, help="GEMV tuning variant")
     parser.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                         help="library tuning option passed to ribn_set_option (measurement runs only)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
     parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
     parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
@@ -240,7 +306,9 @@ def main() -> None:
     cursor = {key: 0 for key in rings}
     cases = [(vt, n, k, m) for vt in FORMATS for n, k in SHAPES for m in MEMBERS]
     step_bytes = sum(case_bytes(*c) for c in cases)
-    launches_per_step = sum((m + 7) // 8 for _, _, _, m in cases)
+    # Every call is two launches: an activation pre-pass (int8 planes for the integer-dot GEMV of 1..4 member
+    # rows, f16 rows for the tensor-core kernel of 5..64) and the GEMV kernel itself.
+    launches_per_step = 2 * len(cases)
 
     def launch(vt, n, k, m):
         ring = rings[(vt, n, k)]
@@ -334,6 +402,39 @@ def main() -> None:
     h2d = sum(m * k * 2 for _, _, k, m in cases)
     d2h = sum(m * n * 4 for _, n, _, m in cases)
 
+    # ---- roofline of the dominant kernel: the tensor-core decode kernel (batches of 5..64 member rows) takes
+    # most of the step; its calls are timed on their own (same graph replay, same cold weight rings).
+    dominant = [c for c in cases if c[3] >= 5]
+    dominant_roofline = None
+    if dominant:
+        def dominant_step():
+            for c in dominant:
+                launch(*c)
+
+        graph = capture(dominant_step)
+        replay = (lambda: graph.replay()) if graph is not None else dominant_step
+        reps = max(3, min(args.steps, 50))
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(ctx.stream)
+            for _ in range(reps):
+                replay()
+            b.record(ctx.stream)
+        torch.cuda.synchronize()
+        dominant_ms = a.elapsed_time(b) / reps
+        dominant_bytes = sum(case_bytes(*c) for c in dominant)
+        dominant_roofline = (dominant_bytes / (dominant_ms * 1e-3) / 1e9, dominant_ms * 1e3 / len(dominant), dominant_bytes / len(dominant))
+
+    # ---- the reference's own CUDA kernels on this GPU, same sweep, same cold weight rings, same graph protocol.
+    # They take f32 activations only and at most eight member rows per launch, so 16 and 64 member rows are
+    # two and eight launches, the way the reference's prefill loop serves them.
+    reference_cuda = None
+    if rank == 0 and world == 1 and not args.no_reference_cuda:
+        reference_cuda = time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, max(3, min(args.steps, 20)))
+
     breakdown = None
     if args.cases and rank == 0:
         breakdown = {}
@@ -370,15 +471,15 @@ def main() -> None:
                        "l2": "ring of distinct weight copies > 2x L2 per (format, shape); inputs larger than L2",
                        "parallelism": "replicas" if world > 1 else "single", "gemv_variant": args.variant, "options": args.option,
                        "cuda_graph": step_graph is not None},
-            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
-                         "traffic": None, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s",
-                         "kernel": "gemv_kernel (all launches of the step)", "bytes_per_step": step_bytes},
+            "roofline": roofline(value / world, step_bytes, dominant_roofline, peak, peak_kind),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
         if breakdown is not None:
             line["cases"] = breakdown
+        if reference_cuda is not None:
+            line["reference_cuda"] = reference_cuda
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_leg()
         print(json.dumps(line))

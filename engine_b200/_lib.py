@@ -39,9 +39,31 @@ class QWeight(ctypes.Structure):
     ]
 
 
+class Attention(ctypes.Structure):
+    """struct ribn_attention"""
+
+    _fields_ = [
+        ("members", ctypes.c_uint32),
+        ("q_heads", ctypes.c_uint32),
+        ("kv_heads", ctypes.c_uint32),
+        ("head_dim", ctypes.c_uint32),
+        ("rot_dims", ctypes.c_uint32),
+        ("rope_base", ctypes.c_float),
+        ("eps", ctypes.c_float),
+        ("q_norm", ctypes.c_void_p),
+        ("k_norm", ctypes.c_void_p),
+        ("positions", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p),
+        ("v_cache", ctypes.c_void_p),
+        ("max_context", ctypes.c_uint64),
+        ("active_context", ctypes.c_uint64),
+    ]
+
+
 _u64p = ctypes.POINTER(ctypes.c_uint64)
 _vp = ctypes.c_void_p
 _qwp = ctypes.POINTER(QWeight)
+_attp = ctypes.POINTER(Attention)
 
 # name -> (restype, argtypes); one entry per declaration in include/ribn_b200.h
 SIGNATURES = {
@@ -67,6 +89,12 @@ SIGNATURES = {
                                       ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_gemv_noalloc": (ctypes.c_int, [ctypes.c_int, _vp, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_int,
                                          ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint64]),
+    "ribn_embedding": (ctypes.c_int, [_vp, _qwp, _vp, ctypes.c_uint32, _vp, ctypes.c_uint64]),
+    "ribn_qk_norm_rope_append": (ctypes.c_int, [_vp, _attp, _vp, _vp, _vp]),
+    "ribn_attention_decode": (ctypes.c_int, [_vp, _attp, _vp, _vp]),
+    "ribn_silu_mul": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64]),
+    "ribn_residual_add": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_uint64]),
+    "ribn_argmax": (ctypes.c_int, [_vp, _vp, ctypes.c_uint32, ctypes.c_uint64, _vp]),
     "ribn_rms_norm": (ctypes.c_int, [_vp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64, _vp, ctypes.c_int,
                                      ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float]),
 }

@@ -348,6 +348,48 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
 
 }  // namespace
 
+namespace {
+
+Failure validate_attention(const ribn_attention* a) {
+    if (a == nullptr) return fail(RIBN_E_INVALID_ARGUMENT, "null attention descriptor");
+    if (a->members == 0 || a->q_heads == 0 || a->kv_heads == 0)
+        return fail(RIBN_E_INPUT_LENGTH, "attention needs at least one member and one head", 1, 0);
+    if (a->head_dim != 128)
+        return fail(RIBN_E_INVALID_ARGUMENT, fmt("attention head size is %u, this build serves 128", a->head_dim));
+    if (a->q_heads % a->kv_heads != 0 || a->q_heads / a->kv_heads > 8)
+        return fail(RIBN_E_INVALID_ARGUMENT, "query heads must be 1..8 times the key/value heads");
+    if (a->rot_dims > a->head_dim || (a->rot_dims & 1u) != 0) return fail(RIBN_E_INVALID_ARGUMENT, "rotary dims must be even and at most the head size");
+    if (a->max_context == 0 || a->active_context == 0 || a->active_context > a->max_context)
+        return fail(RIBN_E_INVALID_ARGUMENT, "the active context must be 1..max_context");
+    if (a->max_context > (1ull << 31)) return fail(RIBN_E_SHAPE_OVERFLOW, "context does not fit CUDA launch arguments");
+    return Failure{};
+}
+
+ribn::LayerAttentionArgs attention_args(const ribn_ctx* ctx, const ribn_attention* a, float* q, const float* k, const float* v) {
+    ribn::LayerAttentionArgs r{};
+    r.q = q;
+    r.k = k;
+    r.v = v;
+    r.q_norm = a->q_norm;
+    r.k_norm = a->k_norm;
+    r.eps = a->eps;
+    r.positions = a->positions;
+    r.members = static_cast<int>(a->members);
+    r.q_heads = static_cast<int>(a->q_heads);
+    r.kv_heads = static_cast<int>(a->kv_heads);
+    r.head_dim = static_cast<int>(a->head_dim);
+    r.rot_dims = static_cast<int>(a->rot_dims);
+    r.rope_base = a->rope_base;
+    r.k_cache = a->k_cache;
+    r.v_cache = a->v_cache;
+    r.max_context = static_cast<long long>(a->max_context);
+    r.active_context = static_cast<long long>(a->active_context);
+    r.stream = ctx->stream;
+    return r;
+}
+
+}  // namespace
+
 extern "C" {
 
 int ribn_create(int device, void* cuda_stream, ribn_ctx** out) {
@@ -456,6 +498,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {
         ctx->tc_row_copies = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "pdl") == 0 && (value == 0 || value == 1)) {
+        ribn::pdl_switch() = static_cast<int>(value);   // process-wide
         return RIBN_OK;
     }
     if (std::strcmp(name, "tc_f32_activations") == 0 && (value == 0 || value == 1)) {
@@ -662,6 +708,114 @@ int ribn_rms_norm(ribn_ctx* ctx, const void* x_device, int x_dtype, uint64_t x_l
                                                 y_dtype == RIBN_BF16, static_cast<int>(members),
                                                 static_cast<int>(length), eps, ctx->stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "RMSNorm launch");
+    return RIBN_OK;
+}
+
+// ---------------------------------------------------------------- decoder-layer operators between the GEMVs
+
+int ribn_embedding(ribn_ctx* ctx, const ribn_qweight* weight, const uint32_t* tokens_device, uint32_t members, float* out_device,
+                   uint64_t out_len) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    uint64_t k = 0, n = 0;
+    Failure f = validate_geometry(weight, 0, &k, &n);   // [hidden, vocabulary]: one encoded row per token
+    if (f.status != RIBN_OK) return record(ctx, f);
+    if (members == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "embedding needs at least one token", 1, 0));
+    if (k % 256 != 0)
+        return record(ctx, fail(RIBN_E_INVALID_WEIGHT, "invalid quantized weight: the embedding needs a hidden size that is a multiple of 256"));
+    uint64_t expected = 0;
+    if (mul_overflows(k, members, &expected)) return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "embedding shape does not fit CUDA launch arguments"));
+    if (out_len != expected)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH, fmt("embedding output has %" PRIu64 " values, expected %" PRIu64, out_len, expected),
+                                expected, out_len));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, tokens_device, "tokens");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_embedding(static_cast<const uint8_t*>(weight->data), weight->value_type, static_cast<int>(k),
+                                                 static_cast<unsigned int>(n), tokens_device, static_cast<int>(members), out_device,
+                                                 ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "embedding launch");
+    return RIBN_OK;
+}
+
+
+int ribn_qk_norm_rope_append(ribn_ctx* ctx, const ribn_attention* attention, float* q_device, const float* k_device,
+                             const float* v_device) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    Failure f = validate_attention(attention);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, q_device, "query");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, k_device, "key");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, v_device, "value");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->positions, "positions");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->k_cache, "key cache");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->v_cache, "value cache");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_qk_norm_rope_append(attention_args(ctx, attention, q_device, k_device, v_device));
+    if (e != cudaSuccess) return record_cuda(ctx, e, "head norm / rope / cache append launch");
+    return RIBN_OK;
+}
+
+int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, float* out_device) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    Failure f = validate_attention(attention);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, q_device, "query");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->positions, "positions");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->k_cache, "key cache");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, attention->v_cache, "value cache");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const ribn::LayerAttentionArgs args = attention_args(ctx, attention, const_cast<float*>(q_device), nullptr, nullptr);
+    int splits = ribn::attention_splits(args.members, args.kv_heads, args.active_context, ctx->sm_count);
+    while (splits > 1 && ribn::attention_scratch_bytes(args.members, args.q_heads, splits) > ctx->workspace_bytes) --splits;
+    if (ribn::attention_scratch_bytes(args.members, args.q_heads, splits) > ctx->workspace_bytes)
+        return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "attention partial results do not fit the context workspace"));
+    const cudaError_t e = ribn::launch_attention_decode(args, out_device, ctx->workspace, splits);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "attention launch");
+    return RIBN_OK;
+}
+
+int ribn_silu_mul(ribn_ctx* ctx, const float* gate_device, const float* up_device, float* out_device, uint32_t members,
+                  uint64_t length, uint64_t input_row_stride) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (members == 0 || length == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "silu_mul needs at least one value", 1, 0));
+    if (input_row_stride < length) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "input rows overlap"));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, gate_device, "gate");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, up_device, "up");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_silu_mul(gate_device, up_device, out_device, members, length, input_row_stride, ctx->sm_count, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "silu_mul launch");
+    return RIBN_OK;
+}
+
+int ribn_residual_add(ribn_ctx* ctx, float* y_device, const float* x_device, uint64_t length) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (length == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "residual_add needs at least one value", 1, 0));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, y_device, "accumulator");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "addend");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_residual_add(y_device, x_device, length, ctx->sm_count, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "residual_add launch");
+    return RIBN_OK;
+}
+
+int ribn_argmax(ribn_ctx* ctx, const float* logits_device, uint32_t members, uint64_t length, uint32_t* out_device) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (members == 0 || length == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "argmax needs at least one value", 1, 0));
+    if (length > (1ull << 32)) return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "argmax indices do not fit 32 bits"));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, logits_device, "logits");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_argmax(logits_device, static_cast<int>(members), length, out_device, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "argmax launch");
     return RIBN_OK;
 }
 

@@ -122,6 +122,7 @@ gemv_kernel(const GemvParams p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -187,6 +188,7 @@ gemv_kernel(const GemvParams p) {
     }
 
     // ---------------- consumer warps ----------------
+    pdl_wait_prior();   // the activations may be the previous kernel's output (the weight stream is already running)
     const int wr = warp / WK;
     const int wk = warp % WK;
     int off_a, off_b;
@@ -358,8 +360,7 @@ cudaError_t launch_variant(const GemvArgs& a, int ctas_per_sm) {
     int grid = a.sm_count * ctas_per_sm;
     // Never more CTAs than rows: a CTA without rows would only burn a launch slot.
     if (grid > a.n) grid = a.n;
-    kernel<<<grid, G::kThreads, G::kSmemBytes, a.stream>>>(p);
-    return cudaGetLastError();
+    return launch_kernel(kernel, dim3(grid), dim3(G::kThreads), G::kSmemBytes, a.stream, p);
 }
 
 template <uint32_t FMT, int MT, typename XT>

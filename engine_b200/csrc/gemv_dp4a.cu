@@ -249,6 +249,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int stages = p.stages;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -271,12 +272,19 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
     if (warp == kConsumerWarps) {
         // ---------------- producer warp: the weight stream does not depend on the activations ----------------
         const unsigned long long safe_end = p.w_bytes & ~15ull;
-        if (lane == 0) {
-            // Packed activations of this launch's members: one bulk copy (a multiple of 576 bytes).
-            const uint32_t bytes = static_cast<uint32_t>(static_cast<unsigned long long>(min(p.members, MT)) * p.x_stride);
-            mbar_arrive_expect_tx(x_bar, bytes);
-            bulk_copy_g2s(const_cast<uint8_t*>(xs), p.xq, bytes, x_bar);
-        }
+        // The first ring-full of weight stages is requested before the packed activations: those come from the
+        // previous kernel of the stream, which this one may overlap.
+        const int prefetch = min(total, stages);
+        auto request_activations = [&]() {
+            pdl_wait_prior();
+            if (lane == 0) {
+                // Packed activations of this launch's members: one bulk copy (a multiple of 576 bytes).
+                const uint32_t bytes = static_cast<uint32_t>(static_cast<unsigned long long>(min(p.members, MT)) * p.x_stride);
+                mbar_arrive_expect_tx(x_bar, bytes);
+                bulk_copy_g2s(const_cast<uint8_t*>(xs), p.xq, bytes, x_bar);
+            }
+        };
+        if (total == 0) request_activations();
         for (int it = 0; it < total; ++it) {
             const int s = it % stages;
             const int use = it / stages;
@@ -315,6 +323,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
             } else {
                 mbar_arrive(&full[s]);
             }
+            if (it == prefetch - 1) request_activations();
         }
         return;
     }
@@ -519,9 +528,8 @@ cudaError_t launch(const GemvArgs& a, bool* handled) {
     p.status = a.device_status;
     int grid = a.sm_count * ctas;
     if (grid > a.n) grid = a.n;
-    kernel<<<grid, kThreads, smem, a.stream>>>(p);
     *handled = true;
-    return cudaGetLastError();
+    return launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, a.stream, p);
 }
 
 template <uint32_t FMT>

@@ -6,6 +6,31 @@
 
 namespace ribn {
 
+// Programmatic dependent launch.  The kernels of the GEMV path call griddepcontrol.launch_dependents at
+// their start and griddepcontrol.wait before their first access to anything an earlier kernel of the
+// stream may have written (activations, scratch) or may still read (scratch, outputs); launched with the
+// attribute below, a kernel's launch latency, prologue and weight prefetch overlap its predecessor's tail.
+// Weights are never written by a kernel, so reading them before the wait is safe.
+inline int& pdl_switch() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_switch() != 0 ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 // Device status word values written by kernels whose bounded waits ran out.
 constexpr int kDeviceOk = 0;
 constexpr int kDeviceWaitTimeout = 1;
@@ -80,6 +105,35 @@ cudaError_t launch_qgemv_tc(const TcArgs& args);
 
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);
+
+// Decoder-layer operators between the GEMVs (layer_ops.cu).  KV cache: [member][kv_head][max_context][head_dim] f16.
+struct LayerAttentionArgs {
+    float* q;                 // [members][q_heads * head_dim], rewritten in place by the norm/rope step
+    const float* k;           // [members][kv_heads * head_dim]
+    const float* v;
+    const float* q_norm;      // [head_dim] or null
+    const float* k_norm;
+    float eps;
+    const int* positions;     // device, one per member: index of the token being appended
+    int members, q_heads, kv_heads, head_dim;
+    int rot_dims;             // rotary dims per head (even, <= head_dim)
+    float rope_base;
+    void* k_cache;
+    void* v_cache;
+    long long max_context;    // tokens the cache holds per (member, head)
+    long long active_context; // upper bound on positions + 1 in this call (plans the KV splits)
+    cudaStream_t stream;
+};
+cudaError_t launch_embedding(const uint8_t* weights, uint32_t value_type, int k, unsigned int vocabulary, const uint32_t* tokens,
+                             int members, float* out, cudaStream_t stream);
+cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& args);
+int attention_splits(int members, int kv_heads, long long active_context, int sm_count);
+size_t attention_scratch_bytes(int members, int q_heads, int splits);
+cudaError_t launch_attention_decode(const LayerAttentionArgs& args, float* out, void* scratch, int splits);
+cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t members, uint64_t length, uint64_t in_stride,
+                            int sm_count, cudaStream_t stream);
+cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream);
+cudaError_t launch_argmax(const float* logits, int members, uint64_t length, uint32_t* out, cudaStream_t stream);
 
 cudaError_t launch_rms_norm(const void* x, bool x_bf16, const float* weight, void* y, bool y_bf16, int members,
                             int length, float eps, cudaStream_t stream);

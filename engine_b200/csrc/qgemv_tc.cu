@@ -56,9 +56,10 @@ constexpr int kSub = kSuperBlock / kBK;  // steps per super-block
 constexpr int kSlots = 4;                // K steps being dequantised at once
 constexpr int kDequantWarps = 4 * kSlots;
 constexpr int kFirstAccWarp = 2 + kDequantWarps;
-constexpr int kAccWarps = 4;
-constexpr int kActivationWarp = kFirstAccWarp + kAccWarps;
-constexpr int kThreads = (kActivationWarp + 1) * 32;
+// Accumulate warps: one per TMEM lane quadrant, two for 64 tokens (32 accumulators per thread either way).
+constexpr int acc_warps(int nt) { return nt >= 64 ? 8 : 4; }
+constexpr int activation_warp(int nt) { return kFirstAccWarp + acc_warps(nt); }
+constexpr int threads(int nt) { return (activation_warp(nt) + 1) * 32; }
 constexpr int kAccBuffers = 4;           // super-blocks whose products may wait in TMEM
 static_assert(kSlots == kSub, "slot s owns K step s of every super-block");
 
@@ -66,6 +67,15 @@ static_assert(kSlots == kSub, "slot s owns K step s of every super-block");
 __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int event) {
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && step < 64)
         p.trace[(role * 64 + step) * 8 + event] = clock64();
+}
+
+// Wall-clock stamps (ns) of one CTA's phases: trace[(3 * 64 + 63) * 8 + event], CTA (0,0,0).
+__device__ __forceinline__ void wall_stamp(const TcParams& p, int event) {
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace[(3 * 64 + 63) * 8 + event] = static_cast<long long>(t);
+    }
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>
@@ -110,11 +120,14 @@ __device__ __forceinline__ void normaliser(float bound, float& inverse, float& s
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads(NT), 1)
 qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     using G = Geometry<FMT, NT, RAWTMA>;
     using F = Format<FMT>;
     using R = RowDequant<FMT, SingleF16>;
+    constexpr int kAccWarps = acc_warps(NT);
+    constexpr int kActivationWarp = activation_warp(NT);
+    constexpr int kAccColumns = NT / (kAccWarps / 4);   // tokens per accumulate thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint8_t* a_tiles = smem;
@@ -139,6 +152,8 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     const int sb_end = static_cast<int>(static_cast<long long>(p.nsb) * (blockIdx.z + 1) / p.ksplit);
     const int nsb_local = sb_end - sb_begin;
     const int steps = nsb_local * kSub;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) wall_stamp(p, 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < G::kRawStages; ++s) {
@@ -162,6 +177,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    if (threadIdx.x == 0) wall_stamp(p, 1);
 
     if (warp == 0) {
         // ---------------- raw weight bytes ----------------
@@ -221,6 +237,10 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         }
     } else if (warp == kActivationWarp) {
         // ---------------- activation tiles ----------------
+        // The f16 activations come from the pre-pass, the kernel before this one in the stream; the raw weight
+        // stream and the dequantisation run ahead of this wait.
+        pdl_wait_prior();
+        if (lane == 0) wall_stamp(p, 2);
         if (lane == 0) {
             for (int j = 0; j < steps; ++j) {
                 const int as = j % G::kStages;
@@ -253,6 +273,8 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&g_full[g], (gi / G::kGroups) & 1));
             if (!ok) break;
             if (lane == 0) stamp(p, 0, gi, 0);
+            if (lane == 0 && gi == 0) wall_stamp(p, 3);
+            if (lane == 0 && gi == groups - 1) wall_stamp(p, 4);
             __syncwarp();
             tcgen05_fence_after_sync();
 #pragma unroll
@@ -361,11 +383,12 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     // ---------------- accumulate warps: acc[m] += s * D_superblock[m]; then the epilogue ----------------
     if (warp >= kFirstAccWarp && warp < kActivationWarp) {
         const int q = warp & 3;                 // a warp may only read TMEM lanes 32*(warp%4) .. +31
+        const int half = (warp - kFirstAccWarp) >> 2;   // which kAccColumns tokens of the tile
         const int rrow = q * 32 + lane;
-        const long long row = static_cast<long long>(n0) + rrow;
-        float acc[NT];
+        const int col0 = half * kAccColumns;
+        float acc[kAccColumns];
 #pragma unroll
-        for (int m = 0; m < NT; ++m) acc[m] = 0.0f;
+        for (int m = 0; m < kAccColumns; ++m) acc[m] = 0.0f;
         bool ok = true;
         for (int i = 0; i < nsb_local && ok; ++i) {
             const int buf = i % kAccBuffers;
@@ -375,44 +398,56 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (rrow == 0) stamp(p, 2, i, 0);
+            if (rrow == 0 && half == 0) stamp(p, 2, i, 0);
             tcgen05_fence_after_sync();
             const float s = scale_ring[buf * kBM + rrow];
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NT;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NT + col0;
+            uint32_t v0[16], v1[16];
+            tmem_ld16(taddr, v0);
+            if (kAccColumns > 16) tmem_ld16(taddr + 16, v1);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t v0[16], v1[16];
-                tmem_ld16(taddr + c0, v0);
-                if (NT > 16) tmem_ld16(taddr + c0 + 16, v1);
-                tmem_ld_wait();
+            for (int jj = 0; jj < 16; ++jj) acc[jj] = fmaf(s, __uint_as_float(v0[jj]), acc[jj]);
+            if (kAccColumns > 16) {
 #pragma unroll
-                for (int jj = 0; jj < 16; ++jj) acc[c0 + jj] = fmaf(s, __uint_as_float(v0[jj]), acc[c0 + jj]);
-                if (NT > 16) {
-#pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) acc[c0 + 16 + jj] = fmaf(s, __uint_as_float(v1[jj]), acc[c0 + 16 + jj]);
-                }
+                for (int jj = 0; jj < 16; ++jj) acc[16 + jj] = fmaf(s, __uint_as_float(v1[jj]), acc[16 + jj]);
             }
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&d_empty[buf]);
-            if (rrow == 0) stamp(p, 2, i, 1);
+            if (rrow == 0 && half == 0) stamp(p, 2, i, 1);
         }
+        if (rrow == 0 && half == 0) wall_stamp(p, 5);
+        pdl_wait_prior();   // the per-row factors are the pre-pass's too (long done by now: the MMAs needed its tiles)
+        // The scaled tile goes through shared memory (the A tiles are free by now: every MMA has completed), so
+        // that all worker warps can store it: one thread per row storing its tokens one after the other
+        // took several microseconds.  Lane l fetches the factor of token col0 + l.
+        const float factor_lane = (lane < kAccColumns && m0 + col0 + lane < p.m) ? __ldg(p.x_scale + m0 + col0 + lane) : 0.0f;
+        float* tile = reinterpret_cast<float*>(a_tiles);   // [NT][kBM]
+#pragma unroll
+        for (int jj = 0; jj < kAccColumns; ++jj) {
+            const float factor = __shfl_sync(0xffffffffu, factor_lane, jj);
+            tile[(col0 + jj) * kBM + rrow] = ok ? acc[jj] * factor : 0.0f;
+        }
+    }
+    if (warp >= 2 && warp < kActivationWarp) {
+        constexpr int kWriters = (kDequantWarps + kAccWarps) * 32;
+        named_barrier_sync(3, kWriters);
+        const float* tile = reinterpret_cast<const float*>(a_tiles);
         const bool split = p.ksplit > 1;
         float* part = split ? p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n : nullptr;
-        if (ok && row < p.n) {
-#pragma unroll
-            for (int jj = 0; jj < NT; ++jj) {
-                const int m = m0 + jj;
-                if (m < p.m) {
-                    const float value = acc[jj] * __ldg(p.x_scale + m);
-                    const size_t o = static_cast<size_t>(m) * p.n + row;
-                    if (split) {
-                        part[o] = value;
-                    } else if (p.y_bf16) {
-                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value);
-                    } else {
-                        static_cast<float*>(p.y)[o] = value;
-                    }
+        for (int idx = threadIdx.x - 64; idx < NT * kBM; idx += kWriters) {
+            const int m = m0 + (idx >> 7);
+            const long long row = static_cast<long long>(n0) + (idx & (kBM - 1));
+            if (m < p.m && row < p.n) {
+                const float value = tile[idx];
+                const size_t o = static_cast<size_t>(m) * p.n + row;
+                if (split) {
+                    part[o] = value;
+                } else if (p.y_bf16) {
+                    static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value);
+                } else {
+                    static_cast<float*>(p.y)[o] = value;
                 }
             }
         }
@@ -467,6 +502,7 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     // ---------------- teardown: every warp arrives here, then TMEM is released ----------------
     tcgen05_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) wall_stamp(p, 6);
     if (warp == 1) tmem_dealloc(tmem_base, G::kTmemColumns);
 }
 
@@ -482,6 +518,8 @@ __device__ __forceinline__ float load_activation(const void* x, bool bf16, size_
 
 __global__ void __launch_bounds__(kConvertThreads)
 convert_activations_f16(const void* x, int x_bf16, const float* norm_weight, float eps, __half* out, float* factor, int k) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // x may be the previous kernel's output; `out` may still be read by it
     __shared__ float red_sum[kConvertThreads / 32];
     __shared__ float red_max[kConvertThreads / 32];
     __shared__ float broadcast[2];
@@ -558,8 +596,15 @@ cudaError_t launch_tile(const TcArgs& a) {
     float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + x16_bytes + factor_bytes);
     const size_t partial_bytes = a.scratch_bytes - x16_bytes - factor_bytes;
 
-    convert_activations_f16<<<a.m, kConvertThreads, 0, a.stream>>>(a.x, a.x_bf16 ? 1 : 0, a.norm_weight, a.eps, x16, factor, a.k);
-    cudaError_t launched = cudaGetLastError();
+    static int prepass_device = -1;
+    if (prepass_device != device) {
+        // Same shared-memory carve-out as the main kernel, so that the two can follow each other on an SM
+        // without a reconfiguration in between.
+        cudaFuncSetAttribute(convert_activations_f16, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        prepass_device = device;
+    }
+    cudaError_t launched = launch_kernel(convert_activations_f16, dim3(a.m), dim3(kConvertThreads), 0, a.stream, a.x, a.x_bf16 ? 1 : 0,
+                                         a.norm_weight, a.eps, x16, factor, a.k);
     if (launched != cudaSuccess) return launched;
 
     CUtensorMap map;
@@ -603,8 +648,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     if (a.force_ksplit > 0 && a.force_ksplit <= p.nsb && plane_bytes * a.force_ksplit <= partial_bytes && n_tiles * m_tiles <= a.ticket_count)
         p.ksplit = a.force_ksplit;
     const dim3 grid(n_tiles, m_tiles, p.ksplit);
-    kernel<<<grid, kThreads, G::kSmemBytes, a.stream>>>(map, wmap, p);
-    return cudaGetLastError();
+    return launch_kernel(kernel, grid, dim3(threads(NT)), G::kSmemBytes, a.stream, map, wmap, p);
 }
 
 template <uint32_t FMT, bool RAWTMA>

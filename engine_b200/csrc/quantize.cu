@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 
 #include "internal.h"
+#include "pipeline.cuh"
 
 namespace ribn {
 namespace {
@@ -55,6 +56,8 @@ __global__ void __launch_bounds__(kPackThreads) quantize_activations_kernel(cons
                                                                             const float* __restrict__ norm_weight, float eps,
                                                                             uint8_t* __restrict__ packed, int k, int kpad) {
     __shared__ float partial[kPackThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait_prior();   // x may be the previous kernel's output; the packed rows may still be read by it
     const XT* xr = x + static_cast<size_t>(blockIdx.x) * k;
     uint8_t* out = packed + static_cast<size_t>(blockIdx.x) * packed_activation_stride(kpad);
     int8_t* q1 = reinterpret_cast<int8_t*>(out);
@@ -136,12 +139,10 @@ template <typename XT>
 cudaError_t launch(const void* x, const float* norm_weight, float eps, void* packed, int members, int k, int kpad,
                    cudaStream_t stream) {
     if (norm_weight != nullptr)
-        quantize_activations_kernel<XT, true><<<members, kPackThreads, 0, stream>>>(
-            static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
-    else
-        quantize_activations_kernel<XT, false><<<members, kPackThreads, 0, stream>>>(
-            static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
-    return cudaGetLastError();
+        return launch_kernel(quantize_activations_kernel<XT, true>, dim3(members), dim3(kPackThreads), 0, stream,
+                             static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
+    return launch_kernel(quantize_activations_kernel<XT, false>, dim3(members), dim3(kPackThreads), 0, stream,
+                         static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
 }
 
 }  // namespace

@@ -1,0 +1,283 @@
+"""Decode loop of a dense grouped-query-attention transformer over the C ABI.
+
+Host-side mirror of the reference's `CudaQwen35Decode::run_step` / `full_attention_layer` /
+`run_output_head` (crates/nvidia/src/decode.rs:544-632, :929-1052, :678-696) and their batch twins
+(`run_step_batch`, :1990-2140), restricted to dense-attention layers: the order of launches is the
+reference's (norm, q/k/v projections, head norms, rope, cache append, attention, output projection,
+residual, norm, gate/up, silu_mul, down, residual; final norm, output head, argmax), every launch goes
+through libribn_b200.so, and torch only owns device memory, the stream, the CUDA graph and -- for
+tensor-parallel runs -- the NCCL process group.
+
+Tensor parallelism (the reference has none): q/k/v/gate/up and the output head are split by output rows,
+attention runs on the local heads, o_proj and ffn_down are split by input columns and followed by an
+all-reduce (sum) of the partial [members][hidden] outputs; norms and the embedding are replicated.
+See sharding.py for the shard arithmetic.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib, synth
+from .quantized import CudaQuantizedWeight, QwenGemvKernel, RibnContext, WeightTensorSpec
+from .sharding import split_even
+
+Q4_K, Q6_K = 12, 14
+
+
+@dataclass(frozen=True)
+class DenseGeometry:
+    hidden: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocabulary: int
+    rope_base: float = 1.0e6
+    eps: float = 1.0e-6
+
+    @staticmethod
+    def qwen3_8b(layers: int = 36) -> "DenseGeometry":
+        return DenseGeometry(4096, layers, 32, 8, 128, 12288, 151936)
+
+    @staticmethod
+    def qwen3_32b(layers: int = 64) -> "DenseGeometry":
+        return DenseGeometry(5120, layers, 64, 8, 128, 25600, 151936)
+
+
+# The Q4_K_M mix named by the benchmark configuration: attn_v, ffn_down and the output head in Q6_K,
+# every other matrix in Q4_K.
+VALUE_TYPES = {"attn_q": Q4_K, "attn_k": Q4_K, "attn_v": Q6_K, "attn_output": Q4_K, "ffn_gate": Q4_K, "ffn_up": Q4_K,
+               "ffn_down": Q6_K, "token_embd": Q4_K, "output": Q6_K}
+
+
+class CudaDenseOps:
+    """The layer operators between the GEMVs (CudaQwen35Ops of model_ops.rs, CudaQ4KEmbedding of quantized.rs:913-1161)."""
+
+    def __init__(self, context: RibnContext):
+        self.context = context
+        self._lib = context._lib
+
+    def embedding(self, weight: CudaQuantizedWeight, tokens: torch.Tensor, output: torch.Tensor) -> None:
+        descriptor = weight.descriptor()
+        self.context.check(self._lib.ribn_embedding(self.context.handle, ctypes.byref(descriptor), tokens.data_ptr(), tokens.numel(),
+                                                    output.data_ptr(), output.numel()))
+
+    def qk_norm_rope_append(self, attention: "_lib.Attention", q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        self.context.check(self._lib.ribn_qk_norm_rope_append(self.context.handle, ctypes.byref(attention), q.data_ptr(), k.data_ptr(),
+                                                              v.data_ptr()))
+
+    def attention_decode(self, attention: "_lib.Attention", q: torch.Tensor, output: torch.Tensor) -> None:
+        self.context.check(self._lib.ribn_attention_decode(self.context.handle, ctypes.byref(attention), q.data_ptr(), output.data_ptr()))
+
+    def silu_mul(self, gate: torch.Tensor, up: torch.Tensor, output: torch.Tensor, members: int, length: int, input_row_stride: int) -> None:
+        self.context.check(self._lib.ribn_silu_mul(self.context.handle, gate.data_ptr(), up.data_ptr(), output.data_ptr(), members, length,
+                                                   input_row_stride))
+
+    def residual_add(self, accumulator: torch.Tensor, addend: torch.Tensor) -> None:
+        self.context.check(self._lib.ribn_residual_add(self.context.handle, accumulator.data_ptr(), addend.data_ptr(), accumulator.numel()))
+
+    def argmax(self, logits: torch.Tensor, members: int, output: torch.Tensor) -> None:
+        self.context.check(self._lib.ribn_argmax(self.context.handle, logits.data_ptr(), members, logits.numel() // members, output.data_ptr()))
+
+
+def attention_descriptor(geometry: DenseGeometry, members: int, q_heads: int, kv_heads: int, q_norm, k_norm, positions, k_cache, v_cache,
+                         max_context: int, active_context: int) -> "_lib.Attention":
+    return _lib.Attention(members, q_heads, kv_heads, geometry.head_dim, geometry.head_dim, geometry.rope_base, geometry.eps,
+                          q_norm.data_ptr() if q_norm is not None else None, k_norm.data_ptr() if k_norm is not None else None,
+                          positions.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), max_context, active_context)
+
+
+class DenseWeights:
+    """Encoded matrices and f32 norm vectors of this rank's shard, on the device."""
+
+    def __init__(self):
+        self.matrices: dict[str, CudaQuantizedWeight] = {}
+        self.vectors: dict[str, torch.Tensor] = {}
+
+    def bytes_per_step(self) -> int:
+        """Encoded weight bytes one decode step streams: every matrix once, except the embedding (one row per member)."""
+        return sum(w.encoded_bytes() for name, w in self.matrices.items() if name != "token_embd")
+
+
+def local_shapes(geometry: DenseGeometry, world: int, rank: int) -> dict:
+    """[K, N] of each matrix on `rank`: output-row splits on whole heads, input-column splits on whole super-blocks."""
+    d = geometry.head_dim
+    if geometry.kv_heads % world or geometry.q_heads % world:
+        raise ValueError(f"{world} ranks do not divide {geometry.q_heads} query / {geometry.kv_heads} key-value heads")
+    q0, q1 = split_even(geometry.q_heads, world, rank)
+    kv0, kv1 = split_even(geometry.kv_heads, world, rank)
+    i0, i1 = split_even(geometry.intermediate // 256, world, rank)   # whole super-blocks; shares may differ by one
+    v0, v1 = split_even(geometry.vocabulary, world, rank)
+    local_q, local_kv, local_inter = (q1 - q0) * d, (kv1 - kv0) * d, (i1 - i0) * 256
+    return {
+        "q_heads": q1 - q0, "kv_heads": kv1 - kv0, "intermediate": local_inter, "vocab_begin": v0, "vocab_end": v1,
+        "attn_q": (geometry.hidden, local_q), "attn_k": (geometry.hidden, local_kv), "attn_v": (geometry.hidden, local_kv),
+        "attn_output": (local_q, geometry.hidden), "ffn_gate": (geometry.hidden, local_inter), "ffn_up": (geometry.hidden, local_inter),
+        "ffn_down": (local_inter, geometry.hidden), "token_embd": (geometry.hidden, geometry.vocabulary),
+        "output": (geometry.hidden, v1 - v0),
+    }
+
+
+def random_weights(context: RibnContext, geometry: DenseGeometry, seed: int = 0, world: int = 1, rank: int = 0) -> DenseWeights:
+    """Random-init shard generated on the device (no checkpoint exists for the benchmark configurations):
+    block scales and quants as the synthetic GEMV weights, norm vectors 1 + N(0, 0.02)."""
+    shapes = local_shapes(geometry, world, rank)
+    weights = DenseWeights()
+    generator = torch.Generator(device=context.device)
+    generator.manual_seed(seed)
+
+    def matrix(name: str, kind: str, salt: int) -> None:
+        k, n = shapes[kind]
+        vt = VALUE_TYPES[kind]
+        shard = 0 if kind == "token_embd" else rank   # the embedding is replicated: every rank generates the same bytes
+        data = synth.random_weight_device(vt, k, n, seed=(seed * 7919 + salt * 104729 + shard * 15485863) & 0x7FFFFFFF, device=context.device)
+        weights.matrices[name] = CudaQuantizedWeight(WeightTensorSpec.new(name, [k, n]), vt, data)
+
+    def vector(name: str, length: int) -> None:
+        weights.vectors[name] = (1.0 + 0.02 * torch.randn(length, device=context.device, generator=generator)).float()
+
+    matrix("token_embd", "token_embd", 1)
+    matrix("output", "output", 2)
+    vector("output_norm", geometry.hidden)
+    for i in range(geometry.layers):
+        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")):
+            matrix(f"blk.{i}.{kind}", kind, 10 + i * 8 + j)
+        vector(f"blk.{i}.attn_norm", geometry.hidden)
+        vector(f"blk.{i}.ffn_norm", geometry.hidden)
+        vector(f"blk.{i}.attn_q_norm", geometry.head_dim)
+        vector(f"blk.{i}.attn_k_norm", geometry.head_dim)
+    return weights
+
+
+class CudaDenseDecode:
+    """One decode step for `members` sequences (one new token each), replayable as a CUDA graph.
+
+    `process_group` (a torch.distributed NCCL group) makes it one rank of a tensor-parallel run; weights
+    must then be that rank's shard (see local_shapes)."""
+
+    def __init__(self, context: RibnContext, geometry: DenseGeometry, weights: DenseWeights, members: int, max_context: int,
+                 process_group=None, world: int = 1, rank: int = 0):
+        self.context, self.geometry, self.weights, self.members, self.max_context = context, geometry, weights, members, max_context
+        self.group, self.world, self.rank = process_group, world, rank
+        self.shapes = local_shapes(geometry, world, rank)
+        self.ops = CudaDenseOps(context)
+        self.kernels = {vt: QwenGemvKernel.from_value_type(vt, context) for vt in (Q4_K, Q6_K)}
+        dev, g, s, m = context.device, geometry, self.shapes, members
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.tokens = torch.zeros(m, dtype=torch.int32, device=dev)       # u32 on the device side
+        self.positions = torch.zeros(m, dtype=torch.int32, device=dev)
+        self.hidden = torch.zeros(m, g.hidden, **f32)
+        self.q = torch.zeros(m, s["q_heads"] * g.head_dim, **f32)
+        self.k = torch.zeros(m, s["kv_heads"] * g.head_dim, **f32)
+        self.v = torch.zeros(m, s["kv_heads"] * g.head_dim, **f32)
+        self.attended = torch.zeros(m, s["q_heads"] * g.head_dim, **f32)
+        self.projected = torch.zeros(m, g.hidden, **f32)
+        self.gate = torch.zeros(m, s["intermediate"], **f32)
+        self.up = torch.zeros(m, s["intermediate"], **f32)
+        self.activated = torch.zeros(m, s["intermediate"], **f32)
+        self.logits = torch.zeros(m, s["vocab_end"] - s["vocab_begin"], **f32)
+        self.next_tokens = torch.zeros(m, dtype=torch.int32, device=dev)
+        cache_shape = (g.layers, m, s["kv_heads"], max_context, g.head_dim)
+        self.k_cache = torch.zeros(cache_shape, dtype=torch.float16, device=dev)
+        self.v_cache = torch.zeros(cache_shape, dtype=torch.float16, device=dev)
+        self.active_context = max_context
+        self.graph = None
+        self.launches_per_step = 0
+        if members > 4:
+            # Batches go to the tensor-core kernel, which rounds the f32 activations to f16 (inside the 2e-3 bound).
+            context.set_option("tc_f32_activations", 1)
+
+    # -- building blocks -------------------------------------------------------------------------
+    def _gemv(self, name: str, x: torch.Tensor, y: torch.Tensor, norm: torch.Tensor | None = None) -> None:
+        weight = self.weights.matrices[name]
+        kernel = self.kernels[weight.value_type()].inner
+        if norm is not None:
+            kernel.execute_rms_norm(weight, x, norm, self.geometry.eps, y, self.members)
+        elif self.members == 1:
+            kernel.execute_warp(weight, x.reshape(-1), y.reshape(-1))
+        else:
+            kernel.execute_warp_batch(weight, x, y, self.members)
+        self.launches_per_step += 2
+
+    def _all_reduce(self, t: torch.Tensor) -> None:
+        if self.group is not None and self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+            self.launches_per_step += 1
+
+    def _layer(self, i: int) -> None:
+        g, s, w = self.geometry, self.shapes, self.weights
+        self._gemv(f"blk.{i}.attn_q", self.hidden, self.q, w.vectors[f"blk.{i}.attn_norm"])
+        self._gemv(f"blk.{i}.attn_k", self.hidden, self.k, w.vectors[f"blk.{i}.attn_norm"])
+        self._gemv(f"blk.{i}.attn_v", self.hidden, self.v, w.vectors[f"blk.{i}.attn_norm"])
+        attention = attention_descriptor(g, self.members, s["q_heads"], s["kv_heads"], w.vectors[f"blk.{i}.attn_q_norm"],
+                                         w.vectors[f"blk.{i}.attn_k_norm"], self.positions, self.k_cache[i], self.v_cache[i],
+                                         self.max_context, self.active_context)
+        self.ops.qk_norm_rope_append(attention, self.q, self.k, self.v)
+        self.ops.attention_decode(attention, self.q, self.attended)
+        self._gemv(f"blk.{i}.attn_output", self.attended, self.projected)
+        self._all_reduce(self.projected)
+        self.ops.residual_add(self.hidden, self.projected)
+        self._gemv(f"blk.{i}.ffn_gate", self.hidden, self.gate, w.vectors[f"blk.{i}.ffn_norm"])
+        self._gemv(f"blk.{i}.ffn_up", self.hidden, self.up, w.vectors[f"blk.{i}.ffn_norm"])
+        self.ops.silu_mul(self.gate, self.up, self.activated, self.members, s["intermediate"], s["intermediate"])
+        self._gemv(f"blk.{i}.ffn_down", self.activated, self.projected)
+        self._all_reduce(self.projected)
+        self.ops.residual_add(self.hidden, self.projected)
+        self.launches_per_step += 6
+
+    def _forward(self) -> None:
+        self.launches_per_step = 0
+        self.ops.embedding(self.weights.matrices["token_embd"], self.tokens, self.hidden)
+        for i in range(self.geometry.layers):
+            self._layer(i)
+        self._gemv("output", self.hidden, self.logits, self.weights.vectors["output_norm"])
+        self.launches_per_step += 1
+        if self.world == 1:
+            self.ops.argmax(self.logits, self.members, self.next_tokens)
+            self.launches_per_step += 1
+
+    def _select_tokens_tensor_parallel(self) -> None:
+        """Each rank holds a slice of the logits: local argmax, then the best (value, index) over the ranks."""
+        local = torch.empty(self.members, dtype=torch.int32, device=self.context.device)
+        self.ops.argmax(self.logits, self.members, local)
+        values = self.logits.gather(1, local.long().unsqueeze(1)).squeeze(1)
+        gathered_values = [torch.empty_like(values) for _ in range(self.world)]
+        gathered_indices = [torch.empty_like(local) for _ in range(self.world)]
+        torch.distributed.all_gather(gathered_values, values, group=self.group)
+        torch.distributed.all_gather(gathered_indices, local + self.shapes["vocab_begin"], group=self.group)
+        all_values = torch.stack(gathered_values)            # [world][members]
+        best = all_values.argmax(dim=0)                        # first rank wins ties: the lowest index
+        self.next_tokens.copy_(torch.stack(gathered_indices).gather(0, best.unsqueeze(0)).squeeze(0))
+
+    # -- public ------------------------------------------------------------------------------------
+    def run_step(self) -> None:
+        """tokens, positions -> next_tokens (all device resident); appends to the KV cache at `positions`."""
+        with torch.cuda.stream(self.context.stream):
+            self._forward()
+            if self.world > 1:
+                self._select_tokens_tensor_parallel()
+
+    def capture(self) -> None:
+        """Record run_step into a CUDA graph (positions and tokens are read from device memory at replay)."""
+        self.run_step()   # first launches set kernel attributes, which a capture must not contain
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=self.context.stream):
+            self._forward()
+            if self.world > 1:
+                self._select_tokens_tensor_parallel()
+        self.graph = graph
+
+    def replay(self) -> None:
+        with torch.cuda.stream(self.context.stream):
+            self.graph.replay()
+
+    def advance(self) -> None:
+        """Feed the chosen tokens back and move every sequence one position on (device-side, graph-safe)."""
+        with torch.cuda.stream(self.context.stream):
+            self.tokens.copy_(self.next_tokens)
+            self.positions.add_(1)

@@ -103,6 +103,8 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "tc_f32_activations": 1 = f32 batches may use it too (they are rounded to f16; default 0);
  *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
  *                   kernel) instead of the f16 decode kernel (default 0);
+ *   "pdl":          0 = launch the GEMV kernels without programmatic dependent launch (process-wide; default 1:
+ *                   a kernel's prologue and weight prefetch overlap the tail of the kernel before it);
  *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);
  *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
  *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not
@@ -212,6 +214,59 @@ int ribn_gemv_noalloc(int device, void *cuda_stream, const ribn_qweight *weight,
                       const void *x_device, int x_dtype, uint64_t x_len,
                       void *y_device, int y_dtype, uint64_t y_len, uint32_t members, int wait,
                       char *error_message, uint64_t error_capacity);
+
+/* ---- decoder-layer operators between the GEMVs -------------------------------------------
+ * The launches crates/nvidia/src/decode.rs:929-1052 (full_attention_layer) and :544-632 (run_step) make
+ * between its projections, for a dense-attention layer with grouped-query attention.  All buffers are
+ * f32 device memory except the KV cache (f16) and token / position arrays (32-bit). */
+
+/* ribn_embedding: CudaQ4KEmbedding::execute / execute_batch (quantized.rs:961, :1058 over
+ * q4_k.cu:1-67) for any of the four block formats.  weight dims are [hidden, vocabulary]; row `token`
+ * is dequantised into out[member][hidden].  A token >= vocabulary leaves its row untouched, as in the
+ * reference kernel. */
+int ribn_embedding(ribn_ctx* ctx, const ribn_qweight* weight, const uint32_t* tokens_device, uint32_t members,
+                   float* out_device, uint64_t out_len);
+
+/* Geometry and buffers of the attention step of one layer.  KV cache layout:
+ * [members][kv_heads][max_context][head_dim] f16 (the reference keeps [token][kv_head][dim]). */
+typedef struct ribn_attention {
+    uint32_t members;          /* sequences decoded together, one new token each */
+    uint32_t q_heads;
+    uint32_t kv_heads;         /* q_heads / kv_heads in 1..8 */
+    uint32_t head_dim;         /* 128 */
+    uint32_t rot_dims;         /* rotary dims per head: pairs (p, p + rot_dims/2), the rest passes through */
+    float rope_base;
+    float eps;                 /* of the per-head RMSNorm */
+    const float* q_norm;       /* [head_dim] raw weights, or NULL for no query norm */
+    const float* k_norm;
+    const int32_t* positions;  /* device, [members]: index of the token being appended */
+    void* k_cache;
+    void* v_cache;
+    uint64_t max_context;      /* tokens the cache holds per (member, head) */
+    uint64_t active_context;   /* upper bound of positions[m] + 1 in this call; plans the split of the KV range */
+} ribn_attention;
+
+/* strided_rms_norm (model_ops.rs:660-684) on the query and key heads, rope_neox (:393-422) on both, and
+ * kv_append_f16 (:1256-1275) of the rotated keys and the values, in one launch.  q is rewritten in place. */
+int ribn_qk_norm_rope_append(ribn_ctx* ctx, const ribn_attention* attention, float* q_device, const float* k_device,
+                             const float* v_device);
+
+/* attn_score_gqa (model_ops.rs:439-562) without its output gate: softmax(q.K / sqrt(head_dim)).V over tokens
+ * 0..positions[m] of every member, f32 accumulation; out is [members][q_heads * head_dim].  The KV range is
+ * split over CTAs and merged (partials in the context workspace). */
+int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, float* out_device);
+
+/* silu_mul (model_ops.rs:316-328): out[m][i] = silu(gate[m][i]) * up[m][i].  gate and up rows are
+ * input_row_stride floats apart (so they can be the halves of one [members][2 * length] GEMV output). */
+int ribn_silu_mul(ribn_ctx* ctx, const float* gate_device, const float* up_device, float* out_device, uint32_t members,
+                  uint64_t length, uint64_t input_row_stride);
+
+/* residual_add (model_ops.rs:600-610): y[i] += x[i]. */
+int ribn_residual_add(ribn_ctx* ctx, float* y_device, const float* x_device, uint64_t length);
+
+/* argmax / argmax_batch (model_ops.rs:201-314): index of the largest logit per member; NaN never wins,
+ * ties go to the lowest index. */
+int ribn_argmax(ribn_ctx* ctx, const float* logits_device, uint32_t members, uint64_t length, uint32_t* out_device);
 
 #ifdef __cplusplus
 }

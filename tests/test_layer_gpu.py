@@ -1,0 +1,212 @@
+"""The decoder-layer operators between the GEMVs, and the decode loop built from them, against the CPU
+restatement of the reference's host model (oracle/layer_np.py)."""
+import numpy as np
+import pytest
+import torch
+
+import engine_b200
+import oracle
+from engine_b200 import _lib, decode, synth
+from oracle import layer_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def ops(ctx):
+    return decode.CudaDenseOps(ctx)
+
+
+def device(ctx, array, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(array)).to(ctx.device)
+    return t if dtype is None else t.to(dtype)
+
+
+# ---- embedding: a row of the encoded table, bit-exact with the block decoders
+@pytest.mark.parametrize("vt", [8, 12, 13, 14])
+def test_embedding_rows_are_bit_exact(ctx, ops, vt):
+    hidden, vocabulary = 512, 97
+    w = synth.random_weight(vt, hidden, vocabulary, seed=vt)
+    weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("token_embd", [hidden, vocabulary]), vt, device(ctx, w))
+    tokens = np.array([0, 96, 5, 5, 33], np.int32)
+    out = torch.full((len(tokens), hidden), float("nan"), device=ctx.device)
+    ops.embedding(weight, device(ctx, tokens), out)
+    ctx.synchronize()
+    table = oracle.dequantize(vt, w, hidden, vocabulary).reshape(vocabulary, hidden)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), table[tokens].view(np.uint32))
+
+
+def test_embedding_leaves_out_of_range_rows_untouched(ctx, ops):
+    hidden, vocabulary = 256, 10
+    w = synth.random_weight(12, hidden, vocabulary, seed=1)
+    weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("token_embd", [hidden, vocabulary]), 12, device(ctx, w))
+    out = torch.full((2, hidden), 7.0, device=ctx.device)
+    ops.embedding(weight, device(ctx, np.array([10, 3], np.int32)), out)
+    ctx.synchronize()
+    assert torch.all(out[0] == 7.0) and not torch.any(out[1] == 7.0)
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+        ops.embedding(weight, device(ctx, np.array([1], np.int32)), torch.empty(hidden + 1, device=ctx.device))
+    assert e.value.kind == "OutputLength"
+
+
+# ---- head norms + rope + cache append
+@pytest.mark.parametrize("members,q_heads,kv_heads", [(1, 4, 2), (3, 8, 1), (2, 32, 8)])
+def test_qk_norm_rope_append(ctx, ops, members, q_heads, kv_heads):
+    d, max_context, base, eps = 128, 40, 1.0e6, 1e-6
+    rng = np.random.default_rng(members)
+    q = rng.standard_normal((members, q_heads, d)).astype(np.float32) * 3
+    k = rng.standard_normal((members, kv_heads, d)).astype(np.float32) * 3
+    v = rng.standard_normal((members, kv_heads, d)).astype(np.float32)
+    q_norm = (1 + 0.02 * rng.standard_normal(d)).astype(np.float32)
+    k_norm = (1 + 0.02 * rng.standard_normal(d)).astype(np.float32)
+    positions = rng.integers(0, max_context, members).astype(np.int32)
+    qd, kd, vd = device(ctx, q), device(ctx, k), device(ctx, v)
+    k_cache = torch.zeros(members, kv_heads, max_context, d, dtype=torch.float16, device=ctx.device)
+    v_cache = torch.zeros_like(k_cache)
+    qn, kn, pos = device(ctx, q_norm), device(ctx, k_norm), device(ctx, positions)
+    attention = _lib.Attention(members, q_heads, kv_heads, d, d, base, eps, qn.data_ptr(), kn.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                               v_cache.data_ptr(), max_context, max_context)
+    ops.qk_norm_rope_append(attention, qd, kd, vd)
+    ctx.synchronize()
+    for m in range(members):
+        p = int(positions[m])
+        q_ref = layer_np.rope_neox(layer_np.rms_norm_raw(q[m], q_norm, eps), p, d, base)
+        k_ref = layer_np.rope_neox(layer_np.rms_norm_raw(k[m], k_norm, eps), p, d, base)
+        # sin/cos of angles up to max_context radians: a few f32 ulps of the angle
+        assert np.max(np.abs(qd[m].cpu().numpy() - q_ref)) <= 2e-5 * np.max(np.abs(q_ref))
+        got_k = k_cache[m, :, p].float().cpu().numpy()
+        assert np.max(np.abs(got_k - k_ref)) <= 1.5e-3 * np.max(np.abs(k_ref))   # one f16 rounding
+        assert np.array_equal(v_cache[m, :, p].cpu().numpy(), v[m].astype(np.float16))
+        untouched = np.delete(np.arange(max_context), p)
+        assert not k_cache[m][:, untouched].any() and not v_cache[m][:, untouched].any()
+
+
+# ---- attention over the cache
+@pytest.mark.parametrize("members,q_heads,kv_heads,tokens", [(1, 4, 2, 1), (1, 32, 8, 2048), (3, 8, 2, 77), (2, 8, 1, 300), (32, 32, 8, 64)])
+def test_attention_decode(ctx, ops, members, q_heads, kv_heads, tokens):
+    d, max_context = 128, 2304
+    rng = np.random.default_rng(tokens)
+    q = rng.standard_normal((members, q_heads, d)).astype(np.float32)
+    lengths = np.array([max(1, tokens - 13 * m) for m in range(members)], np.int32)
+    keys = (rng.standard_normal((members, kv_heads, int(lengths.max()), d)) * 0.5).astype(np.float16)
+    values = rng.standard_normal((members, kv_heads, int(lengths.max()), d)).astype(np.float16)
+    k_cache = torch.zeros(members, kv_heads, max_context, d, dtype=torch.float16, device=ctx.device)
+    v_cache = torch.zeros_like(k_cache)
+    k_cache[:, :, :keys.shape[2]] = device(ctx, keys)
+    v_cache[:, :, :keys.shape[2]] = device(ctx, values)
+    # poison what lies beyond each sequence: it must not be read
+    for m in range(members):
+        k_cache[m, :, int(lengths[m]):] = float("nan")
+        v_cache[m, :, int(lengths[m]):] = float("nan")
+    positions = device(ctx, lengths - 1)
+    out = torch.full((members, q_heads * d), float("nan"), device=ctx.device)
+    for active in sorted({int(lengths.max()), max_context}):
+        attention = _lib.Attention(members, q_heads, kv_heads, d, d, 1e6, 1e-6, None, None, positions.data_ptr(), k_cache.data_ptr(),
+                                   v_cache.data_ptr(), max_context, active)
+        ops.attention_decode(attention, device(ctx, q), out)
+        ctx.synchronize()
+        for m in range(members):
+            n = int(lengths[m])
+            ref = layer_np.attention(q[m], keys[m, :, :n].astype(np.float32).transpose(1, 0, 2), values[m, :, :n].astype(np.float32).transpose(1, 0, 2))
+            got = out[m].cpu().numpy().reshape(q_heads, d)
+            assert np.all(np.isfinite(got))
+            assert np.max(np.abs(got - ref)) <= 2e-5 * max(1.0, np.max(np.abs(ref)))
+
+
+# ---- elementwise and argmax
+def test_silu_mul_and_residual_add(ctx, ops):
+    rng = np.random.default_rng(0)
+    members, length = 3, 1000
+    both = (rng.standard_normal((members, 2 * length)) * 4).astype(np.float32)
+    bd = device(ctx, both)
+    out = torch.empty(members, length, device=ctx.device)
+    ops.silu_mul(bd, bd[:, length:], out, members, length, 2 * length)   # the halves of one [members][2 * length] buffer
+    ctx.synchronize()
+    ref = layer_np.silu_mul(both[:, :length], both[:, length:])
+    assert np.max(np.abs(out.cpu().numpy() - ref)) <= 1e-6 * np.max(np.abs(ref))
+    y = device(ctx, ref)
+    ops.residual_add(y, out)
+    ctx.synchronize()
+    assert np.array_equal(y.cpu().numpy(), ref + out.cpu().numpy())
+
+
+def test_argmax_rules(ctx, ops):
+    rng = np.random.default_rng(1)
+    logits = rng.standard_normal((5, 151936)).astype(np.float32)
+    logits[1, 7] = logits[1, 9000] = 50.0        # tie: lowest index
+    logits[2, 100] = np.nan                       # NaN never wins
+    logits[2, 3] = 60.0
+    logits[3, :] = np.nan                         # a row of NaNs gives 0
+    logits[4, :] = -np.inf
+    logits[4, 151935] = -1e30
+    out = torch.zeros(5, dtype=torch.int32, device=ctx.device)
+    ops.argmax(device(ctx, logits), 5, out)
+    ctx.synchronize()
+    assert out.cpu().tolist() == [layer_np.argmax(row) for row in logits]
+    assert out.cpu().tolist()[1:] == [7, 3, 0, 151935]
+
+
+# ---- the decode loop on a small random model
+def small_model(ctx, geometry, seed=0):
+    shapes = decode.local_shapes(geometry, 1, 0)
+    weights, host = decode.DenseWeights(), {}
+    rng = np.random.default_rng(seed)
+
+    def matrix(name, kind, salt):
+        k, n = shapes[kind]
+        vt = decode.VALUE_TYPES[kind]
+        encoded = synth.random_weight(vt, k, n, seed=seed * 100 + salt)
+        weights.matrices[name] = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new(name, [k, n]), vt, device(ctx, encoded))
+        host[name] = oracle.dequantize(vt, encoded, k, n).reshape(n, k)
+
+    def vector(name, length):
+        host[name] = (1 + 0.02 * rng.standard_normal(length)).astype(np.float32)
+        weights.vectors[name] = device(ctx, host[name])
+
+    matrix("token_embd", "token_embd", 1)
+    matrix("output", "output", 2)
+    vector("output_norm", geometry.hidden)
+    for i in range(geometry.layers):
+        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")):
+            matrix(f"blk.{i}.{kind}", kind, 10 + 8 * i + j)
+        vector(f"blk.{i}.attn_norm", geometry.hidden)
+        vector(f"blk.{i}.ffn_norm", geometry.hidden)
+        vector(f"blk.{i}.attn_q_norm", geometry.head_dim)
+        vector(f"blk.{i}.attn_k_norm", geometry.head_dim)
+    return weights, host
+
+
+@pytest.mark.parametrize("members,graph", [(1, False), (1, True), (3, True), (6, True)])
+def test_decode_loop_matches_host_model(members, graph):
+    context = engine_b200.RibnContext(0, stream=torch.cuda.Stream())   # its own stream: the step is captured into a graph
+    geometry = decode.DenseGeometry(hidden=512, layers=2, q_heads=4, kv_heads=2, head_dim=128, intermediate=768, vocabulary=1000)
+    weights, host = small_model(context, geometry, seed=members)
+    decoder = decode.CudaDenseDecode(context, geometry, weights, members, max_context=64)
+    models = [layer_np.DenseModel(host, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.head_dim, geometry.rope_base, geometry.eps)
+              for _ in range(members)]
+    tokens = [(17 * m + 3) % geometry.vocabulary for m in range(members)]
+    decoder.tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
+    torch.cuda.synchronize()
+    if graph:
+        decoder.capture()          # runs one step eagerly first: reset what that step wrote
+        decoder.k_cache.zero_()
+        decoder.v_cache.zero_()
+        torch.cuda.synchronize()
+    steps = 6
+    for step in range(steps):
+        decoder.replay() if graph else decoder.run_step()
+        context.synchronize()
+        logits = decoder.logits.cpu().numpy()
+        chosen = decoder.next_tokens.cpu().tolist()
+        for m in range(members):
+            ref = models[m].step(tokens[m], step)
+            scale = np.max(np.abs(ref))
+            # every GEMV is within 2e-3 of its own scale; seven of them per layer feed the logits
+            assert np.max(np.abs(logits[m] - ref)) <= 2e-2 * scale, f"step {step} member {m}"
+            top = np.sort(ref)[-2:]
+            if top[1] - top[0] > 4e-2 * scale:     # a clear winner must be chosen
+                assert chosen[m] == int(np.argmax(ref))
+            tokens[m] = chosen[m]
+        decoder.advance()
+    assert decoder.positions.cpu().tolist() == [steps] * members
+    context.close()
