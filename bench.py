@@ -164,6 +164,71 @@ def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
             "whole_step": {"achieved": step_gbps, "frac": step_gbps / peak, "bytes_per_step": step_bytes}}
 
 
+def decode_leg(args, ctx, device, rank, world, peak):
+    """Decode tok/s.  One GPU: Qwen3-8B shape, Q4_K_M mix, 2048 tokens of context, 256 generated, batch 1 and 32.
+    Several GPUs: Qwen3-32B shape, tensor parallel over all ranks, 4096 tokens of context, batch 64, all-reduce
+    after o_proj and ffn_down.  Weights are random-init on the device and the context is random KV entries
+    (what a random-token prompt leaves in the cache)."""
+    import torch
+    import torch.distributed as dist
+
+    from engine_b200 import decode
+
+    results = {}
+    generated = 256
+    if world == 1:
+        geometry = decode.DenseGeometry.qwen3_8b(args.decode_layers or 36)
+        plans = [("qwen3_8b_batch1", 1, 2048), ("qwen3_8b_batch32", 32, 2048)]
+        group = None
+    else:
+        geometry = decode.DenseGeometry.qwen3_32b(args.decode_layers or 64)
+        plans = [(f"qwen3_32b_tp{world}_batch64", 64, 4096)]
+        group = dist.group.WORLD
+    try:
+        weights = decode.random_weights(ctx, geometry, seed=1, world=world, rank=rank)
+        for name, members, context_tokens in plans:
+            decoder = decode.CudaDenseDecode(ctx, geometry, weights, members, context_tokens + generated + 8, process_group=group,
+                                             world=world, rank=rank)
+            decoder.fill_context(context_tokens)
+            decoder.capture(advance=True)
+            decoder.fill_context(context_tokens)   # the eager step inside capture() advanced nothing but wrote one cache slot
+            for _ in range(3):
+                decoder.replay()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(ctx.stream)
+            for _ in range(generated - 3):
+                decoder.replay()
+            b.record(ctx.stream)
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            if world > 1:
+                t = torch.tensor([ms], device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            steps = generated - 3
+            step_ms = ms / steps
+            weight_bytes = weights.bytes_per_step()   # this rank's shard
+            shapes = decoder.shapes
+            kv_bytes = geometry.layers * members * shapes["kv_heads"] * geometry.head_dim * 2 * 2 * (context_tokens + generated // 2)
+            results[name] = {
+                "tokens_per_s": members * steps / (ms * 1e-3), "ms_per_token_step": step_ms, "members": members,
+                "context": context_tokens, "generated": generated, "layers": geometry.layers, "launches_per_step": decoder.launches_per_step,
+                "weight_bytes_per_step_per_gpu": weight_bytes, "kv_bytes_per_step_per_gpu": kv_bytes,
+                "hbm_GBps_per_gpu": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9,
+                "hbm_frac_of_peak": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / peak,
+                "data": "random-init weights (Q4_K_M mix), random KV context, greedy decoding", "n_gpus": world,
+            }
+            del decoder
+            torch.cuda.empty_cache()
+        results["reference_cuda_decode"] = "not measured (the reference's layer forward is Rust host code; only its GEMV kernels are timed here)"
+    except Exception as exc:   # the sweep line must still be printed
+        results["error"] = f"{type(exc).__name__}: {exc}"
+    return results
+
+
 def time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, reps):
     """GB/s of the sweep when the reference project's own GEMV kernels serve it (cubins from oracle/build_ref.py)."""
     import torch
@@ -244,6 +309,8 @@ def main() -> None:
                         help="library tuning option passed to ribn_set_option (measurement runs only)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
+    parser.add_argument("--no-decode", action="store_true", help="skip the decode-loop measurements")
+    parser.add_argument("--decode-layers", type=int, default=0, help="layer count of the decode models (0 = the full 36 / 64)")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
     parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
     parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
@@ -435,6 +502,11 @@ def main() -> None:
     if rank == 0 and world == 1 and not args.no_reference_cuda:
         reference_cuda = time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, max(3, min(args.steps, 20)))
 
+    # ---- decode loop: tokens per second of a random-init dense model (second half of the metric)
+    decode_results = None
+    if not args.no_decode and not args.only:
+        decode_results = decode_leg(args, ctx, device, rank, world, peak=measured_peak()[0])
+
     breakdown = None
     if args.cases and rank == 0:
         breakdown = {}
@@ -480,6 +552,8 @@ def main() -> None:
             line["cases"] = breakdown
         if reference_cuda is not None:
             line["reference_cuda"] = reference_cuda
+        if decode_results is not None:
+            line["decode"] = decode_results
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_leg()
         print(json.dumps(line))

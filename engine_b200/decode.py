@@ -261,8 +261,10 @@ class CudaDenseDecode:
             if self.world > 1:
                 self._select_tokens_tensor_parallel()
 
-    def capture(self) -> None:
-        """Record run_step into a CUDA graph (positions and tokens are read from device memory at replay)."""
+    def capture(self, advance: bool = False) -> None:
+        """Record run_step into a CUDA graph (positions and tokens are read from device memory at replay).
+        With `advance` the graph also feeds the chosen tokens back and increments the positions, so that
+        one replay is one generated token per sequence."""
         self.run_step()   # first launches set kernel attributes, which a capture must not contain
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -270,7 +272,28 @@ class CudaDenseDecode:
             self._forward()
             if self.world > 1:
                 self._select_tokens_tensor_parallel()
+            if advance:
+                self.tokens.copy_(self.next_tokens)
+                self.positions.add_(1)
         self.graph = graph
+
+    def fill_context(self, tokens_in_context: int, seed: int = 0) -> None:
+        """Stand-in for a prompt of `tokens_in_context` random tokens: the cache positions below it get random
+        f16 keys and values (what a random prompt leaves there, at none of the prefill cost), positions point
+        at the next free slot and every sequence starts from a random token."""
+        generator = torch.Generator(device=self.context.device)
+        generator.manual_seed(seed + self.rank)
+        with torch.cuda.stream(self.context.stream):
+            for cache in (self.k_cache, self.v_cache):
+                for layer in range(self.geometry.layers):
+                    view = cache[layer][:, :, :tokens_in_context]
+                    view.copy_(torch.randn(view.shape, device=self.context.device, generator=generator, dtype=torch.float32).to(torch.float16))
+            self.positions.fill_(tokens_in_context)
+            token_generator = torch.Generator(device=self.context.device)
+            token_generator.manual_seed(seed)   # the same tokens on every rank
+            self.tokens.copy_(torch.randint(0, self.geometry.vocabulary, (self.members,), device=self.context.device, generator=token_generator,
+                                            dtype=torch.int32))
+        torch.cuda.synchronize()
 
     def replay(self) -> None:
         with torch.cuda.stream(self.context.stream):
