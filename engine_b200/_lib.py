@@ -60,6 +60,21 @@ class Attention(ctypes.Structure):
     ]
 
 
+class GemvJob(ctypes.Structure):
+    """struct ribn_gemv_job"""
+
+    _fields_ = [
+        ("expected_type", ctypes.c_uint32),
+        ("weight", ctypes.POINTER(QWeight)),
+        ("y_device", ctypes.c_void_p),
+        ("y_dtype", ctypes.c_int),
+        ("y_len", ctypes.c_uint64),
+        ("accumulate", ctypes.c_int),
+    ]
+
+
+RIBN_FUSED_SWIGLU = 1
+
 _u64p = ctypes.POINTER(ctypes.c_uint64)
 _vp = ctypes.c_void_p
 _qwp = ctypes.POINTER(QWeight)
@@ -89,6 +104,8 @@ SIGNATURES = {
                                       ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_gemv_noalloc": (ctypes.c_int, [ctypes.c_int, _vp, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_int,
                                          ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint64]),
+    "ribn_gemv_fused": (ctypes.c_int, [_vp, ctypes.POINTER(GemvJob), ctypes.c_uint32, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64,
+                                       ctypes.c_float, ctypes.c_uint32, ctypes.c_uint32]),
     "ribn_embedding": (ctypes.c_int, [_vp, _qwp, _vp, ctypes.c_uint32, _vp, ctypes.c_uint64]),
     "ribn_qk_norm_rope_append": (ctypes.c_int, [_vp, _attp, _vp, _vp, _vp]),
     "ribn_attention_decode": (ctypes.c_int, [_vp, _attp, _vp, _vp]),

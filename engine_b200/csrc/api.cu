@@ -239,8 +239,14 @@ Failure validate_gemv(const ribn_qweight* w, uint32_t expected_type, int x_dtype
     return Failure{};
 }
 
+struct TcExtras {
+    bool swiglu = false;        // x rows are [gate | up]
+    bool skip_prepass = false;  // reuse the f16 activations the previous call of the group left in the workspace
+    bool accumulate = false;    // y += W x
+};
+
 int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y, int y_dtype,
-               uint64_t members, const float* norm_weight = nullptr, float eps = 0.0f) {
+               uint64_t members, const float* norm_weight = nullptr, float eps = 0.0f, TcExtras extras = TcExtras{}) {
     ribn::TcArgs t{};
     t.weights = static_cast<const uint8_t*>(w->data);
     t.weight_bytes = w->encoded_bytes;
@@ -252,6 +258,9 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     t.x_bf16 = x_dtype == RIBN_BF16;
     t.norm_weight = norm_weight;
     t.eps = eps;
+    t.swiglu = extras.swiglu;
+    t.skip_prepass = extras.skip_prepass;
+    t.accumulate = extras.accumulate;
     t.y = y;
     t.y_bf16 = y_dtype == RIBN_BF16;
     t.scratch = ctx->workspace;
@@ -272,7 +281,8 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     // Decode batches: one f16 tile per step, normalised per super-block, accumulated in registers.  Prefill:
     // split bf16 operands accumulated in TMEM over the whole K range (hundreds of tokens per tile do not
     // fit the registers of the accumulate warps).
-    const bool decode = members <= 64 && (ctx->tc_split_operands == 0 || !t.x_bf16 || norm_weight != nullptr);
+    const bool decode = members <= 64 && (ctx->tc_split_operands == 0 || !t.x_bf16 || norm_weight != nullptr || extras.swiglu ||
+                                          extras.skip_prepass || extras.accumulate);
     const cudaError_t e = decode ? ribn::launch_qgemv_tc(t) : ribn::launch_qgemm_tc(t);
     if (e != cudaSuccess) return record_cuda(ctx, e, "tensor-core GEMM launch");
     return RIBN_OK;
@@ -349,6 +359,63 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
 }  // namespace
 
 namespace {
+// One activation pre-pass, then one GEMV launch per job (see ribn_gemv_fused).  Every job was validated.
+int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, const uint64_t* ns, uint64_t k, const void* x,
+                  int x_dtype, const float* norm_weight, float eps, uint32_t members, bool swiglu) {
+    const bool x_bf16 = x_dtype == RIBN_BF16;
+    bool all_tc = true, all_dp4a = true;
+    const int members_per_launch = members < 4 ? static_cast<int>(members) : 4;
+    for (uint32_t j = 0; j < job_count; ++j) {
+        all_tc = all_tc && ribn::qgemm_tc_supports(jobs[j].weight->value_type, static_cast<int>(k));
+        all_dp4a = all_dp4a && ribn::gemv_dp4a_fits(jobs[j].weight->value_type, static_cast<int>(k), members_per_launch);
+    }
+    if (ctx->gemv_path == 0 && (x_bf16 || ctx->tc_f32_activations != 0) && members >= static_cast<uint32_t>(ctx->tc_min_members) && all_tc &&
+        members * k * 2 + (1u << 20) <= ctx->workspace_bytes) {
+        for (uint32_t j = 0; j < job_count; ++j) {
+            TcExtras extras;
+            extras.swiglu = swiglu;
+            extras.skip_prepass = j > 0;
+            extras.accumulate = jobs[j].accumulate != 0;
+            const int rc = enqueue_tc(ctx, jobs[j].weight, k, ns[j], x, x_dtype, jobs[j].y_device, jobs[j].y_dtype, members, norm_weight, eps,
+                                      extras);
+            if (rc != RIBN_OK) return rc;
+        }
+        return RIBN_OK;
+    }
+    const uint64_t stride = ribn::packed_activation_stride(ribn::padded_k(static_cast<int>(k)));
+    if (ctx->gemv_path == 1 || !all_dp4a || stride * members > ctx->workspace_bytes)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "the fused call needs a shape the packed-activation kernels serve"));
+    cudaError_t e = ribn::launch_quantize_activations(x, x_bf16, norm_weight, eps, ctx->workspace, static_cast<int>(members),
+                                                      static_cast<int>(k), ctx->stream, swiglu);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "activation packing launch");
+    for (uint32_t j = 0; j < job_count; ++j) {
+        GemvArgs a{};
+        a.weights = static_cast<const uint8_t*>(jobs[j].weight->data);
+        a.weight_bytes = jobs[j].weight->encoded_bytes;
+        a.value_type = jobs[j].weight->value_type;
+        a.k = static_cast<int>(k);
+        a.n = static_cast<int>(ns[j]);
+        a.x_bf16 = x_bf16;
+        a.y_bf16 = jobs[j].y_dtype == RIBN_BF16;
+        a.accumulate = jobs[j].accumulate != 0;
+        a.device_status = ctx->device_status;
+        a.sm_count = ctx->sm_count;
+        a.variant = ctx->variant;
+        a.stream = ctx->stream;
+        for (uint32_t m0 = 0; m0 < members; m0 += 4) {
+            a.members = static_cast<int>(members - m0 < 4 ? members - m0 : 4);
+            a.x = static_cast<const uint8_t*>(ctx->workspace) + static_cast<uint64_t>(m0) * stride;
+            a.y = static_cast<uint8_t*>(jobs[j].y_device) + static_cast<uint64_t>(m0) * ns[j] * dtype_bytes(jobs[j].y_dtype);
+            bool handled = false;
+            e = ribn::launch_gemv_dp4a(a, &handled);
+            if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+            if (!handled) return record(ctx, fail(RIBN_E_DRIVER, "integer-dot GEMV refused a shape it had accepted"));
+        }
+    }
+    return RIBN_OK;
+}
+
+
 
 Failure validate_attention(const ribn_attention* a) {
     if (a == nullptr) return fail(RIBN_E_INVALID_ARGUMENT, "null attention descriptor");
@@ -817,6 +884,47 @@ int ribn_argmax(ribn_ctx* ctx, const float* logits_device, uint32_t members, uin
     const cudaError_t e = ribn::launch_argmax(logits_device, static_cast<int>(members), length, out_device, ctx->stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "argmax launch");
     return RIBN_OK;
+}
+
+int ribn_gemv_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, const void* x_device, int x_dtype, uint64_t x_len,
+                    const float* norm_weight_device, uint64_t norm_weight_len, float eps, uint32_t members, uint32_t flags) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (jobs == nullptr || job_count == 0 || job_count > RIBN_MAX_FUSED_JOBS)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, fmt("a fused call takes 1..%u projections", RIBN_MAX_FUSED_JOBS)));
+    const bool swiglu = (flags & RIBN_FUSED_SWIGLU) != 0;
+    if ((flags & ~RIBN_FUSED_SWIGLU) != 0) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "unknown flag"));
+    if (swiglu && norm_weight_device != nullptr)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "RMSNorm and silu_mul cannot both be fused in front of one projection"));
+    uint64_t ns[RIBN_MAX_FUSED_JOBS];
+    uint64_t k = 0;
+    // Every projection is validated before anything is launched, with the reference's checks.
+    for (uint32_t j = 0; j < job_count; ++j) {
+        if (jobs[j].weight == nullptr) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "null weight"));
+        uint64_t kj = 0;
+        uint64_t x_expected = x_len;
+        if (swiglu) {
+            if (x_len % 2 != 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "a [gate | up] input has an even number of values", x_len + 1, x_len));
+            x_expected = x_len / 2;
+        }
+        Failure f = validate_gemv(jobs[j].weight, jobs[j].expected_type, x_dtype, x_expected, jobs[j].y_dtype, jobs[j].y_len, members, &kj,
+                                  &ns[j]);
+        if (f.status != RIBN_OK) return record(ctx, f);
+        if (j == 0) k = kj;
+        if (kj != k)
+            return record(ctx, fail(RIBN_E_INPUT_LENGTH, fmt("projection %u has input size %" PRIu64 ", the first has %" PRIu64, j, kj, k), k, kj));
+    }
+    if (norm_weight_device != nullptr && norm_weight_len != k)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH, fmt("RMSNorm weight has %" PRIu64 " values, expected %" PRIu64, norm_weight_len, k), k,
+                                norm_weight_len));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK && norm_weight_device != nullptr) f = check_device_pointer(ctx, norm_weight_device, "norm weight");
+    for (uint32_t j = 0; j < job_count && f.status == RIBN_OK; ++j) {
+        f = check_device_pointer(ctx, jobs[j].weight->data, "weight");
+        if (f.status == RIBN_OK) f = check_device_pointer(ctx, jobs[j].y_device, "output");
+    }
+    if (f.status != RIBN_OK) return record(ctx, f);
+    return enqueue_fused(ctx, jobs, job_count, ns, k, x_device, x_dtype, norm_weight_device, eps, members, swiglu);
 }
 
 }  // extern "C"

@@ -58,6 +58,7 @@ struct Dp4aParams {
     int nsb;
     int members;
     int y_bf16;
+    int accumulate;                // y += W x
     int stages;
     int* status;
 };
@@ -469,8 +470,10 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
                 for (int q = 1; q < kWK; ++q) v += red_buf[(q * kRows + rr) * MT + m];
                 const size_t o = static_cast<size_t>(m) * p.n + row;
                 if (p.y_bf16) {
+                    if (p.accumulate) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]);
                     static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(v);
                 } else {
+                    if (p.accumulate) v += static_cast<const float*>(p.y)[o];
                     static_cast<float*>(p.y)[o] = v;
                 }
             }
@@ -524,6 +527,7 @@ cudaError_t launch(const GemvArgs& a, bool* handled) {
     p.nsb = nsb;
     p.members = a.members;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
+    p.accumulate = a.accumulate ? 1 : 0;
     p.stages = stages;
     p.status = a.device_status;
     int grid = a.sm_count * ctas;

@@ -46,6 +46,7 @@ struct GemvArgs {
     void* y;                  // [members][n]
     bool y_bf16;
     int members;              // 1..8 per launch
+    bool accumulate;          // y += W x instead of y = W x (integer-dot kernel only)
     int* device_status;
     int sm_count;
     int variant;              // tuning variant, 0 = default
@@ -64,9 +65,10 @@ __host__ __device__ inline unsigned long long packed_activation_stride(int kpad)
 inline int padded_k(int k) { return (k + 255) / 256 * 256; }
 
 // x [members][k] (f32 or bf16) -> packed rows; with norm_weight != nullptr the row is RMS-normalised
-// and scaled first (y = x * rsqrt(mean(x^2)+eps) * norm_weight), i.e. RMSNorm fused into the packer.
+// and scaled first (y = x * rsqrt(mean(x^2)+eps) * norm_weight), i.e. RMSNorm fused into the packer.  With
+// swiglu the input rows are [gate | up] (2k values) and silu(gate) * up is what gets packed.
 cudaError_t launch_quantize_activations(const void* x, bool x_bf16, const float* norm_weight, float eps, void* packed,
-                                        int members, int k, cudaStream_t stream);
+                                        int members, int k, cudaStream_t stream, bool swiglu = false);
 
 // Integer-dot GEMV for 1..4 members over packed activations (args.x = packed rows).  *handled is
 // false when the shape does not fit (activations too large for shared memory); nothing was launched
@@ -84,6 +86,9 @@ struct TcArgs {
     bool x_bf16;
     const float* norm_weight; // launch_qgemv_tc only: RMSNorm weight applied to x first, or null
     float eps;
+    bool swiglu;              // launch_qgemv_tc only: x rows are [gate | up], the operand is silu(gate) * up
+    bool skip_prepass;        // launch_qgemv_tc only: the f16 activations of the previous call are still in the scratch
+    bool accumulate;          // launch_qgemv_tc only: y += W x
     void* y;                  // [m][n]
     bool y_bf16;
     void* scratch;            // split-K partial tiles

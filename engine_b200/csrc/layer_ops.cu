@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
 // memory once for the whole group; lane = token for the scores, lane = 4 output dims for P.V.
 constexpr int kAttnTile = 32;
 constexpr int kAttnHeadDim = 128;
-constexpr int kAttnKStride = kAttnHeadDim + 2;   // halves; 65 words per row: lanes hit distinct banks
+constexpr int kAttnKStride = kAttnHeadDim + 8;   // halves; rows 272 bytes apart: the 16-byte loads of eight lanes cover all banks once
 constexpr int kAttnMaxGroup = 8;
 
 __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(const float* __restrict__ q, const __half* __restrict__ k_cache,
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
                                                                              long long max_context, int chunk, float scale) {
-    __shared__ __half k_tile[kAttnTile * kAttnKStride];
+    __shared__ __align__(16) __half k_tile[kAttnTile * kAttnKStride];
     __shared__ __align__(16) __half v_tile[kAttnTile * kAttnHeadDim];
     __shared__ __align__(16) float q_rows[kAttnMaxGroup * kAttnHeadDim];
     const int kv_head = blockIdx.x;
@@ -160,17 +160,17 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     for (int t0 = begin; t0 < end; t0 += kAttnTile) {
         const int valid = min(kAttnTile, end - t0);
         __syncthreads();   // previous tile fully consumed (and q_rows written, first time round)
-        // Tile loads: 32 tokens x 128 halves each; a thread moves 4-byte words (the padded K rows are only 4-byte aligned).
-        for (int i = threadIdx.x; i < kAttnTile * (kAttnHeadDim / 2); i += blockDim.x) {
-            const int row = i / (kAttnHeadDim / 2);
-            const int word = i % (kAttnHeadDim / 2);
-            uint32_t kw = 0, vw = 0;
+        // Tile loads: 32 tokens x 128 halves each, 16 bytes per thread and step.
+        for (int i = threadIdx.x; i < kAttnTile * (kAttnHeadDim / 8); i += blockDim.x) {
+            const int row = i / (kAttnHeadDim / 8);
+            const int chunk = i % (kAttnHeadDim / 8);
+            uint4 kw = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
             if (row < valid) {
-                kw = *reinterpret_cast<const uint32_t*>(k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 2 * word);
-                vw = *reinterpret_cast<const uint32_t*>(v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 2 * word);
+                kw = *reinterpret_cast<const uint4*>(k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk);
+                vw = *reinterpret_cast<const uint4*>(v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk);
             }
-            *reinterpret_cast<uint32_t*>(k_tile + row * kAttnKStride + 2 * word) = kw;
-            *reinterpret_cast<uint32_t*>(v_tile + row * kAttnHeadDim + 2 * word) = vw;
+            *reinterpret_cast<uint4*>(k_tile + row * kAttnKStride + 8 * chunk) = kw;
+            *reinterpret_cast<uint4*>(v_tile + row * kAttnHeadDim + 8 * chunk) = vw;
         }
         __syncthreads();
         if (warp < group) {
@@ -178,12 +178,23 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
             const float* qv = q_rows + warp * kAttnHeadDim;
             const __half* kr = k_tile + lane * kAttnKStride;
             float dot = 0.0f;
-#pragma unroll 16
-            for (int d = 0; d < kAttnHeadDim; d += 2) {
-                const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kr + d));
-                const float2 qq = *reinterpret_cast<const float2*>(qv + d);
-                dot = fmaf(qq.x, kk.x, dot);
-                dot = fmaf(qq.y, kk.y, dot);
+#pragma unroll 4
+            for (int d = 0; d < kAttnHeadDim; d += 8) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
+                const float4 q0 = *reinterpret_cast<const float4*>(qv + d);
+                const float4 q1 = *reinterpret_cast<const float4*>(qv + d + 4);
+                const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                const float2 k45 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
+                const float2 k67 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                dot = fmaf(q0.x, k01.x, dot);
+                dot = fmaf(q0.y, k01.y, dot);
+                dot = fmaf(q0.z, k23.x, dot);
+                dot = fmaf(q0.w, k23.y, dot);
+                dot = fmaf(q1.x, k45.x, dot);
+                dot = fmaf(q1.y, k45.y, dot);
+                dot = fmaf(q1.z, k67.x, dot);
+                dot = fmaf(q1.w, k67.y, dot);
             }
             const float score = lane < valid ? dot * scale : -INFINITY;
             float tile_max = score;
@@ -337,7 +348,9 @@ cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& a) {
 }
 
 int attention_splits(int members, int kv_heads, long long active_context, int sm_count) {
-    int splits = (2 * sm_count) / (members * kv_heads);
+    // About eight CTAs per SM: a CTA walks its tiles one after the other, so the memory latency is hidden by
+    // the CTAs that share its SM.
+    int splits = (8 * sm_count) / (members * kv_heads);
     if (splits < 1) splits = 1;
     if (splits > 32) splits = 32;
     const long long tiles = (active_context + kAttnTile - 1) / kAttnTile;

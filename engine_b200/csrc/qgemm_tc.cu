@@ -453,6 +453,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.m = a.m;
     p.nsb = a.k / kSuperBlock;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
+    p.accumulate = 0;
     p.status = a.device_status;
     p.trace = a.trace;
     const int n_tiles = (a.n + kBM - 1) / kBM;

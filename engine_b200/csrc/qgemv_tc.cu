@@ -445,9 +445,11 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 if (split) {
                     part[o] = value;
                 } else if (p.y_bf16) {
-                    static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value);
+                    const float old = p.accumulate ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]) : 0.0f;
+                    static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value + old);
                 } else {
-                    static_cast<float*>(p.y)[o] = value;
+                    const float old = p.accumulate ? static_cast<const float*>(p.y)[o] : 0.0f;
+                    static_cast<float*>(p.y)[o] = value + old;
                 }
             }
         }
@@ -489,8 +491,10 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 for (int u = 0; u < 4; ++u) {
                     if (m + u < m_end) {
                         if (p.y_bf16) {
+                            if (p.accumulate) sum[u] += __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o[u]]);
                             static_cast<__nv_bfloat16*>(p.y)[o[u]] = __float2bfloat16_rn(sum[u]);
                         } else {
+                            if (p.accumulate) sum[u] += static_cast<const float*>(p.y)[o[u]];
                             static_cast<float*>(p.y)[o[u]] = sum[u];
                         }
                     }
@@ -512,12 +516,19 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 // that its largest magnitude lands in (2^13, 2^14], and rounded to f16; factor[m] = 2^e.
 constexpr int kConvertThreads = 512;
 
-__device__ __forceinline__ float load_activation(const void* x, bool bf16, size_t i) {
+__device__ __forceinline__ float load_scalar(const void* x, bool bf16, size_t i) {
     return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]) : static_cast<const float*>(x)[i];
+}
+// Element i of member row `member`; with swiglu the row is [gate | up] (2k values) and the element is
+// silu(gate[i]) * up[i] (silu_mul of the reference, model_ops.rs:316-328).
+__device__ __forceinline__ float load_activation(const void* x, bool bf16, int swiglu, size_t member, int k, int i) {
+    if (swiglu == 0) return load_scalar(x, bf16, member * k + i);
+    const float gate = load_scalar(x, bf16, member * 2 * k + i);
+    return (gate / (1.0f + expf(-gate))) * load_scalar(x, bf16, member * 2 * k + k + i);
 }
 
 __global__ void __launch_bounds__(kConvertThreads)
-convert_activations_f16(const void* x, int x_bf16, const float* norm_weight, float eps, __half* out, float* factor, int k) {
+convert_activations_f16(const void* x, int x_bf16, int swiglu, const float* norm_weight, float eps, __half* out, float* factor, int k) {
     pdl_launch_dependents();
     pdl_wait_prior();   // x may be the previous kernel's output; `out` may still be read by it
     __shared__ float red_sum[kConvertThreads / 32];
@@ -526,7 +537,7 @@ convert_activations_f16(const void* x, int x_bf16, const float* norm_weight, flo
     const size_t base = static_cast<size_t>(blockIdx.x) * k;
     float sum = 0.0f, biggest = 0.0f;
     for (int i = threadIdx.x; i < k; i += kConvertThreads) {
-        const float v = load_activation(x, x_bf16 != 0, base + i);
+        const float v = load_activation(x, x_bf16 != 0, swiglu, blockIdx.x, k, i);
         sum = fmaf(v, v, sum);
         biggest = fmaxf(biggest, fabsf(norm_weight != nullptr ? v * norm_weight[i] : v));
     }
@@ -566,7 +577,7 @@ convert_activations_f16(const void* x, int x_bf16, const float* norm_weight, flo
     }
     if (threadIdx.x == 0) factor[blockIdx.x] = up;
     for (int i = threadIdx.x; i < k; i += kConvertThreads) {
-        float v = load_activation(x, x_bf16 != 0, base + i);
+        float v = load_activation(x, x_bf16 != 0, swiglu, blockIdx.x, k, i);
         if (norm_weight != nullptr) v = v * inv_rms * norm_weight[i];
         out[base + i] = __float2half_rn(v * down);
     }
@@ -603,9 +614,11 @@ cudaError_t launch_tile(const TcArgs& a) {
         cudaFuncSetAttribute(convert_activations_f16, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         prepass_device = device;
     }
-    cudaError_t launched = launch_kernel(convert_activations_f16, dim3(a.m), dim3(kConvertThreads), 0, a.stream, a.x, a.x_bf16 ? 1 : 0,
-                                         a.norm_weight, a.eps, x16, factor, a.k);
-    if (launched != cudaSuccess) return launched;
+    if (!a.skip_prepass) {
+        cudaError_t launched = launch_kernel(convert_activations_f16, dim3(a.m), dim3(kConvertThreads), 0, a.stream, a.x, a.x_bf16 ? 1 : 0,
+                                             a.swiglu ? 1 : 0, a.norm_weight, a.eps, x16, factor, a.k);
+        if (launched != cudaSuccess) return launched;
+    }
 
     CUtensorMap map;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
@@ -639,6 +652,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.m = a.m;
     p.nsb = a.k / kSuperBlock;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
+    p.accumulate = a.accumulate ? 1 : 0;
     p.status = a.device_status;
     p.trace = a.trace;
     const int n_tiles = (a.n + kBM - 1) / kBM;

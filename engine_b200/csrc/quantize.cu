@@ -51,14 +51,17 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 
 // One CTA per member row.  Thread t owns the 8-element chunks t, t + 512, ...; four consecutive
 // threads share a block of 32 and combine their maxima and sums with two shuffles.
-template <typename XT, bool NORM>
+// MODE 0: the row as it is; 1: RMSNorm first; 2: the row is [gate | up], 2k values, and silu(gate) * up is packed
+// (silu_mul of the reference, model_ops.rs:316-328, fused in front of the down projection).
+template <typename XT, int MODE>
 __global__ void __launch_bounds__(kPackThreads) quantize_activations_kernel(const XT* __restrict__ x,
                                                                             const float* __restrict__ norm_weight, float eps,
                                                                             uint8_t* __restrict__ packed, int k, int kpad) {
     __shared__ float partial[kPackThreads / 32];
     pdl_launch_dependents();
     pdl_wait_prior();   // x may be the previous kernel's output; the packed rows may still be read by it
-    const XT* xr = x + static_cast<size_t>(blockIdx.x) * k;
+    constexpr bool NORM = MODE == 1;
+    const XT* xr = x + static_cast<size_t>(blockIdx.x) * k * (MODE == 2 ? 2 : 1);
     uint8_t* out = packed + static_cast<size_t>(blockIdx.x) * packed_activation_stride(kpad);
     int8_t* q1 = reinterpret_cast<int8_t*>(out);
     int8_t* q2 = q1 + kpad;
@@ -91,6 +94,12 @@ __global__ void __launch_bounds__(kPackThreads) quantize_activations_kernel(cons
         float v[8];
         if (c * 8 < k) {
             load_x8<XT>(xr + c * 8, v);
+            if (MODE == 2) {
+                float u[8];
+                load_x8<XT>(xr + k + c * 8, u);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u[j];
+            }
             if (NORM) {
                 float g[8];
                 load_x8<float>(norm_weight + c * 8, g);
@@ -137,21 +146,24 @@ __global__ void __launch_bounds__(kPackThreads) quantize_activations_kernel(cons
 
 template <typename XT>
 cudaError_t launch(const void* x, const float* norm_weight, float eps, void* packed, int members, int k, int kpad,
-                   cudaStream_t stream) {
-    if (norm_weight != nullptr)
-        return launch_kernel(quantize_activations_kernel<XT, true>, dim3(members), dim3(kPackThreads), 0, stream,
+                   bool swiglu, cudaStream_t stream) {
+    if (swiglu)
+        return launch_kernel(quantize_activations_kernel<XT, 2>, dim3(members), dim3(kPackThreads), 0, stream,
                              static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
-    return launch_kernel(quantize_activations_kernel<XT, false>, dim3(members), dim3(kPackThreads), 0, stream,
+    if (norm_weight != nullptr)
+        return launch_kernel(quantize_activations_kernel<XT, 1>, dim3(members), dim3(kPackThreads), 0, stream,
+                             static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
+    return launch_kernel(quantize_activations_kernel<XT, 0>, dim3(members), dim3(kPackThreads), 0, stream,
                          static_cast<const XT*>(x), norm_weight, eps, static_cast<uint8_t*>(packed), k, kpad);
 }
 
 }  // namespace
 
 cudaError_t launch_quantize_activations(const void* x, bool x_bf16, const float* norm_weight, float eps, void* packed,
-                                        int members, int k, cudaStream_t stream) {
+                                        int members, int k, cudaStream_t stream, bool swiglu) {
     const int kpad = padded_k(k);
-    return x_bf16 ? launch<__nv_bfloat16>(x, norm_weight, eps, packed, members, k, kpad, stream)
-                  : launch<float>(x, norm_weight, eps, packed, members, k, kpad, stream);
+    return x_bf16 ? launch<__nv_bfloat16>(x, norm_weight, eps, packed, members, k, kpad, swiglu, stream)
+                  : launch<float>(x, norm_weight, eps, packed, members, k, kpad, swiglu, stream);
 }
 
 }  // namespace ribn

@@ -20,6 +20,7 @@ struct TcParams {
     int nsb;                 // super-blocks per row
     int ksplit;
     int y_bf16;
+    int accumulate;          // decode kernel: add to y instead of overwriting it
     int* status;
     // Diagnostics: when non-null, CTA (0,0,0) of the decode kernel records SM clock stamps of its
     // pipeline events here: trace[(role * 64 + step) * 8 + event], 4 roles x 64 steps x 8 events.

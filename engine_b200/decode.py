@@ -50,7 +50,7 @@ class DenseGeometry:
 
 # The Q4_K_M mix named by the benchmark configuration: attn_v, ffn_down and the output head in Q6_K,
 # every other matrix in Q4_K.
-VALUE_TYPES = {"attn_q": Q4_K, "attn_k": Q4_K, "attn_v": Q6_K, "attn_output": Q4_K, "ffn_gate": Q4_K, "ffn_up": Q4_K,
+VALUE_TYPES = {"attn_q": Q4_K, "attn_k": Q4_K, "attn_v": Q6_K, "attn_output": Q4_K, "ffn_gate": Q4_K, "ffn_up": Q4_K, "ffn_gate_up": Q4_K,
                "ffn_down": Q6_K, "token_embd": Q4_K, "output": Q6_K}
 
 
@@ -82,6 +82,24 @@ class CudaDenseOps:
 
     def argmax(self, logits: torch.Tensor, members: int, output: torch.Tensor) -> None:
         self.context.check(self._lib.ribn_argmax(self.context.handle, logits.data_ptr(), members, logits.numel() // members, output.data_ptr()))
+
+
+def gemv_fused(context: RibnContext, jobs, x: torch.Tensor, members: int, norm: torch.Tensor | None = None, eps: float = 0.0,
+               swiglu: bool = False) -> None:
+    """ribn_gemv_fused: `jobs` is a list of (weight, output, accumulate); one activation pre-pass serves them all."""
+    array = (_lib.GemvJob * len(jobs))()
+    descriptors = [weight.descriptor() for weight, _, _ in jobs]   # kept alive until the call returns
+    for slot, descriptor, (weight, y, accumulate) in zip(array, descriptors, jobs):
+        slot.expected_type = 0
+        slot.weight = ctypes.pointer(descriptor)
+        slot.y_device = y.data_ptr()
+        slot.y_dtype = _lib.RIBN_F32 if y.dtype == torch.float32 else _lib.RIBN_BF16
+        slot.y_len = y.numel()
+        slot.accumulate = 1 if accumulate else 0
+    context.check(context._lib.ribn_gemv_fused(context.handle, array, len(jobs), x.data_ptr(),
+                                               _lib.RIBN_F32 if x.dtype == torch.float32 else _lib.RIBN_BF16, x.numel(),
+                                               norm.data_ptr() if norm is not None else None, norm.numel() if norm is not None else 0, eps,
+                                               members, _lib.RIBN_FUSED_SWIGLU if swiglu else 0))
 
 
 def attention_descriptor(geometry: DenseGeometry, members: int, q_heads: int, kv_heads: int, q_norm, k_norm, positions, k_cache, v_cache,
@@ -117,6 +135,7 @@ def local_shapes(geometry: DenseGeometry, world: int, rank: int) -> dict:
         "q_heads": q1 - q0, "kv_heads": kv1 - kv0, "intermediate": local_inter, "vocab_begin": v0, "vocab_end": v1,
         "attn_q": (geometry.hidden, local_q), "attn_k": (geometry.hidden, local_kv), "attn_v": (geometry.hidden, local_kv),
         "attn_output": (local_q, geometry.hidden), "ffn_gate": (geometry.hidden, local_inter), "ffn_up": (geometry.hidden, local_inter),
+        "ffn_gate_up": (geometry.hidden, 2 * local_inter),   # rows: this rank's gate rows, then its up rows
         "ffn_down": (local_inter, geometry.hidden), "token_embd": (geometry.hidden, geometry.vocabulary),
         "output": (geometry.hidden, v1 - v0),
     }
@@ -144,7 +163,8 @@ def random_weights(context: RibnContext, geometry: DenseGeometry, seed: int = 0,
     matrix("output", "output", 2)
     vector("output_norm", geometry.hidden)
     for i in range(geometry.layers):
-        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")):
+        # ffn_gate and ffn_up are stored as one matrix (gate rows, then up rows): one GEMV writes [gate | up]
+        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate_up", "ffn_down")):
             matrix(f"blk.{i}.{kind}", kind, 10 + i * 8 + j)
         vector(f"blk.{i}.attn_norm", geometry.hidden)
         vector(f"blk.{i}.ffn_norm", geometry.hidden)
@@ -176,9 +196,7 @@ class CudaDenseDecode:
         self.v = torch.zeros(m, s["kv_heads"] * g.head_dim, **f32)
         self.attended = torch.zeros(m, s["q_heads"] * g.head_dim, **f32)
         self.projected = torch.zeros(m, g.hidden, **f32)
-        self.gate = torch.zeros(m, s["intermediate"], **f32)
-        self.up = torch.zeros(m, s["intermediate"], **f32)
-        self.activated = torch.zeros(m, s["intermediate"], **f32)
+        self.gate_up = torch.zeros(m, 2 * s["intermediate"], **f32)
         self.logits = torch.zeros(m, s["vocab_end"] - s["vocab_begin"], **f32)
         self.next_tokens = torch.zeros(m, dtype=torch.int32, device=dev)
         cache_shape = (g.layers, m, s["kv_heads"], max_context, g.head_dim)
@@ -192,49 +210,49 @@ class CudaDenseDecode:
             context.set_option("tc_f32_activations", 1)
 
     # -- building blocks -------------------------------------------------------------------------
-    def _gemv(self, name: str, x: torch.Tensor, y: torch.Tensor, norm: torch.Tensor | None = None) -> None:
-        weight = self.weights.matrices[name]
-        kernel = self.kernels[weight.value_type()].inner
-        if norm is not None:
-            kernel.execute_rms_norm(weight, x, norm, self.geometry.eps, y, self.members)
-        elif self.members == 1:
-            kernel.execute_warp(weight, x.reshape(-1), y.reshape(-1))
-        else:
-            kernel.execute_warp_batch(weight, x, y, self.members)
-        self.launches_per_step += 2
+    def _fused(self, names_outputs, x: torch.Tensor, norm: torch.Tensor | None = None, swiglu: bool = False, accumulate: bool = False) -> None:
+        jobs = [(self.weights.matrices[name], y, accumulate) for name, y in names_outputs]
+        gemv_fused(self.context, jobs, x, self.members, norm, self.geometry.eps, swiglu)
+        self.launches_per_step += 1 + len(jobs) * (1 if self.members > 4 else (self.members + 3) // 4)
 
     def _all_reduce(self, t: torch.Tensor) -> None:
-        if self.group is not None and self.world > 1:
-            torch.distributed.all_reduce(t, group=self.group)
-            self.launches_per_step += 1
+        torch.distributed.all_reduce(t, group=self.group)
+        self.launches_per_step += 1
 
     def _layer(self, i: int) -> None:
         g, s, w = self.geometry, self.shapes, self.weights
-        self._gemv(f"blk.{i}.attn_q", self.hidden, self.q, w.vectors[f"blk.{i}.attn_norm"])
-        self._gemv(f"blk.{i}.attn_k", self.hidden, self.k, w.vectors[f"blk.{i}.attn_norm"])
-        self._gemv(f"blk.{i}.attn_v", self.hidden, self.v, w.vectors[f"blk.{i}.attn_norm"])
+        parallel = self.group is not None and self.world > 1
+        self._fused([(f"blk.{i}.attn_q", self.q), (f"blk.{i}.attn_k", self.k), (f"blk.{i}.attn_v", self.v)], self.hidden,
+                    norm=w.vectors[f"blk.{i}.attn_norm"])
         attention = attention_descriptor(g, self.members, s["q_heads"], s["kv_heads"], w.vectors[f"blk.{i}.attn_q_norm"],
                                          w.vectors[f"blk.{i}.attn_k_norm"], self.positions, self.k_cache[i], self.v_cache[i],
                                          self.max_context, self.active_context)
         self.ops.qk_norm_rope_append(attention, self.q, self.k, self.v)
         self.ops.attention_decode(attention, self.q, self.attended)
-        self._gemv(f"blk.{i}.attn_output", self.attended, self.projected)
-        self._all_reduce(self.projected)
-        self.ops.residual_add(self.hidden, self.projected)
-        self._gemv(f"blk.{i}.ffn_gate", self.hidden, self.gate, w.vectors[f"blk.{i}.ffn_norm"])
-        self._gemv(f"blk.{i}.ffn_up", self.hidden, self.up, w.vectors[f"blk.{i}.ffn_norm"])
-        self.ops.silu_mul(self.gate, self.up, self.activated, self.members, s["intermediate"], s["intermediate"])
-        self._gemv(f"blk.{i}.ffn_down", self.activated, self.projected)
-        self._all_reduce(self.projected)
-        self.ops.residual_add(self.hidden, self.projected)
-        self.launches_per_step += 6
+        self.launches_per_step += 3
+        if parallel:
+            # partial sums of the column-split projection: all-reduce, then the residual
+            self._fused([(f"blk.{i}.attn_output", self.projected)], self.attended)
+            self._all_reduce(self.projected)
+            self.ops.residual_add(self.hidden, self.projected)
+            self.launches_per_step += 1
+        else:
+            self._fused([(f"blk.{i}.attn_output", self.hidden)], self.attended, accumulate=True)      # hidden += W attended
+        self._fused([(f"blk.{i}.ffn_gate_up", self.gate_up)], self.hidden, norm=w.vectors[f"blk.{i}.ffn_norm"])
+        if parallel:
+            self._fused([(f"blk.{i}.ffn_down", self.projected)], self.gate_up, swiglu=True)
+            self._all_reduce(self.projected)
+            self.ops.residual_add(self.hidden, self.projected)
+            self.launches_per_step += 1
+        else:
+            self._fused([(f"blk.{i}.ffn_down", self.hidden)], self.gate_up, swiglu=True, accumulate=True)
 
     def _forward(self) -> None:
         self.launches_per_step = 0
         self.ops.embedding(self.weights.matrices["token_embd"], self.tokens, self.hidden)
         for i in range(self.geometry.layers):
             self._layer(i)
-        self._gemv("output", self.hidden, self.logits, self.weights.vectors["output_norm"])
+        self._fused([("output", self.logits)], self.hidden, norm=self.weights.vectors["output_norm"])
         self.launches_per_step += 1
         if self.world == 1:
             self.ops.argmax(self.logits, self.members, self.next_tokens)

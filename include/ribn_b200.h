@@ -215,6 +215,29 @@ int ribn_gemv_noalloc(int device, void *cuda_stream, const ribn_qweight *weight,
                       void *y_device, int y_dtype, uint64_t y_len, uint32_t members, int wait,
                       char *error_message, uint64_t error_capacity);
 
+/* ribn_gemv_fused: several projections of the same activations behind one activation pre-pass, with the
+ * operators the reference launches around them folded in -- the sequences of decode.rs:929-1052:
+ *   rms_norm -> q, k, v GEMVs          norm_weight given, three jobs
+ *   GEMV -> residual_add               job.accumulate = 1: y += W x (model_ops.rs:600-610)
+ *   silu_mul -> down GEMV              RIBN_FUSED_SWIGLU: x is [members][2K], rows [gate | up], the operand is
+ *                                      silu(gate) * up (model_ops.rs:316-328)
+ * All jobs share K; each is validated like ribn_gemv before anything is launched.  Served by the integer-dot
+ * kernel (1..4 member rows per launch) and the tensor-core decode kernel; shapes that only the f32 kernel
+ * serves are refused with RIBN_E_INVALID_ARGUMENT (use the separate calls). */
+typedef struct ribn_gemv_job {
+    uint32_t expected_type;      /* 0 = the weight's own type */
+    const ribn_qweight* weight;
+    void* y_device;              /* [members][N] */
+    int y_dtype;
+    uint64_t y_len;
+    int accumulate;              /* 0: y = W x;  1: y += W x */
+} ribn_gemv_job;
+#define RIBN_MAX_FUSED_JOBS 8u
+#define RIBN_FUSED_SWIGLU 1u
+int ribn_gemv_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, const void* x_device, int x_dtype,
+                    uint64_t x_len, const float* norm_weight_device, uint64_t norm_weight_len, float eps, uint32_t members,
+                    uint32_t flags);
+
 /* ---- decoder-layer operators between the GEMVs -------------------------------------------
  * The launches crates/nvidia/src/decode.rs:929-1052 (full_attention_layer) and :544-632 (run_step) make
  * between its projections, for a dense-attention layer with grouped-query attention.  All buffers are

@@ -146,6 +146,47 @@ def test_argmax_rules(ctx, ops):
     assert out.cpu().tolist()[1:] == [7, 3, 0, 151935]
 
 
+# ---- ribn_gemv_fused: one pre-pass, several projections, residual and silu_mul folded in
+@pytest.mark.parametrize("members,x_dtype", [(1, torch.float32), (3, torch.float32), (4, torch.bfloat16), (9, torch.bfloat16), (40, torch.bfloat16)])
+def test_gemv_fused_equals_the_separate_calls(ctx, members, x_dtype):
+    k, inter = 1024, 768
+    rng = np.random.default_rng(members)
+    wq = synth.random_weight(12, k, 300, seed=1)
+    wv = synth.random_weight(14, k, 130, seed=2)
+    wd = synth.random_weight(14, inter, k, seed=3)
+    upload = lambda w, vt, kk, n: engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [kk, n]), vt, device(ctx, w))
+    q_w, v_w, d_w = upload(wq, 12, k, 300), upload(wv, 14, k, 130), upload(wd, 14, inter, k)
+    x = device(ctx, rng.standard_normal((members, k)).astype(np.float32) * 2, x_dtype)
+    gain = (1 + 0.02 * rng.standard_normal(k)).astype(np.float32)
+    x_seen = oracle.rms_norm(x.float().cpu().numpy(), gain, 1e-6)
+    # norm -> two projections of different formats
+    yq = torch.full((members, 300), float("nan"), device=ctx.device)
+    yv = torch.full((members, 130), float("nan"), device=ctx.device)
+    decode.gemv_fused(ctx, [(q_w, yq, False), (v_w, yv, False)], x, members, norm=device(ctx, gain), eps=1e-6)
+    ctx.synchronize()
+    for vt, w, n, y in ((12, wq, 300, yq), (14, wv, 130, yv)):
+        err = oracle.max_rel_error(y.cpu().numpy().astype(np.float64), oracle.gemv_f64(vt, w, k, n, x_seen), oracle.gemv_scale(vt, w, k, n, x_seen))
+        assert err <= 2e-3
+    # silu_mul -> down projection -> residual
+    gate_up = device(ctx, rng.standard_normal((members, 2 * inter)).astype(np.float32) * 2, x_dtype)
+    host_gu = gate_up.float().cpu().numpy()
+    act = layer_np.silu_mul(host_gu[:, :inter], host_gu[:, inter:])
+    residual = rng.standard_normal((members, k)).astype(np.float32)
+    y = device(ctx, residual)
+    decode.gemv_fused(ctx, [(d_w, y, True)], gate_up, members, swiglu=True)
+    ctx.synchronize()
+    ref = oracle.gemv_f64(14, wd, inter, k, act)
+    err = oracle.max_rel_error(y.cpu().numpy().astype(np.float64) - residual, ref, oracle.gemv_scale(14, wd, inter, k, act))
+    assert err <= 2e-3 + 1e-6
+    # rejections come before any launch
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+        decode.gemv_fused(ctx, [(q_w, yq, False), (d_w, y, False)], x, members)       # different input sizes
+    assert e.value.kind == "InputLength"
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+        decode.gemv_fused(ctx, [(q_w, yq[:, :-1].contiguous(), False)], x, members)
+    assert e.value.kind == "OutputLength"
+
+
 # ---- the decode loop on a small random model
 def small_model(ctx, geometry, seed=0):
     shapes = decode.local_shapes(geometry, 1, 0)
@@ -158,6 +199,10 @@ def small_model(ctx, geometry, seed=0):
         encoded = synth.random_weight(vt, k, n, seed=seed * 100 + salt)
         weights.matrices[name] = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new(name, [k, n]), vt, device(ctx, encoded))
         host[name] = oracle.dequantize(vt, encoded, k, n).reshape(n, k)
+        if kind == "ffn_gate_up":   # the decoder stores gate rows then up rows as one matrix; the host model keeps them apart
+            half = n // 2
+            host[name.replace("ffn_gate_up", "ffn_gate")] = host[name][:half]
+            host[name.replace("ffn_gate_up", "ffn_up")] = host[name][half:]
 
     def vector(name, length):
         host[name] = (1 + 0.02 * rng.standard_normal(length)).astype(np.float32)
@@ -167,7 +212,7 @@ def small_model(ctx, geometry, seed=0):
     matrix("output", "output", 2)
     vector("output_norm", geometry.hidden)
     for i in range(geometry.layers):
-        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")):
+        for j, kind in enumerate(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate_up", "ffn_down")):
             matrix(f"blk.{i}.{kind}", kind, 10 + 8 * i + j)
         vector(f"blk.{i}.attn_norm", geometry.hidden)
         vector(f"blk.{i}.ffn_norm", geometry.hidden)
