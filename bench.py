@@ -145,9 +145,10 @@ def run_reference(args, rank: int, world: int) -> None:
 
 
 # DRAM bytes moved per algorithmic byte by the tensor-core decode kernel, from an ncu capture of one launch
-# (dram__bytes_read.sum + dram__bytes_write.sum over the encoded weight bytes + activations + outputs;
-# the summary of that capture is committed under profiles/).  None until a capture exists.
-TC_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# (dram__bytes_read.sum + dram__bytes_write.sum = 28.53 MB over 28.44 MB of encoded weights, activations and
+# outputs for Q4_K 12288x4096 with 16 member rows; profiles/qgemv_tc_q4k_12288x4096_m16.md).  The kernel reads
+# every weight byte once whatever the shape, so the ratio is applied to the sweep's mean call.
+TC_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.003
 
 
 def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
