@@ -134,8 +134,9 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
                                                                              long long max_context, int chunk, float scale) {
-    __shared__ __align__(16) __half k_tile[kAttnTile * kAttnKStride];
-    __shared__ __align__(16) __half v_tile[kAttnTile * kAttnHeadDim];
+    // Two tiles of each: the next one streams in (cp.async) while the warps work on the current one.
+    __shared__ __align__(16) __half k_tiles[2][kAttnTile * kAttnKStride];
+    __shared__ __align__(16) __half v_tiles[2][kAttnTile * kAttnHeadDim];
     __shared__ __align__(16) float q_rows[kAttnMaxGroup * kAttnHeadDim];
     const int kv_head = blockIdx.x;
     const int member = blockIdx.y;
@@ -157,22 +158,40 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     float running_max = -INFINITY, running_sum = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-    for (int t0 = begin; t0 < end; t0 += kAttnTile) {
+    // Tile loads: 32 tokens x 128 halves each, 16 bytes per request; rows past the range are zero-filled.
+    auto request_tile = [&](int buffer, int t0) {
         const int valid = min(kAttnTile, end - t0);
-        __syncthreads();   // previous tile fully consumed (and q_rows written, first time round)
-        // Tile loads: 32 tokens x 128 halves each, 16 bytes per thread and step.
         for (int i = threadIdx.x; i < kAttnTile * (kAttnHeadDim / 8); i += blockDim.x) {
             const int row = i / (kAttnHeadDim / 8);
             const int chunk = i % (kAttnHeadDim / 8);
-            uint4 kw = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
+            __half* kd = k_tiles[buffer] + row * kAttnKStride + 8 * chunk;
+            __half* vd = v_tiles[buffer] + row * kAttnHeadDim + 8 * chunk;
             if (row < valid) {
-                kw = *reinterpret_cast<const uint4*>(k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk);
-                vw = *reinterpret_cast<const uint4*>(v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk);
+                const __half* ks = k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk;
+                const __half* vs = v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(kd))), "l"(ks) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(vd))), "l"(vs) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4*>(k_tile + row * kAttnKStride + 8 * chunk) = kw;
-            *reinterpret_cast<uint4*>(v_tile + row * kAttnHeadDim + 8 * chunk) = vw;
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (begin < end) request_tile(0, begin);
+
+    int buffer = 0;
+    for (int t0 = begin; t0 < end; t0 += kAttnTile, buffer ^= 1) {
+        const int valid = min(kAttnTile, end - t0);
+        if (t0 + kAttnTile < end) {
+            request_tile(buffer ^ 1, t0 + kAttnTile);   // its previous contents were consumed before the barrier that ended the last round
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();   // this tile has landed for every thread (and q_rows is written, first time round)
+        const __half* k_tile = k_tiles[buffer];
+        const __half* v_tile = v_tiles[buffer];
         if (warp < group) {
             // scores: lane = token of the tile
             const float* qv = q_rows + warp * kAttnHeadDim;
@@ -222,6 +241,7 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                 acc[3] = fmaf(pt, v23.y, acc[3]);
             }
         }
+        __syncthreads();   // every warp is done with this buffer before the next round refills it
     }
     if (warp < group) {
         const size_t slot = (static_cast<size_t>(member) * q_heads + q_head) * splits + split;
