@@ -34,6 +34,7 @@ struct ribn_ctx {
     int tc_split_operands = 0;      // 1 = bf16 batches <= 64 use the split-operand GEMM (the prefill kernel) instead of the f16 decode kernel
     int tc_trace = 0;               // 1 = the decode tensor-core kernel records pipeline clock stamps in the workspace tail
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
+    int dp4a_prepass = 1;           // 0 = calls of 1..4 rows pack their activations inside the GEMV kernel (measured slower: see the header)
     int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
     int tc_min_members = 5;         // batches of at least this many rows go to the tensor-core kernel
     std::string message;
@@ -301,6 +302,7 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.device_status = ctx->device_status;
     a.sm_count = ctx->sm_count;
     a.variant = ctx->variant;
+    a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
     a.stream = ctx->stream;
     // Path 0: tensor-core decode kernel for batches (RMSNorm, when asked for, is applied in f32 by its
     // activation pre-pass).  Its operands are f16: bf16 activations convert exactly and the weights'
@@ -316,6 +318,20 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     const uint64_t stride = ribn::packed_activation_stride(ribn::padded_k(a.k));
     if (ctx->gemv_path != 1 && ribn::gemv_dp4a_fits(a.value_type, a.k, members_per_launch) &&
         stride * members <= ctx->workspace_bytes) {
+        if (members <= 4 && ctx->dp4a_prepass == 0) {
+            // Up to four member rows: the kernel packs the activations itself (no pre-pass launch, no dependency on it).
+            a.members = static_cast<int>(members);
+            a.x = x;
+            a.y = y;
+            a.pack_mode = norm_weight != nullptr ? 2 : 1;
+            a.norm_weight = norm_weight;
+            a.eps = eps;
+            bool handled = false;
+            const cudaError_t e = ribn::launch_gemv_dp4a(a, &handled);
+            if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+            if (!handled) return record(ctx, fail(RIBN_E_DRIVER, "integer-dot GEMV refused a shape it had accepted"));
+            return RIBN_OK;
+        }
         cudaError_t e = ribn::launch_quantize_activations(x, a.x_bf16, norm_weight, eps, ctx->workspace,
                                                           static_cast<int>(members), a.k, ctx->stream);
         if (e != cudaSuccess) return record_cuda(ctx, e, "activation packing launch");
@@ -385,9 +401,13 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
     const uint64_t stride = ribn::packed_activation_stride(ribn::padded_k(static_cast<int>(k)));
     if (ctx->gemv_path == 1 || !all_dp4a || stride * members > ctx->workspace_bytes)
         return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "the fused call needs a shape the packed-activation kernels serve"));
-    cudaError_t e = ribn::launch_quantize_activations(x, x_bf16, norm_weight, eps, ctx->workspace, static_cast<int>(members),
-                                                      static_cast<int>(k), ctx->stream, swiglu);
-    if (e != cudaSuccess) return record_cuda(ctx, e, "activation packing launch");
+    const bool in_kernel = members <= 4 && ctx->dp4a_prepass == 0;
+    if (!in_kernel) {
+        const cudaError_t e = ribn::launch_quantize_activations(x, x_bf16, norm_weight, eps, ctx->workspace, static_cast<int>(members),
+                                                                static_cast<int>(k), ctx->stream, swiglu);
+        if (e != cudaSuccess) return record_cuda(ctx, e, "activation packing launch");
+    }
+    cudaError_t e = cudaSuccess;
     for (uint32_t j = 0; j < job_count; ++j) {
         GemvArgs a{};
         a.weights = static_cast<const uint8_t*>(jobs[j].weight->data);
@@ -401,10 +421,17 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         a.device_status = ctx->device_status;
         a.sm_count = ctx->sm_count;
         a.variant = ctx->variant;
+        a.trace = nullptr;
         a.stream = ctx->stream;
         for (uint32_t m0 = 0; m0 < members; m0 += 4) {
             a.members = static_cast<int>(members - m0 < 4 ? members - m0 : 4);
             a.x = static_cast<const uint8_t*>(ctx->workspace) + static_cast<uint64_t>(m0) * stride;
+            if (in_kernel) {
+                a.x = x;
+                a.pack_mode = swiglu ? 3 : (norm_weight != nullptr ? 2 : 1);
+                a.norm_weight = norm_weight;
+                a.eps = eps;
+            }
             a.y = static_cast<uint8_t*>(jobs[j].y_device) + static_cast<uint64_t>(m0) * ns[j] * dtype_bytes(jobs[j].y_dtype);
             bool handled = false;
             e = ribn::launch_gemv_dp4a(a, &handled);
@@ -565,6 +592,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {
         ctx->tc_row_copies = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "dp4a_prepass") == 0 && (value == 0 || value == 1)) {
+        ctx->dp4a_prepass = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "pdl") == 0 && (value == 0 || value == 1)) {

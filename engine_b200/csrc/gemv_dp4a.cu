@@ -32,6 +32,7 @@
 // prologue.
 #include "formats.cuh"
 #include "internal.h"
+#include "pack_activations.cuh"
 #include "pipeline.cuh"
 
 namespace ribn {
@@ -53,8 +54,15 @@ struct Dp4aParams {
     const uint8_t* w;
     unsigned long long w_bytes;
     unsigned long long row_bytes;
-    const uint8_t* xq;             // packed activations (quantize.cu), `x_stride` bytes per member
+    const uint8_t* xq;             // packed activations (quantize.cu), `x_stride` bytes per member; used when pack_mode < 0
     unsigned long long x_stride;
+    // pack_mode >= 0: the kernel packs the activations itself (every CTA its own copy in shared memory: a few thousand
+    // values, cheaper than a separate launch and the dependency on it).  0 plain, 1 RMSNorm first, 2 silu(gate) * up.
+    int pack_mode;
+    const void* x_raw;             // [members][k] (mode 2: [members][2k]) f32 or bf16
+    int x_raw_bf16;
+    const float* norm_weight;
+    float eps;
     void* y;
     int k;
     int n;
@@ -64,7 +72,17 @@ struct Dp4aParams {
     int accumulate;                // y += W x
     int stages;
     int* status;
+    long long* trace;              // diagnostics (option tc_trace): wall-clock stamps of CTA 0, or null
 };
+
+// trace[event] = globaltimer, CTA 0 only.
+__device__ __forceinline__ void wall_stamp(const Dp4aParams& p, int event) {
+    if (p.trace != nullptr && blockIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace[event] = static_cast<long long>(t);
+    }
+}
 
 // Lanes per super-block and the geometry of a lane's 16 quant bytes.
 template <uint32_t FMT>
@@ -254,6 +272,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
     const int lane = threadIdx.x & 31;
     const int stages = p.stages;
     pdl_launch_dependents();
+    if (threadIdx.x == 0) wall_stamp(p, 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -280,7 +299,10 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
         // previous kernel of the stream, which this one may overlap.
         const int prefetch = min(total, stages);
         auto request_activations = [&]() {
+            if (lane == 0) wall_stamp(p, 1);
+            if (p.pack_mode >= 0) return;   // the consumers pack the activations themselves
             pdl_wait_prior();
+            if (lane == 0) wall_stamp(p, 2);
             if (lane == 0) {
                 // Packed activations of this launch's members: one bulk copy (a multiple of 576 bytes).
                 const uint32_t bytes = static_cast<uint32_t>(static_cast<unsigned long long>(min(p.members, MT)) * p.x_stride);
@@ -332,11 +354,22 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
         return;
     }
 
-    // ---------------- consumers: wait for the packed activations ----------------
-    if (!mbar_wait_bounded(x_bar, 0)) {
+    // ---------------- consumers: the packed activations, fetched or made here ----------------
+    if (p.pack_mode >= 0) {
+        pdl_wait_prior();   // the raw activations may be the previous kernel's output
+        const int rows = min(p.members, MT);
+        const size_t row_elements = static_cast<size_t>(p.k) * (p.pack_mode == 2 ? 2 : 1);
+        for (int m = 0; m < rows; ++m) {
+            const AnyRow row{static_cast<const uint8_t*>(p.x_raw) + m * row_elements * (p.x_raw_bf16 ? 2 : 4), p.x_raw_bf16};
+            pack_activation_row<kConsumerThreads>(row, p.pack_mode, p.norm_weight, p.eps, const_cast<uint8_t*>(xs) + m * p.x_stride, p.k, kpad,
+                                                  red, static_cast<int>(threadIdx.x), [] { named_barrier_sync(1, kConsumerThreads); });
+        }
+        named_barrier_sync(1, kConsumerThreads);
+    } else if (!mbar_wait_bounded(x_bar, 0)) {
         atomicExch(p.status, kDeviceWaitTimeout);
         return;
     }
+    if (threadIdx.x == 0) wall_stamp(p, 3);
 
     // ---------------- consumers: main loop ----------------
     const int wr = warp / kWK;
@@ -367,6 +400,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
                 atomicExch(p.status, kDeviceWaitTimeout);
                 return;
             }
+            if (threadIdx.x == 0 && it < 12) wall_stamp(p, 8 + 2 * it);
             const uint8_t* stage = ring + static_cast<size_t>(s) * P::kStageBytes + wr * kRW * P::kSlot;
 
             // Scale tables: one lane per (row, super-block) of this warp's share of the stage.
@@ -447,6 +481,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
+            if (threadIdx.x == 0 && it < 12) wall_stamp(p, 9 + 2 * it);
         }
 
         if (kWK == 1) {
@@ -506,7 +541,9 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const Dp4aParams p)
                 }
             }
         }
+        if (threadIdx.x == 0 && tile < 8) wall_stamp(p, 40 + tile);
     }
+    if (threadIdx.x == 0) wall_stamp(p, 4);
 }
 
 constexpr size_t kSmemLimit = 227 * 1024;
@@ -531,6 +568,16 @@ cudaError_t launch(const GemvArgs& a, bool* handled) {
         *handled = false;  // activations too large to stage in shared memory: the caller uses the f32 kernel
         return cudaSuccess;
     }
+    // Tuning variants 4 and 5 (option "gemv_variant"): three or four CTAs per SM with shorter rings -- a CTA of the
+    // sweep's shapes consumes only a handful of stages, so residency may matter more than ring depth.
+    if (MT != 4 && (a.variant == 4 || a.variant == 5)) {
+        const int want = a.variant == 4 ? 3 : 4;
+        const size_t share = (kSmemLimit - 1024 * want) / want;
+        if (fixed + 2 * static_cast<size_t>(P::kStageBytes) <= share) {
+            ctas = want;
+            budget = share;
+        }
+    }
     int stages = static_cast<int>((budget - fixed) / P::kStageBytes);
     if (stages > 6) stages = 6;
     const size_t smem = fixed + static_cast<size_t>(stages) * P::kStageBytes;
@@ -548,6 +595,11 @@ cudaError_t launch(const GemvArgs& a, bool* handled) {
     p.row_bytes = a.value_type == kQ8_0 ? static_cast<unsigned long long>(a.k / 32) * 34
                                         : static_cast<unsigned long long>(a.k / kSuperBlock) * Format<FMT>::kBytes;
     p.xq = static_cast<const uint8_t*>(a.x);
+    p.pack_mode = a.pack_mode - 1;
+    p.x_raw = a.x;
+    p.x_raw_bf16 = a.x_bf16 ? 1 : 0;
+    p.norm_weight = a.norm_weight;
+    p.eps = a.eps;
     p.x_stride = packed_activation_stride(kpad);
     p.y = a.y;
     p.k = a.k;
@@ -558,6 +610,7 @@ cudaError_t launch(const GemvArgs& a, bool* handled) {
     p.accumulate = a.accumulate ? 1 : 0;
     p.stages = stages;
     p.status = a.device_status;
+    p.trace = a.trace;
     int grid = a.sm_count * ctas;
     if (grid > a.n) grid = a.n;
     *handled = true;

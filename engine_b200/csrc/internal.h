@@ -47,9 +47,15 @@ struct GemvArgs {
     bool y_bf16;
     int members;              // 1..8 per launch
     bool accumulate;          // y += W x instead of y = W x (integer-dot kernel only)
+    // Integer-dot kernel: pack_mode 0 -> x is packed activations (quantize.cu); 1 / 2 / 3 -> x is the raw rows and the
+    // kernel packs them itself (plain / RMSNorm with norm_weight, eps / silu(gate) * up of [gate | up] rows).
+    int pack_mode;
+    const float* norm_weight;
+    float eps;
     int* device_status;
     int sm_count;
     int variant;              // tuning variant, 0 = default
+    long long* trace;         // diagnostics: wall-clock stamps of one CTA of the integer-dot kernel, or null
     cudaStream_t stream;
 };
 

@@ -25,6 +25,7 @@
 
 #include "formats.cuh"
 #include "internal.h"
+#include "pipeline.cuh"
 
 namespace ribn {
 namespace {
@@ -34,6 +35,8 @@ template <uint32_t FMT>
 __global__ void __launch_bounds__(256) embedding_kernel(const uint8_t* __restrict__ w, const uint32_t* __restrict__ tokens,
                                                         float* __restrict__ out, int k, unsigned int vocabulary,
                                                         unsigned long long row_bytes, int nsb) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     using F = Format<FMT>;
     const int lane = threadIdx.x & 31;
     const int sb = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -62,6 +65,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
                                                                   const int* __restrict__ positions, int q_heads, int kv_heads,
                                                                   int head_dim, int rot_pairs, float base, __half* __restrict__ k_cache,
                                                                   __half* __restrict__ v_cache, long long max_context) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     __shared__ float values[256];
     __shared__ float warp_sums[8];
     const int member = blockIdx.y;
@@ -134,6 +139,8 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
                                                                              long long max_context, int chunk, float scale) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     // Two tiles of each: the next one streams in (cp.async) while the warps work on the current one.
     __shared__ __align__(16) __half k_tiles[2][kAttnTile * kAttnKStride];
     __shared__ __align__(16) __half v_tiles[2][kAttnTile * kAttnHeadDim];
@@ -256,6 +263,8 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
 // grid (q_heads, members), 128 threads: merges the splits of one query head.
 __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                          float* __restrict__ out, int q_heads, int splits) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     const size_t base = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * splits;
     float global_max = -INFINITY;
     for (int s = 0; s < splits; ++s) global_max = fmaxf(global_max, part_ml[(base + s) * 2]);
@@ -274,6 +283,8 @@ __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const f
 // halves of one [members][2 * length] GEMV output), out rows are `length` apart.
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
                                                        unsigned long long length, unsigned long long in_stride, unsigned long long total) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
         const unsigned long long member = i / length;
@@ -284,6 +295,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 }
 
 __global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ y, const float* __restrict__ x, unsigned long long total) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<unsigned long long>(gridDim.x) * blockDim.x)
         y[i] += x[i];
@@ -298,6 +311,8 @@ __device__ __forceinline__ unsigned int logit_key(float value) {
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, unsigned int* __restrict__ out, unsigned long long length) {
+    pdl_launch_dependents();
+    pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     __shared__ unsigned int keys[32];
     __shared__ unsigned int indices[32];
     const float* row = logits + static_cast<size_t>(blockIdx.x) * length;
@@ -349,22 +364,19 @@ cudaError_t launch_embedding(const uint8_t* weights, uint32_t value_type, int k,
     const dim3 grid((nsb + 7) / 8, members);
     const unsigned long long blocks_per_row = value_type == kQ8_0 ? k / 32 : nsb;
     switch (value_type) {
-        case kQ4_K: embedding_kernel<kQ4_K><<<grid, 256, 0, stream>>>(weights, tokens, out, k, vocabulary, blocks_per_row * 144, nsb); break;
-        case kQ5_K: embedding_kernel<kQ5_K><<<grid, 256, 0, stream>>>(weights, tokens, out, k, vocabulary, blocks_per_row * 176, nsb); break;
-        case kQ6_K: embedding_kernel<kQ6_K><<<grid, 256, 0, stream>>>(weights, tokens, out, k, vocabulary, blocks_per_row * 210, nsb); break;
-        case kQ8_0: embedding_kernel<kQ8_0><<<grid, 256, 0, stream>>>(weights, tokens, out, k, vocabulary, blocks_per_row * 34, nsb); break;
+        case kQ4_K: return launch_kernel(embedding_kernel<kQ4_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 144ull, nsb);
+        case kQ5_K: return launch_kernel(embedding_kernel<kQ5_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 176ull, nsb);
+        case kQ6_K: return launch_kernel(embedding_kernel<kQ6_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 210ull, nsb);
+        case kQ8_0: return launch_kernel(embedding_kernel<kQ8_0>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 34ull, nsb);
         default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& a) {
     const dim3 grid(a.q_heads + 2 * a.kv_heads, a.members);
-    qk_norm_rope_append_kernel<<<grid, a.head_dim, 0, a.stream>>>(a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions, a.q_heads,
-                                                                   a.kv_heads, a.head_dim, a.rot_dims / 2, a.rope_base,
-                                                                   static_cast<__half*>(a.k_cache), static_cast<__half*>(a.v_cache),
-                                                                   a.max_context);
-    return cudaGetLastError();
+    return launch_kernel(qk_norm_rope_append_kernel, grid, dim3(a.head_dim), 0, a.stream, a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions,
+                         a.q_heads, a.kv_heads, a.head_dim, a.rot_dims / 2, a.rope_base, static_cast<__half*>(a.k_cache),
+                         static_cast<__half*>(a.v_cache), a.max_context);
 }
 
 int attention_splits(int members, int kv_heads, long long active_context, int sm_count) {
@@ -390,13 +402,12 @@ cudaError_t launch_attention_decode(const LayerAttentionArgs& a, float* out, voi
     float* part_o = static_cast<float*>(scratch);
     float* part_ml = part_o + static_cast<size_t>(a.members) * a.q_heads * splits * kAttnHeadDim;
     const float scale = 1.0f / sqrtf(static_cast<float>(a.head_dim));
-    attention_split_kernel<<<dim3(a.kv_heads, a.members, splits), group * 32, 0, a.stream>>>(
-        a.q, static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache), a.positions, part_o, part_ml, a.q_heads,
-        a.kv_heads, a.max_context, static_cast<int>(chunk), scale);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_kernel(attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
+                                  static_cast<const float*>(a.q), static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache),
+                                  a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale);
     if (e != cudaSuccess) return e;
-    attention_combine_kernel<<<dim3(a.q_heads, a.members), kAttnHeadDim, 0, a.stream>>>(part_o, part_ml, out, a.q_heads, splits);
-    return cudaGetLastError();
+    return launch_kernel(attention_combine_kernel, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
+                         static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);
 }
 
 cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t members, uint64_t length, uint64_t in_stride,
@@ -404,20 +415,19 @@ cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint
     const unsigned long long total = members * length;
     unsigned long long blocks = (total + 255) / 256;
     if (blocks > static_cast<unsigned long long>(sm_count) * 8) blocks = static_cast<unsigned long long>(sm_count) * 8;
-    silu_mul_kernel<<<static_cast<unsigned>(blocks ? blocks : 1), 256, 0, stream>>>(gate, up, out, length, in_stride, total);
-    return cudaGetLastError();
+    return launch_kernel(silu_mul_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, gate, up, out,
+                         static_cast<unsigned long long>(length), static_cast<unsigned long long>(in_stride), total);
 }
 
 cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream) {
     unsigned long long blocks = (total + 255) / 256;
     if (blocks > static_cast<unsigned long long>(sm_count) * 8) blocks = static_cast<unsigned long long>(sm_count) * 8;
-    residual_add_kernel<<<static_cast<unsigned>(blocks ? blocks : 1), 256, 0, stream>>>(y, x, total);
-    return cudaGetLastError();
+    return launch_kernel(residual_add_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, y, x,
+                         static_cast<unsigned long long>(total));
 }
 
 cudaError_t launch_argmax(const float* logits, int members, uint64_t length, uint32_t* out, cudaStream_t stream) {
-    argmax_kernel<<<members, 1024, 0, stream>>>(logits, out, length);
-    return cudaGetLastError();
+    return launch_kernel(argmax_kernel, dim3(members), dim3(1024), 0, stream, logits, out, static_cast<unsigned long long>(length));
 }
 
 }  // namespace ribn

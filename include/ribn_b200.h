@@ -103,6 +103,10 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "tc_f32_activations": 1 = f32 batches may use it too (they are rounded to f16; default 0);
  *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
  *                   kernel) instead of the f16 decode kernel (default 0);
+ *   "dp4a_prepass": 0 = calls of 1..4 rows pack their activations inside the integer-dot kernel, every CTA its own
+ *                   copy, instead of in a launch of their own (default 1: with dependent launch the separate pre-pass
+ *                   overlaps the kernel before and the weight prefetch after it; packing in the kernel measured equal for
+ *                   one row and 5-30 % slower for four rows and for K = 12288);
  *   "pdl":          0 = launch the GEMV kernels without programmatic dependent launch (process-wide; default 1:
  *                   a kernel's prologue and weight prefetch overlap the tail of the kernel before it);
  *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);

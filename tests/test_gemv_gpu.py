@@ -312,6 +312,30 @@ def test_f32_batches_on_the_tensor_core_kernel(ctx, vt, fused):
     check(vt, w, k, n, y.cpu().numpy().astype(np.float64), seen)
 
 
+# ---- calls of 1..4 rows can pack their activations inside the integer-dot kernel (option dp4a_prepass = 0)
+@pytest.mark.parametrize("vt", [8, 12, 13, 14])
+@pytest.mark.parametrize("members,x_dtype,fused", [(1, torch.float32, False), (3, torch.bfloat16, False), (4, torch.float32, True), (2, torch.bfloat16, True)])
+def test_activations_packed_inside_the_kernel(ctx, vt, members, x_dtype, fused):
+    k, n = 2304, 333
+    w = synth.random_weight(vt, k, n, seed=vt + members)
+    weight = upload(ctx, vt, w, k, n)
+    rng = np.random.default_rng(members)
+    x = torch.from_numpy((rng.standard_normal((members, k)) * 2.0).astype(np.float32)).to(ctx.device).to(x_dtype)
+    gain_host = (1.0 + 0.02 * rng.standard_normal(k)).astype(np.float32)
+    y = torch.full((members, n), float("nan"), device=ctx.device)
+    ctx.set_option("dp4a_prepass", 0)
+    try:
+        if fused:
+            KERNELS[vt].from_context(ctx).execute_rms_norm(weight, x, torch.from_numpy(gain_host).to(ctx.device), 1e-6, y, members)
+        else:
+            KERNELS[vt].from_context(ctx).execute_warp_batch(weight, x, y, members)
+        ctx.synchronize()
+    finally:
+        ctx.set_option("dp4a_prepass", 1)
+    seen = x.float().cpu().numpy()
+    check(vt, w, k, n, y.cpu().numpy().astype(np.float64), oracle.rms_norm(seen, gain_host, 1e-6) if fused else seen)
+
+
 def test_fused_rejections(ctx):
     k, n = 512, 4
     w = synth.random_weight(12, k, n, seed=1)
