@@ -598,7 +598,7 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
         ctx->dp4a_prepass = static_cast<int>(value);
         return RIBN_OK;
     }
-    if (std::strcmp(name, "pdl") == 0 && (value == 0 || value == 1)) {
+    if (std::strcmp(name, "pdl") == 0 && value >= 0 && value <= 2) {
         ribn::pdl_switch() = static_cast<int>(value);   // process-wide
         return RIBN_OK;
     }

@@ -12,12 +12,16 @@ namespace ribn {
 // attribute below, a kernel's launch latency, prologue and weight prefetch overlap its predecessor's tail.
 // Weights are never written by a kernel, so reading them before the wait is safe.
 inline int& pdl_switch() {
-    static int enabled = 1;
+    static int enabled = 2;
     return enabled;
 }
 
+// pdl_switch(): 0 = off, 1 = every kernel of the path, 2 = the GEMV kernels and their pre-passes only (default;
+// measured on the decode loop: 233 tok/s off, 266 with every kernel, 274 with the GEMV kernels only -- the small
+// layer operators gain nothing from starting early and hold SM slots while they wait).
 template <typename... KernelArgs, typename... Args>
-cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+cudaError_t launch_kernel_if(bool dependent, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
     cudaLaunchConfig_t config{};
     config.gridDim = grid;
     config.blockDim = block;
@@ -27,8 +31,13 @@ cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = pdl_switch() != 0 ? 1 : 0;
+    config.numAttrs = dependent ? 1 : 0;
     return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return launch_kernel_if(pdl_switch() != 0, kernel, grid, block, smem, stream, args...);
 }
 
 // Device status word values written by kernels whose bounded waits ran out.

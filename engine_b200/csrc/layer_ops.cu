@@ -364,17 +364,17 @@ cudaError_t launch_embedding(const uint8_t* weights, uint32_t value_type, int k,
     const dim3 grid((nsb + 7) / 8, members);
     const unsigned long long blocks_per_row = value_type == kQ8_0 ? k / 32 : nsb;
     switch (value_type) {
-        case kQ4_K: return launch_kernel(embedding_kernel<kQ4_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 144ull, nsb);
-        case kQ5_K: return launch_kernel(embedding_kernel<kQ5_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 176ull, nsb);
-        case kQ6_K: return launch_kernel(embedding_kernel<kQ6_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 210ull, nsb);
-        case kQ8_0: return launch_kernel(embedding_kernel<kQ8_0>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 34ull, nsb);
+        case kQ4_K: return launch_kernel_if(pdl_switch() == 1, embedding_kernel<kQ4_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 144ull, nsb);
+        case kQ5_K: return launch_kernel_if(pdl_switch() == 1, embedding_kernel<kQ5_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 176ull, nsb);
+        case kQ6_K: return launch_kernel_if(pdl_switch() == 1, embedding_kernel<kQ6_K>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 210ull, nsb);
+        case kQ8_0: return launch_kernel_if(pdl_switch() == 1, embedding_kernel<kQ8_0>, grid, dim3(256), 0, stream, weights, tokens, out, k, vocabulary, blocks_per_row * 34ull, nsb);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& a) {
     const dim3 grid(a.q_heads + 2 * a.kv_heads, a.members);
-    return launch_kernel(qk_norm_rope_append_kernel, grid, dim3(a.head_dim), 0, a.stream, a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions,
+    return launch_kernel_if(pdl_switch() == 1, qk_norm_rope_append_kernel, grid, dim3(a.head_dim), 0, a.stream, a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions,
                          a.q_heads, a.kv_heads, a.head_dim, a.rot_dims / 2, a.rope_base, static_cast<__half*>(a.k_cache),
                          static_cast<__half*>(a.v_cache), a.max_context);
 }
@@ -402,11 +402,11 @@ cudaError_t launch_attention_decode(const LayerAttentionArgs& a, float* out, voi
     float* part_o = static_cast<float*>(scratch);
     float* part_ml = part_o + static_cast<size_t>(a.members) * a.q_heads * splits * kAttnHeadDim;
     const float scale = 1.0f / sqrtf(static_cast<float>(a.head_dim));
-    cudaError_t e = launch_kernel(attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
+    cudaError_t e = launch_kernel_if(pdl_switch() == 1, attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
                                   static_cast<const float*>(a.q), static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache),
                                   a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale);
     if (e != cudaSuccess) return e;
-    return launch_kernel(attention_combine_kernel, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
+    return launch_kernel_if(pdl_switch() == 1, attention_combine_kernel, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
                          static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);
 }
 
@@ -415,19 +415,19 @@ cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint
     const unsigned long long total = members * length;
     unsigned long long blocks = (total + 255) / 256;
     if (blocks > static_cast<unsigned long long>(sm_count) * 8) blocks = static_cast<unsigned long long>(sm_count) * 8;
-    return launch_kernel(silu_mul_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, gate, up, out,
+    return launch_kernel_if(pdl_switch() == 1, silu_mul_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, gate, up, out,
                          static_cast<unsigned long long>(length), static_cast<unsigned long long>(in_stride), total);
 }
 
 cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream) {
     unsigned long long blocks = (total + 255) / 256;
     if (blocks > static_cast<unsigned long long>(sm_count) * 8) blocks = static_cast<unsigned long long>(sm_count) * 8;
-    return launch_kernel(residual_add_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, y, x,
+    return launch_kernel_if(pdl_switch() == 1, residual_add_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, y, x,
                          static_cast<unsigned long long>(total));
 }
 
 cudaError_t launch_argmax(const float* logits, int members, uint64_t length, uint32_t* out, cudaStream_t stream) {
-    return launch_kernel(argmax_kernel, dim3(members), dim3(1024), 0, stream, logits, out, static_cast<unsigned long long>(length));
+    return launch_kernel_if(pdl_switch() == 1, argmax_kernel, dim3(members), dim3(1024), 0, stream, logits, out, static_cast<unsigned long long>(length));
 }
 
 }  // namespace ribn

@@ -107,8 +107,9 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *                   copy, instead of in a launch of their own (default 1: with dependent launch the separate pre-pass
  *                   overlaps the kernel before and the weight prefetch after it; packing in the kernel measured equal for
  *                   one row and 5-30 % slower for four rows and for K = 12288);
- *   "pdl":          0 = launch the GEMV kernels without programmatic dependent launch (process-wide; default 1:
- *                   a kernel's prologue and weight prefetch overlap the tail of the kernel before it);
+ *   "pdl":          programmatic dependent launch, process-wide: 0 = off, 1 = every kernel of the path, 2 = the GEMV
+ *                   kernels and their pre-passes only (default: a kernel's prologue and weight prefetch overlap the
+ *                   tail of the kernel before it; the small layer operators measured slower with it);
  *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);
  *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
  *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not
