@@ -165,6 +165,47 @@ def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
             "whole_step": {"achieved": step_gbps, "frac": step_gbps / peak, "bytes_per_step": step_bytes}}
 
 
+def prefill_leg(ctx, device, stream):
+    """ribn_gemm on the two configuration-3 matrices, 512 and 2048 tokens, bf16 in and out: TFLOP/s and the fraction of
+    the measured dense bf16 throughput (the kernel issues two MMAs per weight -- high and low bf16 part -- so half of
+    the tensor peak is its ceiling)."""
+    import torch
+
+    import engine_b200
+    from engine_b200 import synth
+
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+        tensor_peak, source = float(peaks["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        tensor_peak, source = 1590.0, "fallback 1.59 PFLOP/s"
+    results = {"peak_tflops": tensor_peak, "peak_source": source}
+    try:
+        for vt, n, k in ((12, 12288, 4096), (14, 4096, 12288)):
+            data = synth.random_weight_device(vt, k, n, seed=vt, device=device)
+            weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [k, n]), vt, data)
+            for tokens in (512, 2048):
+                x = torch.randn(tokens, k, device=device).to(torch.bfloat16)
+                y = torch.empty(tokens, n, dtype=torch.bfloat16, device=device)
+                with torch.cuda.stream(stream):
+                    for _ in range(3):
+                        engine_b200.gemm(ctx, weight, x, y)
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    reps = 10
+                    for _ in range(reps):
+                        engine_b200.gemm(ctx, weight, x, y)
+                    b.record(stream)
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / reps
+                tflops = 2.0 * tokens * n * k / (ms * 1e-3) / 1e12
+                results[f"{synth.TYPE_NAMES[vt]}_{n}x{k}_M{tokens}"] = {"ms": ms, "tflops": tflops, "frac_of_peak": tflops / tensor_peak}
+    except Exception as exc:
+        results["error"] = f"{type(exc).__name__}: {exc}"
+    return results
+
+
 def decode_leg(args, ctx, device, rank, world, peak):
     """Decode tok/s.  One GPU: Qwen3-8B shape, Q4_K_M mix, 2048 tokens of context, 256 generated, batch 1 and 32.
     Several GPUs: Qwen3-32B shape, tensor parallel over all ranks, 4096 tokens of context, batch 64, all-reduce
@@ -310,6 +351,7 @@ def main() -> None:
                         help="library tuning option passed to ribn_set_option (measurement runs only)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM measurements")
     parser.add_argument("--no-decode", action="store_true", help="skip the decode-loop measurements")
     parser.add_argument("--decode-layers", type=int, default=0, help="layer count of the decode models (0 = the full 36 / 64)")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
@@ -503,6 +545,11 @@ def main() -> None:
     if rank == 0 and world == 1 and not args.no_reference_cuda:
         reference_cuda = time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, max(3, min(args.steps, 20)))
 
+    # ---- prefill GEMM (BASELINE configuration 3): tensor-core TFLOP/s against the measured dense bf16 peak
+    prefill_results = None
+    if rank == 0 and world == 1 and not args.no_prefill and not args.only:
+        prefill_results = prefill_leg(ctx, device, stream)
+
     # ---- decode loop: tokens per second of a random-init dense model (second half of the metric)
     decode_results = None
     if not args.no_decode and not args.only:
@@ -555,6 +602,8 @@ def main() -> None:
             line["reference_cuda"] = reference_cuda
         if decode_results is not None:
             line["decode"] = decode_results
+        if prefill_results is not None:
+            line["prefill"] = prefill_results
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_leg()
         print(json.dumps(line))
