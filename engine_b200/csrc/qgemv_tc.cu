@@ -325,13 +325,12 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                                           static_cast<unsigned long long>(sb_begin + i) * F::kBytes;
             const uint8_t* blk = raw + rs * G::kRawStageBytes + r * G::kSlot + static_cast<uint32_t>(g0 & 15ull);
             float inverse = 0.0f, s = 0.0f;
-            // All eight group scales are decoded here although the slot uses two: decoding them inside the unrolled
-            // step branch (where the compiler can drop the rest) measured 6 % slower -- four copies of the decoder
-            // in a kernel that already stalls on instruction fetch.
-            typename R::Scales scales;
+            // The slot's K step is a run-time index: one copy of the dequantiser serves the four slots (four unrolled
+            // copies measured slower: the kernel stalls on instruction fetch), and only the step's own scales are decoded.
+            typename R::StepScales scales;
             if (row_ok) {
                 normaliser(R::magnitude_bound(blk), inverse, s);
-                R::load_scales(blk, scales, inverse);
+                R::load_step_scales(blk, slot, inverse, scales);
             }
             const int j = i * kSub + slot;
             const int as = j % G::kStages;
@@ -344,21 +343,17 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             if (r == 0) stamp(p, 1, j, 0);
             uint8_t* tile = a_tiles + as * G::kATileBytes + row_off;
 #pragma unroll
-            for (int t = 0; t < kSub; ++t) {
-                if (t != slot) continue;   // compile-time step index for the format's tables
+            for (int h = 0; h < 2; ++h) {
+                typename R::Chunk out[4];
+                if (row_ok) {
+                    R::step(blk, scales, slot, h, out);
+                } else {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    typename R::Chunk out[4];
-                    if (row_ok) {
-                        R::step(blk, scales, t, h, out);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) out[c] = SingleF16::zero();
-                    }
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4*>(tile + ((static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4)) = out[c].high;
+                    for (int c = 0; c < 4; ++c) out[c] = SingleF16::zero();
                 }
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(tile + ((static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4)) = out[c].high;
             }
             if (r == 0) stamp(p, 1, j, 1);
             if (slot == 0) {

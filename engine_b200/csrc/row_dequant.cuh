@@ -119,12 +119,35 @@ struct RowDequant<kQ4_K, Enc> {
         }
     }
     __device__ static int chunk_index(int h, int c) { return (c >> 1) * 4 + 2 * h + (c & 1); }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+    // The four values one K step needs, for callers whose step index is only known at run time (an array of all
+    // sixteen indexed dynamically would live in local memory): scale and minimum of groups 2t and 2t+1.
+    struct StepScales { float v[4]; };
+    __device__ static void load_step_scales(const uint8_t* blk, int t, float prescale, StepScales& ss) {
+        const uint4 h = raw16(blk);
+        const float d = f16_bits_to_f32(h.x & 0xffffu) * prescale;
+        const float dmin = f16_bits_to_f32(h.x >> 16) * prescale;
+        uint32_t sc_lo, sc_hi, m_lo, m_hi;
+        unpack_k_scales(h.y, h.z, h.w, sc_lo, sc_hi, m_lo, m_hi);
+        const uint32_t sc = t < 2 ? sc_lo : sc_hi;
+        const uint32_t mn = t < 2 ? m_lo : m_hi;
+        const int shift = (t & 1) * 16;
+        ss.v[0] = d * static_cast<float>((sc >> shift) & 0xffu);
+        ss.v[1] = dmin * static_cast<float>((mn >> shift) & 0xffu);
+        ss.v[2] = d * static_cast<float>((sc >> (shift + 8)) & 0xffu);
+        ss.v[3] = dmin * static_cast<float>((mn >> (shift + 8)) & 0xffu);
+    }
+    __device__ static void step_with(const uint8_t* blk, int t, int h, float a0, float b0, float a1, float b1, Chunk (&out)[4]) {
         const uint4 w = raw16(blk + 16 + 32 * t + 16 * h);
-        out[0] = chunk_from_bytes<Enc>(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, 0.0f, s.a[2 * t], s.b[2 * t]);
-        out[1] = chunk_from_bytes<Enc>(w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu, 0.0f, s.a[2 * t], s.b[2 * t]);
-        out[2] = chunk_from_bytes<Enc>((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, 0.0f, s.a[2 * t + 1], s.b[2 * t + 1]);
-        out[3] = chunk_from_bytes<Enc>((w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu, 0.0f, s.a[2 * t + 1], s.b[2 * t + 1]);
+        out[0] = chunk_from_bytes<Enc>(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, 0.0f, a0, b0);
+        out[1] = chunk_from_bytes<Enc>(w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu, 0.0f, a0, b0);
+        out[2] = chunk_from_bytes<Enc>((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, 0.0f, a1, b1);
+        out[3] = chunk_from_bytes<Enc>((w.z >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu, 0.0f, a1, b1);
+    }
+    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, s.a[2 * t], s.b[2 * t], s.a[2 * t + 1], s.b[2 * t + 1], out);
+    }
+    __device__ static void step(const uint8_t* blk, const StepScales& ss, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, ss.v[0], ss.v[1], ss.v[2], ss.v[3], out);
     }
 };
 
@@ -143,14 +166,24 @@ struct RowDequant<kQ5_K, Enc> {
     __device__ static uint32_t hi5(uint32_t w, uint32_t hb, int g) {
         return ((w >> 4) & 0x0f0f0f0fu) | (((hb >> g) & 0x01010101u) << 4);
     }
-    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+    __device__ static void step_with(const uint8_t* blk, int t, int h, float a0, float b0, float a1, float b1, Chunk (&out)[4]) {
         const uint4 w = raw16(blk + 48 + 32 * t + 16 * h);
         const uint4 hb = raw16(blk + 16 + 16 * h);
         const int g = 2 * t;
-        out[0] = chunk_from_bytes<Enc>(lo5(w.x, hb.x, g), lo5(w.y, hb.y, g), 0.0f, s.a[g], s.b[g]);
-        out[1] = chunk_from_bytes<Enc>(lo5(w.z, hb.z, g), lo5(w.w, hb.w, g), 0.0f, s.a[g], s.b[g]);
-        out[2] = chunk_from_bytes<Enc>(hi5(w.x, hb.x, g + 1), hi5(w.y, hb.y, g + 1), 0.0f, s.a[g + 1], s.b[g + 1]);
-        out[3] = chunk_from_bytes<Enc>(hi5(w.z, hb.z, g + 1), hi5(w.w, hb.w, g + 1), 0.0f, s.a[g + 1], s.b[g + 1]);
+        out[0] = chunk_from_bytes<Enc>(lo5(w.x, hb.x, g), lo5(w.y, hb.y, g), 0.0f, a0, b0);
+        out[1] = chunk_from_bytes<Enc>(lo5(w.z, hb.z, g), lo5(w.w, hb.w, g), 0.0f, a0, b0);
+        out[2] = chunk_from_bytes<Enc>(hi5(w.x, hb.x, g + 1), hi5(w.y, hb.y, g + 1), 0.0f, a1, b1);
+        out[3] = chunk_from_bytes<Enc>(hi5(w.z, hb.z, g + 1), hi5(w.w, hb.w, g + 1), 0.0f, a1, b1);
+    }
+    using StepScales = typename RowDequant<kQ4_K, Enc>::StepScales;
+    __device__ static void load_step_scales(const uint8_t* blk, int t, float prescale, StepScales& ss) {
+        RowDequant<kQ4_K, Enc>::load_step_scales(blk, t, prescale, ss);
+    }
+    __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, s.a[2 * t], s.b[2 * t], s.a[2 * t + 1], s.b[2 * t + 1], out);
+    }
+    __device__ static void step(const uint8_t* blk, const StepScales& ss, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, ss.v[0], ss.v[1], ss.v[2], ss.v[3], out);
     }
 };
 
@@ -176,15 +209,28 @@ struct RowDequant<kQ6_K, Enc> {
     __device__ static uint32_t q6(uint32_t l, uint32_t hb, int nib, int shift) {
         return ((l >> nib) & 0x0f0f0f0fu) | (((hb >> shift) & 0x03030303u) << 4);
     }
+    struct StepScales { float v[4]; };   // d * scales[4t .. 4t+3]
+    __device__ static void load_step_scales(const uint8_t* blk, int t, float prescale, StepScales& ss) {
+        const float d = f16_bits_to_f32(ld_u16(blk + 208)) * prescale;
+        const uint32_t lo = ld_u16(blk + 192 + 4 * t), hi = ld_u16(blk + 194 + 4 * t);
+        ss.v[0] = d * static_cast<float>(static_cast<int8_t>(lo & 0xffu));
+        ss.v[1] = d * static_cast<float>(static_cast<int8_t>(lo >> 8));
+        ss.v[2] = d * static_cast<float>(static_cast<int8_t>(hi & 0xffu));
+        ss.v[3] = d * static_cast<float>(static_cast<int8_t>(hi >> 8));
+    }
     __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, h ? s.a[4 * t + 1] : s.a[4 * t], h ? s.a[4 * t + 3] : s.a[4 * t + 2], out);
+    }
+    __device__ static void step(const uint8_t* blk, const StepScales& ss, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, h ? ss.v[1] : ss.v[0], h ? ss.v[3] : ss.v[2], out);
+    }
+    __device__ static void step_with(const uint8_t* blk, int t, int h, float s0, float s1, Chunk (&out)[4]) {
         const int c = t >> 1;
         const int nib = (t & 1) * 4;
         const int v2 = (t & 1) * 4;  // 2 * variant of the first group
         const uint4 l0 = raw16_a2(blk + c * 64 + 16 * h);
         const uint4 l1 = raw16_a2(blk + c * 64 + 32 + 16 * h);
         const uint4 hb = raw16_a2(blk + 128 + c * 32 + 16 * h);
-        const float s0 = h ? s.a[4 * t + 1] : s.a[4 * t];      // scale index 2*group + position/16
-        const float s1 = h ? s.a[4 * t + 3] : s.a[4 * t + 2];
         out[0] = chunk_from_bytes<Enc>(q6(l0.x, hb.x, nib, v2), q6(l0.y, hb.y, nib, v2), 32.0f, s0, 0.0f);
         out[1] = chunk_from_bytes<Enc>(q6(l0.z, hb.z, nib, v2), q6(l0.w, hb.w, nib, v2), 32.0f, s0, 0.0f);
         out[2] = chunk_from_bytes<Enc>(q6(l1.x, hb.x, nib, v2 + 2), q6(l1.y, hb.y, nib, v2 + 2), 32.0f, s1, 0.0f);
@@ -208,11 +254,22 @@ struct RowDequant<kQ8_0, Enc> {
         for (int b = 0; b < 8; ++b) s.d[b] = f16_bits_to_f32(ld_u16(blk + 34 * b)) * prescale;
     }
     __device__ static int chunk_index(int h, int c) { return 4 * h + c; }
+    struct StepScales { float v[4]; };   // d of blocks 2t and 2t+1
+    __device__ static void load_step_scales(const uint8_t* blk, int t, float prescale, StepScales& ss) {
+        ss.v[0] = f16_bits_to_f32(ld_u16(blk + 34 * (2 * t))) * prescale;
+        ss.v[1] = f16_bits_to_f32(ld_u16(blk + 34 * (2 * t + 1))) * prescale;
+        ss.v[2] = ss.v[3] = 0.0f;
+    }
     __device__ static void step(const uint8_t* blk, const Scales& s, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, h ? s.d[2 * t + 1] : s.d[2 * t], out);
+    }
+    __device__ static void step(const uint8_t* blk, const StepScales& ss, int t, int h, Chunk (&out)[4]) {
+        step_with(blk, t, h, h ? ss.v[1] : ss.v[0], out);
+    }
+    __device__ static void step_with(const uint8_t* blk, int t, int h, float d, Chunk (&out)[4]) {
         const uint8_t* q = blk + 34 * (2 * t + h) + 2;
         const uint4 w0 = raw16_a2(q);
         const uint4 w1 = raw16_a2(q + 16);
-        const float d = h ? s.d[2 * t + 1] : s.d[2 * t];
         out[0] = chunk_from_bytes<Enc>(w0.x ^ 0x80808080u, w0.y ^ 0x80808080u, 128.0f, d, 0.0f);
         out[1] = chunk_from_bytes<Enc>(w0.z ^ 0x80808080u, w0.w ^ 0x80808080u, 128.0f, d, 0.0f);
         out[2] = chunk_from_bytes<Enc>(w1.x ^ 0x80808080u, w1.y ^ 0x80808080u, 128.0f, d, 0.0f);
