@@ -656,7 +656,7 @@ cudaError_t launch_tile(const TcArgs& a) {
     const int n_tiles = (a.n + kBM - 1) / kBM;
     const int m_tiles = (a.m + NT - 1) / NT;
     const size_t plane_bytes = static_cast<size_t>(a.m) * a.n * sizeof(float);
-    p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, plane_bytes, partial_bytes, a.ticket_count);
+    p.ksplit = choose_ksplit_decode(n_tiles * m_tiles, p.nsb, a.sm_count, plane_bytes, partial_bytes, a.ticket_count, NT);
     if (a.force_ksplit > 0 && a.force_ksplit <= p.nsb && plane_bytes * a.force_ksplit <= partial_bytes && n_tiles * m_tiles <= a.ticket_count)
         p.ksplit = a.force_ksplit;
     const dim3 grid(n_tiles, m_tiles, p.ksplit);

@@ -64,4 +64,27 @@ inline int choose_ksplit(int tiles, int nsb, int sm_count, size_t plane_bytes, s
     return best;
 }
 
+// The decode kernel's split factor, fitted to measurements on B200 (times in units of one 128-row super-block,
+// ~1.45 us): a CTA costs its K share plus ~5 units of launch, pipeline fill and epilogue; every split adds a partial
+// tile the last CTA of the tile has to add, ~0.33 units per 16 tokens.  Ties go to the smaller factor.
+inline int choose_ksplit_decode(int tiles, int nsb, int sm_count, size_t plane_bytes, size_t scratch_bytes, int max_tickets,
+                                int tokens_per_tile) {
+    if (tiles > max_tickets) return 1;
+    int best = 1;
+    double best_cost = 1e30;
+    const int limit = nsb < 16 ? nsb : 16;
+    for (int ks = 1; ks <= limit; ++ks) {
+        if (ks > 1 && plane_bytes * ks > scratch_bytes) break;
+        const int waves = (tiles * ks + sm_count - 1) / sm_count;
+        const double per_cta = static_cast<double>((nsb + ks - 1) / ks) + 5.0;
+        const double reduce = ks > 1 ? ks * 0.33 * (tokens_per_tile / 16.0) : 0.0;
+        const double cost = waves * per_cta + reduce;
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = ks;
+        }
+    }
+    return best;
+}
+
 }  // namespace ribn
