@@ -43,6 +43,7 @@
 
 #include "formats.cuh"
 #include "internal.h"
+#include "pack_activations.cuh"
 #include "row_dequant.cuh"
 #include "tc_host.h"
 #include "tcgen05.cuh"
@@ -514,15 +515,17 @@ qgemv_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
 // that its largest magnitude lands in (2^13, 2^14], and rounded to f16; factor[m] = 2^e.
 constexpr int kConvertThreads = 512;
 
-__device__ __forceinline__ float load_scalar(const void* x, bool bf16, size_t i) {
-    return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[i]) : static_cast<const float*>(x)[i];
-}
-// Element i of member row `member`; with swiglu the row is [gate | up] (2k values) and the element is
-// silu(gate[i]) * up[i] (silu_mul of the reference, model_ops.rs:316-328).
-__device__ __forceinline__ float load_activation(const void* x, bool bf16, int swiglu, size_t member, int k, int i) {
-    if (swiglu == 0) return load_scalar(x, bf16, member * k + i);
-    const float gate = load_scalar(x, bf16, member * 2 * k + i);
-    return (gate / (1.0f + expf(-gate))) * load_scalar(x, bf16, member * 2 * k + k + i);
+// Eight consecutive elements of member row `member` starting at i; with swiglu the row is [gate | up] (2k values)
+// and the elements are silu(gate) * up (silu_mul of the reference, model_ops.rs:316-328).
+__device__ __forceinline__ void load_activation8(const void* x, int bf16, int swiglu, size_t member, int k, int i, float (&v)[8]) {
+    const AnyRow row{static_cast<const uint8_t*>(x) + member * static_cast<size_t>(k) * (swiglu ? 2 : 1) * (bf16 ? 2 : 4), bf16};
+    load_row8(row + i, v);
+    if (swiglu != 0) {
+        float u[8];
+        load_row8(row + (k + i), u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u[j];
+    }
 }
 
 __global__ void __launch_bounds__(kConvertThreads)
@@ -534,10 +537,17 @@ convert_activations_f16(const void* x, int x_bf16, int swiglu, const float* norm
     __shared__ float broadcast[2];
     const size_t base = static_cast<size_t>(blockIdx.x) * k;
     float sum = 0.0f, biggest = 0.0f;
-    for (int i = threadIdx.x; i < k; i += kConvertThreads) {
-        const float v = load_activation(x, x_bf16 != 0, swiglu, blockIdx.x, k, i);
-        sum = fmaf(v, v, sum);
-        biggest = fmaxf(biggest, fabsf(norm_weight != nullptr ? v * norm_weight[i] : v));
+    // k is a multiple of 256 on this path: chunks of eight elements, 16- or 32-byte loads.
+    for (int i = threadIdx.x * 8; i < k; i += kConvertThreads * 8) {
+        float v[8];
+        load_activation8(x, x_bf16, swiglu, blockIdx.x, k, i, v);
+        float g[8];
+        if (norm_weight != nullptr) load_x8<float>(norm_weight + i, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sum = fmaf(v[j], v[j], sum);
+            biggest = fmaxf(biggest, fabsf(norm_weight != nullptr ? v[j] * g[j] : v[j]));
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -574,10 +584,22 @@ convert_activations_f16(const void* x, int x_bf16, int swiglu, const float* norm
         up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
     }
     if (threadIdx.x == 0) factor[blockIdx.x] = up;
-    for (int i = threadIdx.x; i < k; i += kConvertThreads) {
-        float v = load_activation(x, x_bf16 != 0, swiglu, blockIdx.x, k, i);
-        if (norm_weight != nullptr) v = v * inv_rms * norm_weight[i];
-        out[base + i] = __float2half_rn(v * down);
+    for (int i = threadIdx.x * 8; i < k; i += kConvertThreads * 8) {
+        float v[8];
+        load_activation8(x, x_bf16, swiglu, blockIdx.x, k, i, v);
+        if (norm_weight != nullptr) {
+            float g[8];
+            load_x8<float>(norm_weight + i, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * g[j];
+        }
+        uint4 packed;
+        __half2 h;
+        h = __floats2half2_rn(v[0] * down, v[1] * down); packed.x = *reinterpret_cast<const uint32_t*>(&h);
+        h = __floats2half2_rn(v[2] * down, v[3] * down); packed.y = *reinterpret_cast<const uint32_t*>(&h);
+        h = __floats2half2_rn(v[4] * down, v[5] * down); packed.z = *reinterpret_cast<const uint32_t*>(&h);
+        h = __floats2half2_rn(v[6] * down, v[7] * down); packed.w = *reinterpret_cast<const uint32_t*>(&h);
+        *reinterpret_cast<uint4*>(out + base + i) = packed;
     }
 }
 
