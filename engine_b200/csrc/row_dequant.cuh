@@ -28,6 +28,7 @@ __device__ __forceinline__ uint4 raw16_a2(const uint8_t* p) {
 //
 // SplitBf16: w_high = bf16(w) and w_low = bf16(w - w_high), two tiles, together 16 significant bits.
 struct SplitBf16 {
+    static constexpr bool kFoldOffset = false;   // 16 significant bits: keep the exact two-step dequantisation
     struct Chunk {
         uint4 high, low;
     };
@@ -57,6 +58,7 @@ struct SplitBf16 {
 // SingleF16: one f16 tile (11 significant bits); the caller keeps the values in f16 range by
 // pre-scaling each super-block (see RowDequant::magnitude_bound).
 struct SingleF16 {
+    static constexpr bool kFoldOffset = true;
     struct Chunk {
         uint4 high;
     };
@@ -76,10 +78,31 @@ struct SingleF16 {
     }
 };
 
+// Byte I of `packed` (0..127) as the float 128 + byte: prmt drops it into the top mantissa bits of 128.0f.
+template <int I>
+__device__ __forceinline__ float byte_plus_128(uint32_t packed) {
+    return __uint_as_float(__byte_perm(packed, 0x43000000u, 0x7054u + (I << 8)));
+}
+
 // Eight weights (two packed words of four byte-sized quants) -> one chunk (pair).
 template <class Enc>
 __device__ __forceinline__ typename Enc::Chunk chunk_from_bytes(uint32_t q0, uint32_t q1, float bias, float scale, float minimum) {
     float a[4], b[4];
+    if (Enc::kFoldOffset && bias < 100.0f) {
+        // Quants below 128 (every K-quant): w = scale * (128 + q) - (scale * (128 + bias) + minimum), one prmt and one
+        // FMA per weight.  The folded constant is rounded at the magnitude of 160 * scale, 2^-17 of a quant step: far
+        // below the f16 rounding that follows (the exact two-step form is kept where results must be bit-exact).
+        const float offset = -fmaf(scale, 128.0f + bias, minimum);
+        a[0] = fmaf(scale, byte_plus_128<0>(q0), offset);
+        a[1] = fmaf(scale, byte_plus_128<1>(q0), offset);
+        a[2] = fmaf(scale, byte_plus_128<2>(q0), offset);
+        a[3] = fmaf(scale, byte_plus_128<3>(q0), offset);
+        b[0] = fmaf(scale, byte_plus_128<0>(q1), offset);
+        b[1] = fmaf(scale, byte_plus_128<1>(q1), offset);
+        b[2] = fmaf(scale, byte_plus_128<2>(q1), offset);
+        b[3] = fmaf(scale, byte_plus_128<3>(q1), offset);
+        return Enc::encode(a, b);
+    }
     bytes_to_float4(q0, bias, a);
     bytes_to_float4(q1, bias, b);
 #pragma unroll
