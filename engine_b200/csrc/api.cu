@@ -36,6 +36,7 @@ struct ribn_ctx {
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int dp4a_prepass = 1;           // 0 = calls of 1..4 rows pack their activations inside the GEMV kernel (measured slower: see the header)
     int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
+    int64_t tc_four_row_bytes = 8 << 20;   // batches of four rows use the tensor-core kernel too when the weights are at least this large
     int tc_min_members = 5;         // batches of at least this many rows go to the tensor-core kernel
     std::string message;
     uint64_t expected = 0, actual = 0;
@@ -308,7 +309,10 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     // activation pre-pass).  Its operands are f16: bf16 activations convert exactly and the weights'
     // rounding (2^-12) is below the one the caller applied to the activations (2^-9); f32 activations
     // would lose 13 bits, so they take it only on request.  Its scratch is the f16 copy of the activations.
-    if (ctx->gemv_path == 0 && (a.x_bf16 || ctx->tc_f32_activations != 0) && members >= static_cast<uint32_t>(ctx->tc_min_members) && ribn::qgemm_tc_supports(a.value_type, a.k) &&
+    // (Measured: a 16-token tile of the tensor-core kernel beats the integer-dot kernel's four rows from ~8 MB of weights up.)
+    const bool tc_batch = members >= static_cast<uint32_t>(ctx->tc_min_members) ||
+                          (members == 4 && ctx->tc_min_members == 5 && static_cast<int64_t>(w->encoded_bytes) >= ctx->tc_four_row_bytes);
+    if (ctx->gemv_path == 0 && (a.x_bf16 || ctx->tc_f32_activations != 0) && tc_batch && ribn::qgemm_tc_supports(a.value_type, a.k) &&
         members * k * 2 + (1u << 20) <= ctx->workspace_bytes)
         return enqueue_tc(ctx, w, k, n, x, x_dtype, y, y_dtype, members, norm_weight, eps);
     // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
@@ -385,7 +389,11 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         all_tc = all_tc && ribn::qgemm_tc_supports(jobs[j].weight->value_type, static_cast<int>(k));
         all_dp4a = all_dp4a && ribn::gemv_dp4a_fits(jobs[j].weight->value_type, static_cast<int>(k), members_per_launch);
     }
-    if (ctx->gemv_path == 0 && (x_bf16 || ctx->tc_f32_activations != 0) && members >= static_cast<uint32_t>(ctx->tc_min_members) && all_tc &&
+    int64_t smallest = INT64_MAX;
+    for (uint32_t j = 0; j < job_count; ++j) smallest = std::min<int64_t>(smallest, static_cast<int64_t>(jobs[j].weight->encoded_bytes));
+    const bool tc_batch = members >= static_cast<uint32_t>(ctx->tc_min_members) ||
+                          (members == 4 && ctx->tc_min_members == 5 && smallest >= ctx->tc_four_row_bytes);
+    if (ctx->gemv_path == 0 && (x_bf16 || ctx->tc_f32_activations != 0) && tc_batch && all_tc &&
         members * k * 2 + (1u << 20) <= ctx->workspace_bytes) {
         for (uint32_t j = 0; j < job_count; ++j) {
             TcExtras extras;
@@ -604,6 +612,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_f32_activations") == 0 && (value == 0 || value == 1)) {
         ctx->tc_f32_activations = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tc_four_row_bytes") == 0 && value >= 0) {
+        ctx->tc_four_row_bytes = value;
         return RIBN_OK;
     }
     if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {

@@ -100,6 +100,8 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
  *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
+ *   "tc_four_row_bytes": bf16 batches of exactly four rows also use it when the encoded weights are at least this
+ *                   many bytes (default 8 MiB; only while tc_min_members is 5);
  *   "tc_f32_activations": 1 = f32 batches may use it too (they are rounded to f16; default 0);
  *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
  *                   kernel) instead of the f16 decode kernel (default 0);
