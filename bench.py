@@ -11,7 +11,7 @@ metric  = algorithmic bytes moved per second over a whole step: for each GEMV th
 L2      = every (format, shape) has a ring of distinct weight copies larger than 2x the 126 MB L2
           and each launch uses the next copy, so no launch finds its weights in cache.
 value   = device-resident inputs, CUDA-event timed on the launching stream.
-e2e     = the same sweep through ribn_gemv_host: pinned host activations in, host outputs out,
+e2e     = the same sweep through ribn_gemv_host_async + one ribn_synchronize per step: pinned host activations in, host outputs out,
           copies inside the timed region.
 --impl reference = the CPU restatement of the reference's host path (dequantise a row, sequential
           f32 dot; oracle/ribn_oracle.c) on all host threads, on a bounded sample of the sweep.
@@ -494,7 +494,8 @@ def main() -> None:
             ring = rings[(vt, n, k)]
             weight = ring[cursor[(vt, n, k)] % len(ring)]
             cursor[(vt, n, k)] += 1
-            kernels[vt].inner.execute_host(weight, host_x[(k, m)], host_y[(n, m)], m)
+            kernels[vt].inner.execute_host(weight, host_x[(k, m)], host_y[(n, m)], m, wait=False)
+        ctx.synchronize()   # the step's results are in host memory from here on
 
     e2e_steps = max(3, min(args.steps, 10))
     e2e_step()

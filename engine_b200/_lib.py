@@ -102,6 +102,8 @@ SIGNATURES = {
     "ribn_reserve_staging": (ctypes.c_int, [_vp, ctypes.c_uint64]),
     "ribn_gemv_host": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp,
                                       ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
+    "ribn_gemv_host_async": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp,
+                                      ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_gemv_noalloc": (ctypes.c_int, [ctypes.c_int, _vp, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_int,
                                          ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint64]),
     "ribn_gemv_fused": (ctypes.c_int, [_vp, ctypes.POINTER(GemvJob), ctypes.c_uint32, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64,

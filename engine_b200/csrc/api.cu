@@ -755,6 +755,15 @@ int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {
 
 int ribn_gemv_host(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_host, int x_dtype,
                    uint64_t x_len, void* y_host, int y_dtype, uint64_t y_len, uint32_t members) {
+    const int status = ribn_gemv_host_async(ctx, expected_type, weight, x_host, x_dtype, x_len, y_host, y_dtype, y_len, members);
+    if (status != RIBN_OK) return status;
+    const cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
+    return RIBN_OK;
+}
+
+int ribn_gemv_host_async(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_host, int x_dtype,
+                         uint64_t x_len, void* y_host, int y_dtype, uint64_t y_len, uint32_t members) {
     if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
     uint64_t k = 0, n = 0;
     Failure f = validate_gemv(weight, expected_type, x_dtype, x_len, y_dtype, y_len, members, &k, &n);
@@ -779,8 +788,6 @@ int ribn_gemv_host(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* we
     if (status != RIBN_OK) return status;
     e = cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, ctx->stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "output download");
-    e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
     return RIBN_OK;
 }
 

@@ -226,14 +226,16 @@ class _CudaQuantizedGemv:
                                               members))
 
     def execute_host(self, weight: CudaQuantizedWeight, input: np.ndarray | torch.Tensor, output: np.ndarray | torch.Tensor,
-                     members: int) -> None:
-        """Host activations in, host outputs out (copies inside); needs context.reserve_staging()."""
+                     members: int, wait: bool = True) -> None:
+        """Host activations in, host outputs out (copies inside); needs context.reserve_staging().  With wait=False
+        the call only enqueues (ribn_gemv_host_async): `output` is valid after context.synchronize(), and `input`
+        must stay untouched (and, for the copies to be asynchronous, pinned) until then."""
         ctx = self.context
         descriptor = weight.descriptor()
         x_ptr, x_code, x_len = _host_view(input)
         y_ptr, y_code, y_len = _host_view(output)
-        ctx.check(ctx._lib.ribn_gemv_host(ctx.handle, self.VALUE_TYPE, ctypes.byref(descriptor), x_ptr, x_code, x_len,
-                                          y_ptr, y_code, y_len, members))
+        entry = ctx._lib.ribn_gemv_host if wait else ctx._lib.ribn_gemv_host_async
+        ctx.check(entry(ctx.handle, self.VALUE_TYPE, ctypes.byref(descriptor), x_ptr, x_code, x_len, y_ptr, y_code, y_len, members))
 
 
 def _host_view(t):
