@@ -16,22 +16,23 @@
 // the path; a bf16 tile would not be) but only five exponent bits.  Range is handled exactly:
 //   * every (row, super-block) is multiplied by a power of two that brings the largest magnitude its
 //     header allows (e.g. |d|*63*15 + |dmin|*63 for Q4_K) to at most 1024; the MMAs of one
-//     super-block accumulate into a TMEM buffer of their own, and four accumulate warps add
+//     super-block accumulate into a TMEM buffer of their own, and the accumulate warps add
 //     s * D_superblock to f32 registers (s = the inverse power of two), once per 256 K elements;
 //   * every activation row is multiplied by a power of two that brings its largest magnitude to at most
 //     2^14 when it is converted to f16 (a pre-pass, convert_activations_f16 below, which can also
 //     apply RMSNorm first); the epilogue multiplies the result by the inverse.
 // Both scalings are exact, so the only roundings are the one of each weight and each activation to f16.
 //
-// Shape of one CTA: 128 weight rows x NT tokens (16, 32 or 64) x a range of K; 23 warps:
+// Shape of one CTA: 128 weight rows x NT tokens (16, 32 or 64) x a range of K; 23 warps (27 for 64 tokens):
 //   warp 0        raw weight bytes of one super-block x 128 rows per stage (one tiled TMA box, or
 //                 per-row bulk copies for rows that are not 16-byte aligned);
 //   warp 1        MMA issuer (one thread): four tcgen05.mma per 64-wide K step, one tcgen05.commit to free
 //                 a group of steps, one to publish the super-block's TMEM buffer after its last step;
 //   warps 2..17   dequantisation: four slots of 128 threads (one per row); slot s converts K step s of
 //                 every super-block into the swizzled K-major A tile, so four steps are in flight;
-//   warps 18..21  accumulate: thread = weight row (TMEM lane), registers = tokens;
-//   warp 22       activation tiles (tiled TMA, 128-byte swizzle), one per K step.
+//   warps 18..    accumulate: thread = weight row (TMEM lane), registers = tokens; one warp per TMEM lane quadrant,
+//                 two for 64 tokens (32 accumulators per thread either way);
+//   last warp     activation tiles (tiled TMA, 128-byte swizzle), one per K step.
 // The ring of A/B tiles is deeper than the four slots, so dequantising step j+4 overlaps the MMAs of
 // step j.  Split-K as in qgemm_tc.cu: partial tiles and an atomic ticket, the last CTA of a tile adds
 // them in index order.
