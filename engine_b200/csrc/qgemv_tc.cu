@@ -26,8 +26,9 @@
 // Shape of one CTA: 128 weight rows x NT tokens (16, 32 or 64) x a range of K; 23 warps (27 for 64 tokens):
 //   warp 0        raw weight bytes of one super-block x 128 rows per stage (one tiled TMA box, or
 //                 per-row bulk copies for rows that are not 16-byte aligned);
-//   warp 1        MMA issuer (one thread): four tcgen05.mma per 64-wide K step, one tcgen05.commit to free
-//                 a group of steps, one to publish the super-block's TMEM buffer after its last step;
+//   warp 1        MMA issuer: the warp runs its loop converged and the elect.sync lane issues four tcgen05.mma per
+//                 64-wide K step, one tcgen05.commit to free a group of steps, one to publish the super-block's
+//                 TMEM buffer after its last step;
 //   warps 2..17   dequantisation: four slots of 128 threads (one per row); slot s converts K step s of
 //                 every super-block into the swizzled K-major A tile, so four steps are in flight;
 //   warps 18..    accumulate: thread = weight row (TMEM lane), registers = tokens; one warp per TMEM lane quadrant,
