@@ -356,12 +356,19 @@ def main() -> None:
     parser.add_argument("--decode-layers", type=int, default=0, help="layer count of the decode models (0 = the full 36 / 64)")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
     parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
+    parser.add_argument("--members", default="", help="comma-separated member counts replacing 1,4,16,64 (measurement runs, not the benchmark line)")
+    parser.add_argument("--formats", default="", help="comma-separated formats (Q8_0,Q4_K,Q5_K,Q6_K) replacing the sweep's three")
     parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
                         "a small run for profiler captures, not a benchmark line")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     global FORMATS, SHAPES, MEMBERS
+    names = {"Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+    if args.members:
+        MEMBERS = [int(v) for v in args.members.split(",")]
+    if args.formats:
+        FORMATS = [names[v] for v in args.formats.split(",")]
     if args.only:
         fmt, shape, m = args.only.split(":")
         FORMATS = [{"Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}[fmt]]

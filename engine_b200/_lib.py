@@ -98,7 +98,6 @@ SIGNATURES = {
                                           ctypes.c_float, _vp, ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_gemm": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_uint64, _vp, ctypes.c_int, ctypes.c_uint64,
                                  ctypes.c_uint64]),
-    "ribn_debug_read_trace": (ctypes.c_int, [_vp, _vp, ctypes.c_uint64]),
     "ribn_reserve_staging": (ctypes.c_int, [_vp, ctypes.c_uint64]),
     "ribn_gemv_host": (ctypes.c_int, [_vp, ctypes.c_uint32, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp,
                                       ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),

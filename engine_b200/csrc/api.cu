@@ -32,12 +32,17 @@ struct ribn_ctx {
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
     int tc_split_operands = 0;      // 1 = bf16 batches <= 64 use the split-operand GEMM (the prefill kernel) instead of the f16 decode kernel
-    int tc_trace = 0;               // 1 = the decode tensor-core kernel records pipeline clock stamps in the workspace tail
+    int tc_trace = 0;               // builds with -DRIBN_TRACE: 1 = kernels record pipeline clock stamps in the workspace tail
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int dp4a_prepass = 1;           // 0 = calls of 1..4 rows pack their activations inside the GEMV kernel (measured slower: see the header)
     int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
     int64_t tc_four_row_bytes = 8 << 20;   // batches of four rows use the tensor-core kernel too when the weights are at least this large
-    int tc_min_members = 5;         // batches of at least this many rows go to the tensor-core kernel
+    int tc_min_members = 9;         // batches of at least this many rows go to the tcgen05 decode kernel
+    int mma_gemv = 1;               // 1 = batches of up to eight rows use the half2-unpack + mma.sync kernel where it serves the shape
+    int mma_image_members = 3;      // launches of at least this many rows convert their activations in a pre-pass, fewer inside the kernel
+    int mma_stages = 0;             // ring depth of that kernel, 0 = as many stages as fit
+    int mma_resident = 0;           // CTAs per SM its shared-memory plan allows for, 0 = up to three
+    int mma_ctas = 0;               // CTAs per SM its grid is sized for, 0 = min(resident, 2)
     std::string message;
     uint64_t expected = 0, actual = 0;
 };
@@ -290,6 +295,59 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     return RIBN_OK;
 }
 
+// The half2-unpack + mma.sync kernel, eight member rows per launch.  mode: 0 plain, 1 RMSNorm, 2 silu(gate) * up.
+// `image_ready` = the activation images of this x are already in the workspace (an earlier projection of the
+// same fused call made them).
+bool mma_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, uint32_t members) {
+    if (ctx->mma_gemv == 0 || ctx->gemv_path != 0) return false;
+    const int per_launch = members < 8 ? static_cast<int>(members) : 8;
+    return ribn::gemv_mma_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), per_launch, w->data);
+}
+
+int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
+                float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready) {
+    const bool x_bf16 = x_dtype == RIBN_BF16;
+    const uint64_t x_row_bytes = k * (mode == 2 ? 2 : 1) * dtype_bytes(x_dtype);
+    uint64_t image_offset = 0;
+    for (uint32_t m0 = 0; m0 < members; m0 += 8) {
+        ribn::MmaGemvArgs a{};
+        a.weights = static_cast<const uint8_t*>(w->data);
+        a.value_type = w->value_type;
+        a.k = static_cast<int>(k);
+        a.n = static_cast<int>(n);
+        a.members = static_cast<int>(members - m0 < 8 ? members - m0 : 8);
+        a.x = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(m0) * x_row_bytes;
+        a.x_bf16 = x_bf16;
+        a.mode = mode;
+        a.norm_weight = norm_weight;
+        a.eps = eps;
+        a.y = static_cast<uint8_t*>(y) + static_cast<uint64_t>(m0) * n * dtype_bytes(y_dtype);
+        a.y_bf16 = y_dtype == RIBN_BF16;
+        a.accumulate = accumulate;
+        a.planes = ribn::gemv_mma_planes(a.value_type, a.k, a.members, x_bf16);
+        a.stages = ctx->mma_stages;
+        a.resident = ctx->mma_resident;
+        a.grid_ctas = ctx->mma_ctas;
+        a.device_status = ctx->device_status;
+        a.sm_count = ctx->sm_count;
+        a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
+        a.stream = ctx->stream;
+        const uint64_t image_bytes = ribn::gemv_mma_image_bytes(a.members, a.k, a.planes);
+        if (a.members >= ctx->mma_image_members && image_offset + image_bytes <= ctx->workspace_bytes) {
+            void* image = static_cast<uint8_t*>(ctx->workspace) + image_offset;
+            image_offset += image_bytes;
+            if (!image_ready) {
+                const cudaError_t e = ribn::launch_gemv_mma_image(a, image);
+                if (e != cudaSuccess) return record_cuda(ctx, e, "activation image launch");
+            }
+            a.image = image;
+        }
+        const cudaError_t e = ribn::launch_gemv_mma(a);
+        if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+    }
+    return RIBN_OK;
+}
+
 int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, void* y,
                  int y_dtype, uint32_t members, const float* norm_weight = nullptr, float eps = 0.0f) {
     GemvArgs a{};
@@ -310,11 +368,15 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     // rounding (2^-12) is below the one the caller applied to the activations (2^-9); f32 activations
     // would lose 13 bits, so they take it only on request.  Its scratch is the f16 copy of the activations.
     // (Measured: a 16-token tile of the tensor-core kernel beats the integer-dot kernel's four rows from ~8 MB of weights up.)
+    const bool mma = mma_serves(ctx, w, k, n, members);
     const bool tc_batch = members >= static_cast<uint32_t>(ctx->tc_min_members) ||
-                          (members == 4 && ctx->tc_min_members == 5 && static_cast<int64_t>(w->encoded_bytes) >= ctx->tc_four_row_bytes);
+                          (!mma && (members >= 5 || (members == 4 && static_cast<int64_t>(w->encoded_bytes) >= ctx->tc_four_row_bytes)));
     if (ctx->gemv_path == 0 && (a.x_bf16 || ctx->tc_f32_activations != 0) && tc_batch && ribn::qgemm_tc_supports(a.value_type, a.k) &&
         members * k * 2 + (1u << 20) <= ctx->workspace_bytes)
         return enqueue_tc(ctx, w, k, n, x, x_dtype, y, y_dtype, members, norm_weight, eps);
+    // Up to eight rows per launch (and wider f32 batches, in groups of eight): half2 unpack + mma.sync.
+    if (mma)
+        return enqueue_mma(ctx, w, k, n, x, x_dtype, norm_weight != nullptr ? 1 : 0, norm_weight, eps, y, y_dtype, members, false, false);
     // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
     // packed once into the context workspace, then consumed four member rows per launch (the
     // weights stay in L2 between the launches of one call).
@@ -390,9 +452,13 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         all_dp4a = all_dp4a && ribn::gemv_dp4a_fits(jobs[j].weight->value_type, static_cast<int>(k), members_per_launch);
     }
     int64_t smallest = INT64_MAX;
-    for (uint32_t j = 0; j < job_count; ++j) smallest = std::min<int64_t>(smallest, static_cast<int64_t>(jobs[j].weight->encoded_bytes));
+    bool all_mma = true;
+    for (uint32_t j = 0; j < job_count; ++j) {
+        smallest = std::min<int64_t>(smallest, static_cast<int64_t>(jobs[j].weight->encoded_bytes));
+        all_mma = all_mma && mma_serves(ctx, jobs[j].weight, k, ns[j], members);
+    }
     const bool tc_batch = members >= static_cast<uint32_t>(ctx->tc_min_members) ||
-                          (members == 4 && ctx->tc_min_members == 5 && smallest >= ctx->tc_four_row_bytes);
+                          (!all_mma && (members >= 5 || (members == 4 && smallest >= ctx->tc_four_row_bytes)));
     if (ctx->gemv_path == 0 && (x_bf16 || ctx->tc_f32_activations != 0) && tc_batch && all_tc &&
         members * k * 2 + (1u << 20) <= ctx->workspace_bytes) {
         for (uint32_t j = 0; j < job_count; ++j) {
@@ -402,6 +468,15 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
             extras.accumulate = jobs[j].accumulate != 0;
             const int rc = enqueue_tc(ctx, jobs[j].weight, k, ns[j], x, x_dtype, jobs[j].y_device, jobs[j].y_dtype, members, norm_weight, eps,
                                       extras);
+            if (rc != RIBN_OK) return rc;
+        }
+        return RIBN_OK;
+    }
+    if (all_mma) {
+        const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
+        for (uint32_t j = 0; j < job_count; ++j) {
+            const int rc = enqueue_mma(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
+                                       jobs[j].accumulate != 0, j > 0);
             if (rc != RIBN_OK) return rc;
         }
         return RIBN_OK;
@@ -594,10 +669,12 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
         ctx->tc_split_operands = static_cast<int>(value);
         return RIBN_OK;
     }
+#ifdef RIBN_TRACE
     if (std::strcmp(name, "tc_trace") == 0 && (value == 0 || value == 1)) {
         ctx->tc_trace = static_cast<int>(value);
         return RIBN_OK;
     }
+#endif
     if (std::strcmp(name, "tc_row_copies") == 0 && (value == 0 || value == 1)) {
         ctx->tc_row_copies = static_cast<int>(value);
         return RIBN_OK;
@@ -620,6 +697,26 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {
         ctx->tc_min_members = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "mma_gemv") == 0 && (value == 0 || value == 1)) {
+        ctx->mma_gemv = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "mma_image_members") == 0 && value >= 1 && value <= 9) {
+        ctx->mma_image_members = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "mma_stages") == 0 && value >= 0 && value <= 8) {
+        ctx->mma_stages = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "mma_resident") == 0 && value >= 0 && value <= 3) {
+        ctx->mma_resident = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "mma_ctas") == 0 && value >= 0 && value <= 3) {
+        ctx->mma_ctas = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "gemv_path") == 0 && value >= 0 && value <= 2) {
@@ -728,6 +825,9 @@ int ribn_gemm(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight,
     return enqueue_tc(ctx, weight, k, n, x_device, RIBN_BF16, y_device, y_dtype, tokens);
 }
 
+#ifdef RIBN_TRACE
+// Diagnostics build only (not declared in the public header): copies the stamps the kernels recorded in the last
+// 64 KiB of the workspace (option "tc_trace" = 1) to the host.
 int ribn_debug_read_trace(ribn_ctx* ctx, void* host_dst, uint64_t bytes) {
     if (ctx == nullptr || host_dst == nullptr || bytes > kTraceBytes) return RIBN_E_INVALID_ARGUMENT;
     DeviceGuard guard(ctx->device);
@@ -737,6 +837,7 @@ int ribn_debug_read_trace(ribn_ctx* ctx, void* host_dst, uint64_t bytes) {
     if (e != cudaSuccess) return record_cuda(ctx, e, "trace readback");
     return RIBN_OK;
 }
+#endif
 
 int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {
     if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;

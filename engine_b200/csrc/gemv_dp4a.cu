@@ -72,16 +72,21 @@ struct Dp4aParams {
     int accumulate;                // y += W x
     int stages;
     int* status;
-    long long* trace;              // diagnostics (option tc_trace): wall-clock stamps of CTA 0, or null
+    long long* trace;              // diagnostics (builds with -DRIBN_TRACE): wall-clock stamps of CTA 0, or null
 };
 
-// trace[event] = globaltimer, CTA 0 only.
+// Diagnostics, compiled in with -DRIBN_TRACE only: trace[event] = globaltimer, CTA 0.
 __device__ __forceinline__ void wall_stamp(const Dp4aParams& p, int event) {
+#ifdef RIBN_TRACE
     if (p.trace != nullptr && blockIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         p.trace[event] = static_cast<long long>(t);
     }
+#else
+    (void)p;
+    (void)event;
+#endif
 }
 
 // Lanes per super-block and the geometry of a lane's 16 quant bytes.

@@ -91,6 +91,37 @@ cudaError_t launch_quantize_activations(const void* x, bool x_bf16, const float*
 cudaError_t launch_gemv_dp4a(const GemvArgs& args, bool* handled);
 bool gemv_dp4a_fits(uint32_t value_type, int k, int members);
 
+// Half2-unpack + mma.sync GEMV for 1..8 members (gemv_mma.cu).  Serves Q4_K / Q5_K / Q6_K tensors whose rows are
+// 16-byte aligned (a tiled TMA box streams them) and whose activation image fits shared memory.
+struct MmaGemvArgs {
+    const uint8_t* weights;
+    uint32_t value_type;
+    int k, n;
+    const void* x;            // [members][k] f32 or bf16 (mode 2: [members][2k])
+    bool x_bf16;
+    int mode;                 // 0 plain, 1 RMSNorm with norm_weight / eps first, 2 silu(gate) * up of [gate | up] rows
+    const float* norm_weight;
+    float eps;
+    const void* image;        // activation image made by launch_gemv_mma_image (then x is not read), or null
+    void* y;                  // [members][n]
+    bool y_bf16;
+    bool accumulate;          // y += W x
+    int members;              // 1..8
+    int planes;               // gemv_mma_planes(): f16 planes the activations are kept in
+    int stages;               // 0 = as many as fit
+    int resident;             // CTAs per SM the shared-memory plan allows for, 0 = up to three
+    int grid_ctas;            // CTAs per SM the grid is sized for, 0 = min(resident, 2)
+    int* device_status;
+    int sm_count;
+    long long* trace;         // diagnostics buffer (builds with -DRIBN_TRACE), or null
+    cudaStream_t stream;
+};
+bool gemv_mma_supports(uint32_t value_type, int k, int n, int members, const void* weights);
+int gemv_mma_planes(uint32_t value_type, int k, int members, bool x_bf16);
+size_t gemv_mma_image_bytes(int members, int k, int planes);
+cudaError_t launch_gemv_mma_image(const MmaGemvArgs& args, void* image);
+cudaError_t launch_gemv_mma(const MmaGemvArgs& args);
+
 // Tensor-core GEMM (tcgen05): Y[m][n] = sum_k dequant(W[n][k]) * X[m][k], X bf16.
 struct TcArgs {
     const uint8_t* weights;

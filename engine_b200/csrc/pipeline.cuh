@@ -56,6 +56,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// The same wait with an explicit suspend-time hint: the thread stays suspended for up to `hint_ns` per poll, so a
+// warp that waits for data takes few issue slots from the warps that compute.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    }
+    return false;
+}
+
 // Untiled bulk copy global -> shared of `bytes` (a multiple of 16; both
 // addresses 16-byte aligned), completion counted on `bar` in bytes.
 __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_global, uint32_t bytes, uint64_t* bar) {

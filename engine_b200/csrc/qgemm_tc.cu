@@ -63,10 +63,17 @@ constexpr int kTcThreads = (4 + kDequantWarps) * 32;
 // viewed as [N rows][row_bytes] of 16-bit elements; it needs row_bytes to be a multiple of 16.
 // Q6_K super-blocks (210 bytes) start on 2-byte boundaries: the box starts at the 16-byte
 // boundary below and is 240 bytes wide, and the remainder is an offset in shared memory.
-// Diagnostics (see TcParams::trace): one stamp per (role, step, event) from CTA (0,0,0).
+// Diagnostics (see TcParams::trace), compiled in with -DRIBN_TRACE only: one stamp per (role, step, event) from CTA (0,0,0).
 __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int event) {
+#ifdef RIBN_TRACE
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && step < 64)
         p.trace[(role * 64 + step) * 8 + event] = clock64();
+#else
+    (void)p;
+    (void)role;
+    (void)step;
+    (void)event;
+#endif
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>

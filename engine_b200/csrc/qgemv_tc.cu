@@ -66,19 +66,31 @@ constexpr int threads(int nt) { return (activation_warp(nt) + 1) * 32; }
 constexpr int kAccBuffers = 4;           // super-blocks whose products may wait in TMEM
 static_assert(kSlots == kSub, "slot s owns K step s of every super-block");
 
-// Diagnostics (see TcParams::trace): one stamp per (role, step, event) from CTA (0,0,0).
+// Diagnostics (see TcParams::trace), compiled in with -DRIBN_TRACE only: one stamp per (role, step, event) from CTA (0,0,0).
 __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int event) {
+#ifdef RIBN_TRACE
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && step < 64)
         p.trace[(role * 64 + step) * 8 + event] = clock64();
+#else
+    (void)p;
+    (void)role;
+    (void)step;
+    (void)event;
+#endif
 }
 
 // Wall-clock stamps (ns) of one CTA's phases: trace[(3 * 64 + 63) * 8 + event], CTA (0,0,0).
 __device__ __forceinline__ void wall_stamp(const TcParams& p, int event) {
+#ifdef RIBN_TRACE
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         p.trace[(3 * 64 + 63) * 8 + event] = static_cast<long long>(t);
     }
+#else
+    (void)p;
+    (void)event;
+#endif
 }
 
 template <uint32_t FMT, int NT, bool RAWTMA>

@@ -99,34 +99,27 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  * (GemvMode, decode.rs:298-307).
  *   "gemv_path":    0 = choose per shape (default), 1 = f32 CUDA-core kernel only,
  *                   2 = integer-dot kernel only (error if the shape does not fit);
- *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tensor-core kernel (default 5);
- *   "tc_four_row_bytes": bf16 batches of exactly four rows also use it when the encoded weights are at least this
- *                   many bytes (default 8 MiB; only while tc_min_members is 5);
- *   "tc_f32_activations": 1 = f32 batches may use it too (they are rounded to f16; default 0);
+ *   "mma_gemv":     1 = calls of up to eight rows per launch (and wider f32 batches, in groups of eight) use the
+ *                   half2-unpack + mma.sync kernel where it serves the shape (Q4_K / Q5_K / Q6_K, 16-byte aligned
+ *                   rows, at least 16 output rows); 0 = leave them to the integer-dot kernel (default 1);
+ *   "mma_image_members": launches of at least this many rows convert their activations in a pre-pass launch,
+ *                   narrower ones inside the GEMV kernel (1..9, default 3);
+ *   "mma_stages":   ring depth of that kernel, 0 = as many stages as fit (default);
+ *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tcgen05 decode kernel (default 9);
+ *   "tc_four_row_bytes": where the mma kernel does not serve a shape, bf16 batches of exactly four rows use the
+ *                   tcgen05 kernel when the encoded weights are at least this many bytes (default 8 MiB);
+ *   "tc_f32_activations": 1 = f32 batches may use the tcgen05 kernel too (they are rounded to f16; default 0);
  *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
  *                   kernel) instead of the f16 decode kernel (default 0);
- *   "dp4a_prepass": 0 = calls of 1..4 rows pack their activations inside the integer-dot kernel, every CTA its own
- *                   copy, instead of in a launch of their own (default 1: with dependent launch the separate pre-pass
- *                   overlaps the kernel before and the weight prefetch after it; packing in the kernel measured equal for
- *                   one row and 5-30 % slower for four rows and for K = 12288);
+ *   "dp4a_prepass": 0 = calls of 1..4 rows on the integer-dot kernel pack their activations inside it, every CTA
+ *                   its own copy, instead of in a launch of their own (default 1);
  *   "pdl":          programmatic dependent launch, process-wide: 0 = off, 1 = every kernel of the path, 2 = the GEMV
- *                   kernels and their pre-passes only (default: a kernel's prologue and weight prefetch overlap the
- *                   tail of the kernel before it; the small layer operators measured slower with it);
- *   "tc_trace":     1 = record pipeline clock stamps (see ribn_debug_read_trace);
- *   "tc_row_copies": 1 = the tensor-core kernel fetches raw weight rows with per-row bulk copies even
- *                   where one tiled TMA box per stage would do (kept for shapes whose rows are not
- *                   16-byte aligned, and for tests);
- *   "tc_ksplit":    split-K factor of the tensor-core kernel, 0 = choose per shape;
- *   "gemv_variant": tile geometry of the f32 kernel, 0 = default, 1..3 = alternatives
- *                   kept for measurement. */
+ *                   kernels and their pre-passes only (default);
+ *   "tc_row_copies": 1 = the tcgen05 kernels fetch raw weight rows with per-row bulk copies even where one tiled
+ *                   TMA box per stage would do (the path of shapes whose rows are not 16-byte aligned);
+ *   "tc_ksplit":    split-K factor of the tcgen05 kernels, 0 = choose per shape;
+ *   "gemv_variant": tile geometry of the f32 kernel, 0 = default, 1..3 = alternatives. */
 int ribn_set_option(ribn_ctx *ctx, const char *name, int64_t value);
-
-/* Diagnostics, no counterpart in the reference: with option "tc_trace" = 1 the decode tensor-core
- * kernel records SM clock stamps of its pipeline events (first CTA, first 64 K steps) in the last
- * 64 KiB of the context workspace; this call waits for the stream and copies them out
- * (int64 trace[(role*64 + step)*8 + event]; roles: 0 MMA issuer, 1 unpack warp, 2 accumulate warp,
- * 3 weight producer). */
-int ribn_debug_read_trace(ribn_ctx *ctx, void *host_dst, uint64_t bytes);
 
 /* tensor_layout (crates/gguf/src/lib.rs:1051-1083): GGML type -> (elements per
  * block, bytes per block).  RIBN_E_UNSUPPORTED_TYPE for unknown ids. */

@@ -27,7 +27,7 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE = os.environ.get("RIBN_REFERENCE_ROOT", "/root/reference")
+REFERENCE = os.environ.get("RIBN_REFERENCE_ROOT", "")   # root of a checkout of the reference project; unset = build nothing
 KERNELS = os.path.join(REFERENCE, "crates", "nvidia", "src", "kernels", "quantized")
 QUANTIZED_UNITS = ["common.cu", "q4_k.cu", "q8_0.cu", "q6_k.cu", "q5_k.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-cubin"]
@@ -41,8 +41,8 @@ def nvcc() -> str:
 
 
 def build() -> list[str]:
-    if not os.path.isdir(KERNELS):
-        print(f"reference tree not found at {REFERENCE}; keeping whatever is in {OUT}")
+    if not REFERENCE or not os.path.isdir(KERNELS):
+        print(f"RIBN_REFERENCE_ROOT does not name a checkout of the reference project; keeping whatever is in {OUT}")
         return []
     os.makedirs(OUT, exist_ok=True)
     built = []

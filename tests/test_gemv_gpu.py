@@ -23,13 +23,16 @@ KERNELS = {8: engine_b200.CudaQ8_0Gemv, 12: engine_b200.CudaQ4KGemv, 13: engine_
 NAMES = {"q8_0": 8, "q4_k": 12, "q5_k": 13, "q6_k": 14}
 
 
-@pytest.fixture(params=[0, 1], ids=["auto", "f32-kernel"], autouse=True)
+@pytest.fixture(params=[0, 1, 2], ids=["auto", "f32-kernel", "integer-dot"], autouse=True)
 def gemv_path(request, ctx):
-    """Every test runs twice: with the default kernel choice (integer-dot kernel for up to four
-    members per launch) and with the f32 CUDA-core kernel forced."""
-    ctx.set_option("gemv_path", request.param)
+    """Every test runs three times: with the default kernel choice (half2-unpack + mma.sync kernel for up to
+    eight members per launch where it serves the shape), with the f32 CUDA-core kernel forced, and with the
+    mma kernel switched off, which leaves 1..4 member rows to the integer-dot kernel."""
+    ctx.set_option("gemv_path", 1 if request.param == 1 else 0)
+    ctx.set_option("mma_gemv", 0 if request.param == 2 else 1)
     yield request.param
     ctx.set_option("gemv_path", 0)
+    ctx.set_option("mma_gemv", 1)
 
 
 def upload(ctx, vt, encoded, k, n, name="w"):
@@ -146,6 +149,52 @@ def test_q8_0_input_sizes_that_are_not_multiples_of_256(ctx, k, n):
         x = synth.random_activations(members, k, seed=members)
         y, x_seen = run_gemv(ctx, 8, weight, x, n)
         check(8, w, k, n, y, x_seen)
+
+
+# ---- the mma kernel's two ways of getting its activations (converted inside the kernel / pre-pass image), every
+# member count, f32 (two f16 planes) and bf16 (one) inputs; and members of one launch do not influence each other:
+# a row's result is the same bits whatever the batch around it (the reference asserts the same of its batch
+# kernels, crates/nvidia/tests/cuda_reference.rs:5243-5337)
+@pytest.mark.parametrize("vt", [12, 13, 14])
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype):
+    if gemv_path != 0:
+        pytest.skip("the mma kernel is the default path only")
+    k, n = 4096, 528
+    w = synth.random_weight(vt, k, n, seed=vt)
+    weight = upload(ctx, vt, w, k, n)
+    x = synth.random_activations(8, k, seed=5)
+    x[2, 256:512] = 0.0            # an all-zero K slice
+    x[3, 1024:1280] *= 3e5         # slices of one row far apart in magnitude
+    x[3, 1280:1536] *= 1e-6
+    results = {}
+    try:
+        for image_members in (1, 9):
+            ctx.set_option("mma_image_members", image_members)
+            for members in range(1, 9):
+                y, x_seen = run_gemv(ctx, vt, weight, x[:members], n, x_dtype=x_dtype)
+                check(vt, w, k, n, y, x_seen)
+                results[(image_members, members)] = y
+    finally:
+        ctx.set_option("mma_image_members", 3)
+    full = results[(1, 8)]
+    for (image_members, members), y in results.items():
+        assert np.array_equal(y, full[:members]), (image_members, members)
+
+
+def test_q6_k_full_range_scales(ctx):
+    """Q6_K scales over the whole int8 range: sc * (q - 32) reaches 4096, beyond the integers f16 holds exactly."""
+    k, n = 2048, 64
+    w = np.array(synth.random_weight(14, k, n, seed=77)).reshape(-1).view(np.uint8).copy()
+    blocks = w.reshape(-1, 210)
+    rng = np.random.default_rng(3)
+    blocks[:, 192:208] = rng.integers(0, 256, size=(blocks.shape[0], 16), dtype=np.uint8)
+    blocks[::7, 192:208] = 0x80    # -128 everywhere in some blocks
+    weight = upload(ctx, 14, w, k, n)
+    for members in (1, 8):
+        x = synth.random_activations(members, k, seed=members)
+        y, x_seen = run_gemv(ctx, 14, weight, x, n)
+        check(14, w, k, n, y, x_seen)
 
 
 def test_every_tuning_variant_agrees(ctx, gemv_path):
@@ -332,6 +381,7 @@ def test_activations_packed_inside_the_kernel(ctx, vt, members, x_dtype, fused):
     gain_host = (1.0 + 0.02 * rng.standard_normal(k)).astype(np.float32)
     y = torch.full((members, n), float("nan"), device=ctx.device)
     ctx.set_option("dp4a_prepass", 0)
+    ctx.set_option("mma_gemv", 0)
     try:
         if fused:
             KERNELS[vt].from_context(ctx).execute_rms_norm(weight, x, torch.from_numpy(gain_host).to(ctx.device), 1e-6, y, members)
@@ -340,6 +390,7 @@ def test_activations_packed_inside_the_kernel(ctx, vt, members, x_dtype, fused):
         ctx.synchronize()
     finally:
         ctx.set_option("dp4a_prepass", 1)
+        ctx.set_option("mma_gemv", 1)
     seen = x.float().cpu().numpy()
     check(vt, w, k, n, y.cpu().numpy().astype(np.float64), oracle.rms_norm(seen, gain_host, 1e-6) if fused else seen)
 

@@ -10,6 +10,7 @@ import pytest
 import torch
 
 import engine_b200
+import oracle
 from engine_b200 import _lib, synth
 
 pytestmark = pytest.mark.gpu
@@ -31,10 +32,13 @@ def test_matches_ribn_gemv_on_two_calls_in_a_row(vt):
     device = torch.device("cuda", 0)
     torch.cuda.synchronize()
     k, n = 4096, 1536
-    w = torch.from_numpy(synth.random_weight(vt, k, n, seed=vt)).to(device)
+    w_host = synth.random_weight(vt, k, n, seed=vt)
+    w = torch.from_numpy(w_host).to(device)
     weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [k, n]), vt, w)
     ctx = engine_b200.RibnContext(0)
     try:
+        # ribn_gemv on the integer-dot kernel, the one the no-allocation entry point runs
+        ctx.set_option("mma_gemv", 0)
         kernel = engine_b200.QwenGemvKernel.from_value_type(vt, ctx)
         for call, (members, dtype) in enumerate([(4, torch.float32), (1, torch.bfloat16)]):
             x = torch.from_numpy(synth.random_activations(members, k, seed=10 + call)).to(device).to(dtype)
@@ -46,6 +50,10 @@ def test_matches_ribn_gemv_on_two_calls_in_a_row(vt):
             assert status == _lib.RIBN_OK, message
             # same kernels, same arithmetic: the tolerance of the GEMV tests (2e-3 relative) is met with equality
             assert torch.equal(got, want)
+            # and against the CPU oracle's f64 product, with the GEMV tests' bound
+            seen = x.float().cpu().numpy()
+            error = oracle.max_rel_error(got.cpu().numpy(), oracle.gemv_f64(vt, w_host, k, n, seen), oracle.gemv_scale(vt, w_host, k, n, seen))
+            assert error <= 2e-3, error
     finally:
         ctx.close()
 
