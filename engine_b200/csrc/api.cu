@@ -38,6 +38,7 @@ struct ribn_ctx {
     int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
     int64_t tc_four_row_bytes = 8 << 20;   // batches of four rows use the tensor-core kernel too when the weights are at least this large
     int tc_min_members = 9;         // batches of at least this many rows go to the tcgen05 decode kernel
+    int tmem_gemv = 0;              // 1 = Q4_K / Q5_K calls of up to 8 f32 / 16 bf16 rows use the kernel that unpacks the weights into tensor memory
     int mma_gemv = 1;               // 1 = batches of up to eight rows use the half2-unpack + mma.sync kernel where it serves the shape
     int mma_image_members = 3;      // launches of at least this many rows convert their activations in a pre-pass, fewer inside the kernel
     int mma_stages = 0;             // ring depth of that kernel, 0 = as many stages as fit
@@ -295,6 +296,43 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
     return RIBN_OK;
 }
 
+// The tcgen05 kernel with the weight operand in tensor memory.
+bool tmem_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, uint32_t members, int x_dtype) {
+    if (ctx->tmem_gemv == 0 || ctx->gemv_path != 0) return false;
+    return ribn::qgemv_tmem_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), static_cast<int>(members), x_dtype == RIBN_BF16,
+                                     w->data);
+}
+
+int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
+                 float eps, void* y, int y_dtype, uint32_t members, bool accumulate) {
+    ribn::TmemGemvArgs a{};
+    a.weights = static_cast<const uint8_t*>(w->data);
+    a.value_type = w->value_type;
+    a.k = static_cast<int>(k);
+    a.n = static_cast<int>(n);
+    a.x = x;
+    a.x_bf16 = x_dtype == RIBN_BF16;
+    a.mode = mode;
+    a.norm_weight = norm_weight;
+    a.eps = eps;
+    a.y = y;
+    a.y_bf16 = y_dtype == RIBN_BF16;
+    a.accumulate = accumulate;
+    a.members = static_cast<int>(members);
+    a.scratch = ctx->workspace;
+    a.scratch_bytes = ctx->workspace_bytes;
+    a.tickets = ctx->tickets;
+    a.ticket_count = kTicketCount;
+    a.force_ksplit = ctx->tc_ksplit;
+    a.stages = ctx->mma_stages;
+    a.device_status = ctx->device_status;
+    a.sm_count = ctx->sm_count;
+    a.stream = ctx->stream;
+    const cudaError_t e = ribn::launch_qgemv_tmem(a);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+    return RIBN_OK;
+}
+
 // The half2-unpack + mma.sync kernel, eight member rows per launch.  mode: 0 plain, 1 RMSNorm, 2 silu(gate) * up.
 // `image_ready` = the activation images of this x are already in the workspace (an earlier projection of the
 // same fused call made them).
@@ -333,7 +371,10 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
         a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
         a.stream = ctx->stream;
         const uint64_t image_bytes = ribn::gemv_mma_image_bytes(a.members, a.k, a.planes);
-        if (a.members >= ctx->mma_image_members && image_offset + image_bytes <= ctx->workspace_bytes) {
+        // Narrow launches convert their activations inside the kernel (no second launch on the critical path); from
+        // about four slices per warp on, the conversion is worth a launch of its own (measured: two rows over K = 12288).
+        const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24);
+        if (wide && image_offset + image_bytes <= ctx->workspace_bytes) {
             void* image = static_cast<uint8_t*>(ctx->workspace) + image_offset;
             image_offset += image_bytes;
             if (!image_ready) {
@@ -368,6 +409,8 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     // rounding (2^-12) is below the one the caller applied to the activations (2^-9); f32 activations
     // would lose 13 bits, so they take it only on request.  Its scratch is the f16 copy of the activations.
     // (Measured: a 16-token tile of the tensor-core kernel beats the integer-dot kernel's four rows from ~8 MB of weights up.)
+    if (tmem_serves(ctx, w, k, n, members, x_dtype))
+        return enqueue_tmem(ctx, w, k, n, x, x_dtype, norm_weight != nullptr ? 1 : 0, norm_weight, eps, y, y_dtype, members, false);
     const bool mma = mma_serves(ctx, w, k, n, members);
     const bool tc_batch = members >= static_cast<uint32_t>(ctx->tc_min_members) ||
                           (!mma && (members >= 5 || (members == 4 && static_cast<int64_t>(w->encoded_bytes) >= ctx->tc_four_row_bytes)));
@@ -450,6 +493,17 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
     for (uint32_t j = 0; j < job_count; ++j) {
         all_tc = all_tc && ribn::qgemm_tc_supports(jobs[j].weight->value_type, static_cast<int>(k));
         all_dp4a = all_dp4a && ribn::gemv_dp4a_fits(jobs[j].weight->value_type, static_cast<int>(k), members_per_launch);
+    }
+    bool all_tmem = true;
+    for (uint32_t j = 0; j < job_count; ++j) all_tmem = all_tmem && tmem_serves(ctx, jobs[j].weight, k, ns[j], members, x_dtype);
+    if (all_tmem) {
+        const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
+        for (uint32_t j = 0; j < job_count; ++j) {
+            const int rc = enqueue_tmem(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
+                                        jobs[j].accumulate != 0);
+            if (rc != RIBN_OK) return rc;
+        }
+        return RIBN_OK;
     }
     int64_t smallest = INT64_MAX;
     bool all_mma = true;
@@ -697,6 +751,10 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tc_min_members") == 0 && value >= 1) {
         ctx->tc_min_members = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "tmem_gemv") == 0 && (value == 0 || value == 1)) {
+        ctx->tmem_gemv = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "mma_gemv") == 0 && (value == 0 || value == 1)) {

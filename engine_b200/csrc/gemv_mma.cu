@@ -38,6 +38,7 @@
 #include "pipeline.cuh"
 #include "tc_host.h"
 #include "tcgen05.cuh"
+#include "unpack.cuh"
 
 namespace ribn {
 namespace {
@@ -48,8 +49,6 @@ constexpr int kMmaThreads = kConsumers + 32;   // + the producer warp
 constexpr int kTileRows = 16;                  // weight rows per tile (the M of m16n8k16)
 constexpr int kMaxStages = 8;
 constexpr int kMaxMembers = 8;                 // the N of m16n8k16
-constexpr uint32_t kMagic = 0x64006400u;       // half2 (1024, 1024)
-constexpr uint32_t kMagicBytes = 0x64646464u;
 
 template <uint32_t FMT>
 struct MmaGeometry;
@@ -131,11 +130,6 @@ __host__ __device__ inline size_t image_bytes(int members, int k, int planes) {
     return image_x16_bytes(members, k, planes) + image_sums_bytes(members, nsb) + image_scale_bytes(nsb);
 }
 
-__device__ __forceinline__ uint32_t half2_bits(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 __device__ __forceinline__ uint32_t group_index(uint32_t j, uint32_t member) {
     return (j ^ ((((j >> 4) ^ (j >> 5)) & 1u) << 3)) ^ (member & 3u);
 }
@@ -165,17 +159,14 @@ __device__ __forceinline__ void load_slice(const MmaParams& p, int m, int sb, in
 __device__ __forceinline__ void store_slice(const MmaParams& p, int m, int sb, int lane, float (&v)[8], uint8_t* x16_row, size_t plane_bytes,
                                             __half* sums_row, float* scale) {
     const int k0 = sb * kSuperBlock + lane * 8;
-    float amax = 0.0f;
-    bool bad = false;
+    // Largest magnitude of the warp's 256 values in one warp reduction: non-negative floats order like their bit
+    // patterns, and infinities and NaNs (0x7f800000 and above) come out on top, which is how they are detected.
+    uint32_t biggest = 0u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float a = fabsf(v[j]);
-        bad = bad || !(a <= 3.0e38f);   // NaN or infinity
-        amax = fmaxf(amax, a);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    bad = __any_sync(0xffffffffu, bad);
+    for (int j = 0; j < 8; ++j) biggest = max(biggest, __float_as_uint(fabsf(v[j])));
+    biggest = __reduce_max_sync(0xffffffffu, biggest);
+    const bool bad = biggest >= 0x7f800000u;
+    const float amax = __uint_as_float(biggest);
     // amax * 2^e in [512, 1024); e clamped so that both 2^e and 2^-e are normal numbers
     int e = 9 - (static_cast<int>(__float_as_uint(amax) >> 23) - 127);
     e = max(-100, min(100, e));
@@ -309,59 +300,6 @@ __device__ __forceinline__ float partial_square_sum(const MmaParams& p, int m, i
     return acc;
 }
 
-// ---------------------------------------------------------------- shared-memory and tensor-core primitives
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-template <int OFFSET>
-__device__ __forceinline__ uint2 lds64_at(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFFSET));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
-    uint32_t v;
-    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ int lds_s8(uint32_t a) {
-    int v;
-    asm volatile("{ .reg .s8 t; ld.shared.s8 t, [%1]; cvt.s32.s8 %0, t; }" : "=r"(v) : "r"(a));
-    return v;
-}
-// (a & b) | c in one logic instruction (the integer pipe issues at half rate on this GPU, so every logic op counts twice)
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
 // D += A(16x16, f16, row) * B(16x8, f16, col), f32 accumulate.  Lane (g = lane / 4, t = lane % 4) holds
 //   a0: row g, K slots 2t,2t+1     a1: row g+8, same slots     a2: row g, K slots 2t+8,2t+9     a3: row g+8
 //   b0: column g, K slots 2t,2t+1  b1: column g, K slots 2t+8,2t+9
@@ -413,23 +351,8 @@ __device__ __forceinline__ void mma_step(float (&c)[4], uint32_t x_addr, uint32_
     }
 }
 
-// half2 (lo, lo) / (hi, hi) of a packed pair
-__device__ __forceinline__ uint32_t dup_low(uint32_t pair) {
-    const __half2 h = __low2half2(*reinterpret_cast<const __half2*>(&pair));
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ uint32_t dup_high(uint32_t pair) {
-    const __half2 h = __high2half2(*reinterpret_cast<const __half2*>(&pair));
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 template <uint32_t FMT>
 struct MmaFormat;
-
-// Scale pairs of Q4_K / Q5_K as f16: bytes (lo, lo + 1) of `packed` -> half2 (b_lo, b_lo+1), exactly.
-__device__ __forceinline__ uint32_t byte_pair_half2(uint32_t packed, bool upper) {
-    return hsub2(__byte_perm(packed, kMagicBytes, upper ? 0x4342u : 0x4140u), kMagic);
-}
 
 // ---- Q4_K.  Lane t of a quad owns, per row, the 16-byte chunks t and t + 4 of the 128 quant bytes: chunk c
 // holds positions 16(c&1)..+15 of the sub-block pair c >> 1 (low nibbles: sub-block 2(c>>1), high nibbles the next).
@@ -544,42 +467,6 @@ struct MmaFormat<kQ5_K> {
 // from qh bytes 32 n2 + 16 h, bit pairs 2v).  Step (v, i): K elements 256 sb + 128 n2 + 32 v + 16 h + 4 i + {0,2,1,3}.
 // Super-blocks are 210 bytes, so a lane's 16-byte chunks start on 2-byte boundaries: two aligned 16-byte loads and
 // a funnel shift by the (warp-uniform) misalignment.
-__device__ __forceinline__ uint4 lds128_unaligned(uint32_t a) {
-    const uint32_t base = a & ~15u;
-    const uint32_t word = (a >> 2) & 3u;
-    const uint32_t shift = (a & 2u) * 8u;
-    const uint4 lo = lds128(base), hi = lds128(base + 16);
-    uint4 r;
-    switch (word) {   // uniform across the warp
-        case 0:
-            r.x = __funnelshift_r(lo.x, lo.y, shift); r.y = __funnelshift_r(lo.y, lo.z, shift);
-            r.z = __funnelshift_r(lo.z, lo.w, shift); r.w = __funnelshift_r(lo.w, hi.x, shift);
-            break;
-        case 1:
-            r.x = __funnelshift_r(lo.y, lo.z, shift); r.y = __funnelshift_r(lo.z, lo.w, shift);
-            r.z = __funnelshift_r(lo.w, hi.x, shift); r.w = __funnelshift_r(hi.x, hi.y, shift);
-            break;
-        case 2:
-            r.x = __funnelshift_r(lo.z, lo.w, shift); r.y = __funnelshift_r(lo.w, hi.x, shift);
-            r.z = __funnelshift_r(hi.x, hi.y, shift); r.w = __funnelshift_r(hi.y, hi.z, shift);
-            break;
-        default:
-            r.x = __funnelshift_r(lo.w, hi.x, shift); r.y = __funnelshift_r(hi.x, hi.y, shift);
-            r.z = __funnelshift_r(hi.y, hi.z, shift); r.w = __funnelshift_r(hi.z, hi.w, shift);
-            break;
-    }
-    return r;
-}
-
-// The four 6-bit quants of one (group v, word i), as bytes shifted left by two: (q << 2) in every byte.
-template <int V>
-__device__ __forceinline__ uint32_t q6_bytes(uint32_t la, uint32_t lb, uint32_t h) {
-    if (V == 0) return and_or(la << 2, 0x3c3c3c3cu, (h << 6) & 0xc0c0c0c0u);
-    if (V == 1) return and_or(lb << 2, 0x3c3c3c3cu, (h << 4) & 0xc0c0c0c0u);
-    if (V == 2) return and_or(la >> 2, 0x3c3c3c3cu, (h << 2) & 0xc0c0c0c0u);
-    return and_or(lb >> 2, 0x3c3c3c3cu, h & 0xc0c0c0c0u);
-}
-
 template <int PLANES>
 __device__ __forceinline__ void superblock_q6(uint32_t p0, uint32_t p1, const LaneX& lx, int t, float (&acc)[4]) {
     const uint32_t n2 = static_cast<uint32_t>(t >> 1), h = static_cast<uint32_t>(t & 1);

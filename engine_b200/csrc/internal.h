@@ -122,6 +122,34 @@ size_t gemv_mma_image_bytes(int members, int k, int planes);
 cudaError_t launch_gemv_mma_image(const MmaGemvArgs& args, void* image);
 cudaError_t launch_gemv_mma(const MmaGemvArgs& args);
 
+// tcgen05 GEMV with the weight operand unpacked into tensor memory (qgemv_tmem.cu): Q4_K / Q5_K, up to 8 f32 or
+// 16 bf16 member rows per launch.
+struct TmemGemvArgs {
+    const uint8_t* weights;
+    uint32_t value_type;
+    int k, n;
+    const void* x;            // [members][k] f32 or bf16 (mode 2: [members][2k])
+    bool x_bf16;
+    int mode;                 // 0 plain, 1 RMSNorm with norm_weight / eps first, 2 silu(gate) * up of [gate | up] rows
+    const float* norm_weight;
+    float eps;
+    void* y;                  // [members][n]
+    bool y_bf16;
+    bool accumulate;          // y += W x
+    int members;
+    void* scratch;            // split-K partial tiles
+    size_t scratch_bytes;
+    unsigned int* tickets;    // zero-initialised counters, one per row tile
+    int ticket_count;
+    int force_ksplit;         // 0 = choose
+    int stages;               // raw ring depth, 0 = as deep as fits
+    int* device_status;
+    int sm_count;
+    cudaStream_t stream;
+};
+bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_bf16, const void* weights);
+cudaError_t launch_qgemv_tmem(const TmemGemvArgs& args);
+
 // Tensor-core GEMM (tcgen05): Y[m][n] = sum_k dequant(W[n][k]) * X[m][k], X bf16.
 struct TcArgs {
     const uint8_t* weights;
