@@ -13,8 +13,11 @@ L2      = every (format, shape) has a ring of distinct weight copies larger than
 value   = device-resident inputs, CUDA-event timed on the launching stream.
 e2e     = the same sweep through ribn_gemv_host_async + one ribn_synchronize per step: pinned host activations in, host outputs out,
           copies inside the timed region.
+cases   = every (format, shape, members) timed on its own (bursts over its cold ring), with the fraction of the
+          measured HBM peak; `sustained` repeats the step for about a second so that the clock sampler sees it.
+parity  = largest error observed in this run, per kernel path, against the CPU checker (computed in the CPU-baseline leg).
 --impl reference = the CPU restatement of the reference's host path (dequantise a row, sequential
-          f32 dot; oracle/ribn_oracle.c) on all host threads, on a bounded sample of the sweep.
+          f32 dot; oracle/ribn_oracle.c) on all host threads, on a bounded sample (a row range) of every GEMV of the sweep.
 """
 from __future__ import annotations
 
@@ -68,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20", "-i",
                  str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -97,8 +100,10 @@ class ClockSampler:
             for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
                 if value.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        # under load: samples at or above 90 % of the highest clock seen are the ones taken while kernels ran
+        busy = [v for v in sm if v >= 0.9 * max(sm)] if sm else []
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm), "sm_mhz_all_median": float(np.median(sm)) if sm else None}
 
 
 def run_reference(args, rank: int, world: int) -> None:
@@ -110,19 +115,23 @@ def run_reference(args, rank: int, world: int) -> None:
     from engine_b200 import synth
 
     threads = os.cpu_count() or 1
-    sample_members = [1, 4]
+    # Every GEMV of the sweep, on a range of its rows sized so that one step is about a second of CPU work:
+    # rows / members (at least 64), i.e. the same number of multiply-adds per case.
     cases = []
+    step_bytes = 0
     for vt in FORMATS:
         for n, k in SHAPES:
-            w = synth.random_weight(vt, k, n, seed=vt * 100 + n // 1024 + k // 1024)
-            for m in sample_members:
+            w = synth.random_weight(vt, k, max(64, n // 4), seed=vt * 100 + n // 1024 + k // 1024)
+            for m in MEMBERS:
+                rows = max(64, n // (4 * m))
                 x = oracle_np.bf16_bits_to_f32(oracle_np.f32_to_bf16_bits(synth.random_activations(m, k, seed=m)))
-                cases.append((vt, n, k, m, w, x))
-    step_bytes = sum(case_bytes(vt, n, k, m) for vt, n, k, m, _, _ in cases)
+                sub = w[:synth.encoded_bytes(vt, k, rows)]
+                cases.append((vt, rows, k, m, sub, x))
+                step_bytes += case_bytes(vt, rows, k, m)
 
     def step():
-        for vt, n, k, m, w, x in cases:
-            oracle.gemv_f32(vt, w, k, n, x, threads=threads)
+        for vt, rows, k, m, w, x in cases:
+            oracle.gemv_f32(vt, w, k, rows, x, threads=threads)
 
     for _ in range(args.warmup):
         step()
@@ -131,13 +140,14 @@ def run_reference(args, rank: int, world: int) -> None:
         step()
     elapsed = time.perf_counter() - t0
     value = step_bytes * args.steps / elapsed / 1e9
-    sample = f"members {sample_members} of the sweep (24 of 48 GEMVs per step), all {threads} host threads, rows split over threads"
+    sample = (f"all {len(cases)} GEMVs of the sweep, each on its first max(64, N / (4 M)) rows; all {threads} host threads, rows split over threads; "
+              "GB/s counts the algorithmic bytes of the rows computed")
     line = {
         "impl": "reference", "metric": "qgemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "gemv_sweep", "formats": ["Q4_K", "Q5_K", "Q6_K"], "shapes_NxK": SHAPES,
-                   "members": sample_members, "activations": "bf16", "outputs": "f32"},
+                   "members": MEMBERS, "activations": "bf16", "outputs": "f32"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -153,9 +163,9 @@ TC_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.003
 
 def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
     source = f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s"
-    if dominant is None:   # a run restricted to calls of 1..4 member rows
+    if dominant is None:   # a run restricted to calls of up to eight member rows
         return {"bound": "hbm", "achieved": step_gbps, "peak": peak, "unit": "GB/s", "frac": step_gbps / peak, "traffic": None,
-                "peak_source": source, "kernel": "gemv_dp4a_kernel + activation pre-pass (all calls of the step)",
+                "peak_source": source, "kernel": "gemv_mma_kernel (+ activation pre-pass from three rows on), all calls of the step",
                 "bytes_per_step": step_bytes}
     achieved, us_per_call, bytes_per_call = dominant
     traffic = None if TC_TRAFFIC_PER_ALGORITHMIC_BYTE is None else TC_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_call
@@ -307,7 +317,35 @@ def time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, r
         torch.cuda.synchronize()
         ms = a.elapsed_time(b) / reps
         launches = sum(ref_cuda.launches_for(m) for _, _, _, m in cases)
+        # the same per member count: the reference serves 16 and 64 rows as two and eight launches that re-read the weights
+        by_members = {}
+        for members in sorted({m for _, _, _, m in cases}):
+            subset = [c for c in cases if c[3] == members]
+
+            def sub_step(subset=subset):
+                for vt, n, k, m in subset:
+                    ring = rings[(vt, n, k)]
+                    weight = ring[cursor[(vt, n, k)] % len(ring)]
+                    cursor[(vt, n, k)] += 1
+                    kernels.gemv(vt, weight.encoded_data(), x32[(k, m)], outs[(n, m)], k, n, m)
+
+            sub_graph = capture(sub_step)
+            with torch.cuda.stream(stream):
+                sub_replay = (lambda g=sub_graph: g.replay()) if sub_graph is not None else sub_step
+                for _ in range(3):
+                    sub_replay()
+                torch.cuda.synchronize()
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record(stream)
+                for _ in range(reps):
+                    sub_replay()
+                c1.record(stream)
+            torch.cuda.synchronize()
+            sub_ms = c0.elapsed_time(c1) / reps
+            sub_bytes = sum(case_bytes(*c) for c in subset)
+            by_members[str(members)] = {"GBps": round(sub_bytes / (sub_ms * 1e-3) / 1e9, 1), "us_per_call": round(sub_ms * 1e3 / len(subset), 2)}
         return {"value": step_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "launches_per_step": launches,
+                "by_members": by_members,
                 "kernels": "q{4,5,6}_k_gemv_warp (1 member row), q{4,5,6}_k_gemv_warp_batch (8 member rows per launch)",
                 "activations": "f32 (the reference has no bf16 input)", "cuda_graph": graph is not None,
                 "source": "the reference's .cu files compiled with nvcc for sm_100a, launched with the reference's geometry"}
@@ -315,15 +353,52 @@ def time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, r
         return {"unavailable": f"{type(exc).__name__}: {exc}"}
 
 
-def cpu_baseline_leg():
+def cpu_baseline_leg(ctx=None):
     """Bounded CPU sample for the main arm: the M=1 GEMV of every (format, shape), reference host
-    arithmetic, once single-threaded (the reference's host path is single-threaded) and once on all cores."""
+    arithmetic, once single-threaded (the reference's host path is single-threaded) and once on all cores.
+    The CPU results double as the checker of this run's GPU results: `parity` holds the largest error observed
+    per kernel path -- task metric |y - ref| / max(|ref|, sqrt(sum (w x)^2)) against the f64 product, the same
+    against the reference's sequential f32 product, and the strict metric of oracle.max_rel_error_strict."""
     import oracle
     from engine_b200 import synth
 
     threads = os.cpu_count() or 1
     total = 0
     t1 = tn = 0.0
+    parity = {}
+
+    def observe(path, vt, n, k, w, x_seen, y, f32_reference=None, norms=None):
+        ref = oracle.gemv_f64(vt, w, k, n, x_seen)
+        scale = oracle.gemv_scale(vt, w, k, n, x_seen)
+        entry = parity.setdefault(path, {"max_rel_err_vs_f64": 0.0, "max_rel_err_strict": 0.0, "cases": 0})
+        entry["max_rel_err_vs_f64"] = max(entry["max_rel_err_vs_f64"], oracle.max_rel_error(y, ref, scale))
+        if norms is None:
+            norms = oracle.row_norms(vt, w, k, n)
+        entry["max_rel_err_strict"] = max(entry["max_rel_err_strict"], oracle.max_rel_error_strict(y, ref, norms, x_seen))
+        if f32_reference is not None:
+            entry["max_rel_err_vs_reference_f32"] = max(entry.get("max_rel_err_vs_reference_f32", 0.0),
+                                                        oracle.max_rel_error(y, f32_reference, scale))
+        entry["cases"] += 1
+
+    def gpu_gemv(vt, w, k, n, x, dtype, options=()):
+        import torch
+
+        import engine_b200
+
+        for name, value in options:
+            ctx.set_option(name, value)
+        try:
+            data = torch.from_numpy(np.ascontiguousarray(w)).to(ctx.device)
+            weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("parity", [k, n]), vt, data)
+            xd = torch.from_numpy(x).to(ctx.device).to(dtype).contiguous()
+            yd = torch.full((x.shape[0], n), float("nan"), device=ctx.device)
+            engine_b200.QwenGemvKernel.from_value_type(vt, ctx).execute_warp_batch(weight, xd, yd, x.shape[0])
+            ctx.synchronize()
+            return yd.cpu().numpy().astype(np.float64), xd.float().cpu().numpy()
+        finally:
+            for name, _ in options:
+                ctx.set_option(name, {"mma_gemv": 1, "gemv_path": 0}[name])
+
     for vt in FORMATS:
         for n, k in SHAPES:
             w = synth.random_weight(vt, k, n, seed=1)
@@ -333,11 +408,28 @@ def cpu_baseline_leg():
             oracle.gemv_f32(vt, w, k, n, x, threads=1)
             t1 += time.perf_counter() - t0
             t0 = time.perf_counter()
-            oracle.gemv_f32(vt, w, k, n, x, threads=threads)
+            y32 = oracle.gemv_f32(vt, w, k, n, x, threads=threads)
             tn += time.perf_counter() - t0
-    return {"value": total / tn / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": "M=1 GEMV of all 12 (format, shape) pairs, one pass; rows split over all host threads",
-            "single_thread_value": total / t1 / 1e9}
+            if ctx is not None and not (n == 12288 or k == 12288):   # the two smaller shapes of every format
+                import torch
+
+                norms = oracle.row_norms(vt, w, k, n)
+                y, seen = gpu_gemv(vt, w, k, n, x, torch.float32)
+                observe("mma_f16x2_planes (1 row, f32 in)", vt, n, k, w, seen, y, f32_reference=y32, norms=norms)
+                x4 = synth.random_activations(4, k, seed=4)
+                y, seen = gpu_gemv(vt, w, k, n, x4, torch.bfloat16)
+                observe("mma_f16 (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                x16 = synth.random_activations(16, k, seed=16)
+                y, seen = gpu_gemv(vt, w, k, n, x16, torch.bfloat16)
+                observe("tcgen05_f16_tile (16 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("mma_gemv", 0),))
+                observe("integer_dot (1 row, f32 in)", vt, n, k, w, seen, y, norms=norms)
+                y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("gemv_path", 1),))
+                observe("f32_cuda_core (1 row, f32 in)", vt, n, k, w, seen, y, norms=norms)
+    result = {"value": total / tn / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+              "sample": "M=1 GEMV of all 12 (format, shape) pairs, one pass; rows split over all host threads",
+              "single_thread_value": total / t1 / 1e9}
+    return result, (parity if parity else None)
 
 
 def main() -> None:
@@ -355,7 +447,8 @@ def main() -> None:
     parser.add_argument("--no-decode", action="store_true", help="skip the decode-loop measurements")
     parser.add_argument("--decode-layers", type=int, default=0, help="layer count of the decode models (0 = the full 36 / 64)")
     parser.add_argument("--no-graph", action="store_true", help="time plain launches instead of a captured CUDA graph")
-    parser.add_argument("--cases", action="store_true", help="add a per-case GB/s breakdown (timed separately)")
+    parser.add_argument("--cases", action="store_true", help="(kept for older command lines: the per-case table is now always produced)")
+    parser.add_argument("--no-cases", action="store_true", help="skip the per-case table and the Q8_0 leg")
     parser.add_argument("--members", default="", help="comma-separated member counts replacing 1,4,16,64 (measurement runs, not the benchmark line)")
     parser.add_argument("--formats", default="", help="comma-separated formats (Q8_0,Q4_K,Q5_K,Q6_K) replacing the sweep's three")
     parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
@@ -423,9 +516,9 @@ def main() -> None:
     cursor = {key: 0 for key in rings}
     cases = [(vt, n, k, m) for vt in FORMATS for n, k in SHAPES for m in MEMBERS]
     step_bytes = sum(case_bytes(*c) for c in cases)
-    # Every call is two launches: an activation pre-pass (int8 planes for the integer-dot GEMV of 1..4 member
-    # rows, f16 rows for the tensor-core kernel of 5..64) and the GEMV kernel itself.
-    launches_per_step = 2 * len(cases)
+    # Launches per call: one for up to two member rows (the kernel converts its activations itself; two rows over more
+    # than 24 super-blocks take the pre-pass too), otherwise an activation pre-pass and the GEMV kernel.
+    launches_per_step = sum(1 if (m == 1 or (m == 2 and k // 256 <= 24)) else 2 for _, _, k, m in cases)
 
     def launch(vt, n, k, m):
         ring = rings[(vt, n, k)]
@@ -468,19 +561,18 @@ def main() -> None:
         else:
             step()
 
-    for _ in range(args.warmup):
-        run_step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        run_step()
+    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(ctx.stream)
     for _ in range(args.steps):
         run_step()
     stop.record(ctx.stream)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     ctx.synchronize()
     ms = start.elapsed_time(stop)
     if world > 1:
@@ -489,6 +581,19 @@ def main() -> None:
         ms = float(t.item())
     ms_per_step = ms / args.steps
     value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the same step repeated for about a second and a half, so that the clock sampler (20 ms period) sees it under load
+    sustained = None
+    if not args.only:
+        reps = max(args.steps, int(1500.0 / max(ms_per_step, 1e-3)))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(ctx.stream)
+        for _ in range(reps):
+            run_step()
+        b.record(ctx.stream)
+        barrier()
+        sustained_ms = a.elapsed_time(b)
+        sustained = {"steps": reps, "seconds": sustained_ms * 1e-3, "value": step_bytes * world * reps / (sustained_ms * 1e-3) / 1e9, "unit": "GB/s"}
 
     # ---- end to end: host activations in, host outputs out, through ribn_gemv_host
     max_stage = max(m * k * 2 + 256 + m * n * 4 for _, n, k, m in cases)
@@ -522,7 +627,7 @@ def main() -> None:
 
     # ---- roofline of the dominant kernel: the tensor-core decode kernel (batches of 5..64 member rows) takes
     # most of the step; its calls are timed on their own (same graph replay, same cold weight rings).
-    dominant = [c for c in cases if c[3] >= 5]
+    dominant = [c for c in cases if c[3] >= 9]
     dominant_roofline = None
     if dominant:
         def dominant_step():
@@ -564,7 +669,8 @@ def main() -> None:
         decode_results = decode_leg(args, ctx, device, rank, world, peak=measured_peak()[0])
 
     breakdown = None
-    if args.cases and rank == 0:
+    peak_now = measured_peak()[0]
+    if rank == 0 and not args.no_cases:
         breakdown = {}
         for c in cases:
             reps = 2 * len(rings[(c[0], c[1], c[2])])  # two trips round the ring of cold copies
@@ -585,10 +691,55 @@ def main() -> None:
             torch.cuda.synchronize()
             us = a.elapsed_time(b) / reps * 1e3
             vt, n, k, m = c
-            breakdown[f"{synth.TYPE_NAMES[vt]}_{n}x{k}_M{m}"] = {"us": round(us, 2), "GBps": round(case_bytes(*c) / us / 1e3, 1)}
+            gbps = case_bytes(*c) / us / 1e3
+            breakdown[f"{synth.TYPE_NAMES[vt]}_{n}x{k}_M{m}"] = {"us": round(us, 2), "GBps": round(gbps, 1), "frac_of_peak": round(gbps / peak_now, 3)}
 
+    # ---- Q8_0 (not part of the headline sweep): the same per-case protocol on two shapes
+    q8_0 = None
+    if rank == 0 and world == 1 and not args.no_cases and not args.only:
+        q8_0 = {}
+        try:
+            kernel8 = engine_b200.QwenGemvKernel.from_value_type(8, ctx)
+            for n, k in ((4096, 4096), (12288, 4096)):
+                nbytes = synth.encoded_bytes(8, k, n)
+                copies = (2 * L2_BYTES + nbytes - 1) // nbytes + 1
+                ring8 = [store.adopt(engine_b200.WeightTensorSpec.new(f"Q8_0.{n}x{k}.{c}", [k, n]), 8,
+                                     synth.random_weight_device(8, k, n, seed=8000 + c, device=device)) for c in range(copies)]
+                for m in (1, 4, 16, 64):
+                    x8 = torch.randn(m, k, device=device).to(torch.bfloat16)
+                    y8 = torch.empty(m, n, dtype=torch.float32, device=device)
+
+                    def burst8(ring8=ring8, x8=x8, y8=y8, m=m):
+                        for _ in range(2):
+                            for wgt in ring8:
+                                kernel8.execute_warp_batch(wgt, x8, y8, m)
+
+                    burst8()
+                    torch.cuda.synchronize()
+                    graph = capture(burst8)
+                    replay = (lambda g=graph: g.replay()) if graph is not None else burst8
+                    with torch.cuda.stream(stream):
+                        replay()
+                        torch.cuda.synchronize()
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(ctx.stream)
+                        replay()
+                        b.record(ctx.stream)
+                    torch.cuda.synchronize()
+                    us = a.elapsed_time(b) / (2 * len(ring8)) * 1e3
+                    gbps = case_bytes(8, n, k, m) / us / 1e3
+                    q8_0[f"Q8_0_{n}x{k}_M{m}"] = {"us": round(us, 2), "GBps": round(gbps, 1), "frac_of_peak": round(gbps / peak_now, 3)}
+                del ring8
+                torch.cuda.empty_cache()
+        except Exception as exc:
+            q8_0["error"] = f"{type(exc).__name__}: {exc}"
+
+    clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         peak, peak_kind = measured_peak()
+        cpu_baseline = parity = None
+        if not args.no_cpu_baseline and world == 1:
+            cpu_baseline, parity = cpu_baseline_leg(ctx)
         line = {
             "metric": "qgemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -604,16 +755,22 @@ def main() -> None:
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if sustained is not None:
+            line["sustained"] = sustained
         if breakdown is not None:
             line["cases"] = breakdown
+        if q8_0 is not None:
+            line["q8_0"] = q8_0
+        if parity is not None:
+            line["parity"] = parity
         if reference_cuda is not None:
             line["reference_cuda"] = reference_cuda
         if decode_results is not None:
             line["decode"] = decode_results
         if prefill_results is not None:
             line["prefill"] = prefill_results
-        if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline_leg()
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -105,6 +105,8 @@ SIGNATURES = {
                                       ctypes.c_int, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_gemv_noalloc": (ctypes.c_int, [ctypes.c_int, _vp, _qwp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_int,
                                          ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint64]),
+    "ribn_noalloc_status": (ctypes.c_int, [ctypes.c_int, _vp]),
+    "ribn_selftest_bounded_wait": (ctypes.c_int, [_vp, ctypes.c_uint32]),
     "ribn_gemv_fused": (ctypes.c_int, [_vp, ctypes.POINTER(GemvJob), ctypes.c_uint32, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64,
                                        ctypes.c_float, ctypes.c_uint32, ctypes.c_uint32]),
     "ribn_embedding": (ctypes.c_int, [_vp, _qwp, _vp, ctypes.c_uint32, _vp, ctypes.c_uint64]),

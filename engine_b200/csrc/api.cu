@@ -327,6 +327,7 @@ int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.stages = ctx->mma_stages;
     a.device_status = ctx->device_status;
     a.sm_count = ctx->sm_count;
+    a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
     a.stream = ctx->stream;
     const cudaError_t e = ribn::launch_qgemv_tmem(a);
     if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
@@ -615,6 +616,7 @@ ribn::LayerAttentionArgs attention_args(const ribn_ctx* ctx, const ribn_attentio
     r.v_cache = a->v_cache;
     r.max_context = static_cast<long long>(a->max_context);
     r.active_context = static_cast<long long>(a->active_context);
+    r.device_status = ctx->device_status;
     r.stream = ctx->stream;
     return r;
 }
@@ -681,8 +683,21 @@ int ribn_synchronize(ribn_ctx* ctx) {
     if (e != cudaSuccess) return record_cuda(ctx, e, "status readback");
     if (status != ribn::kDeviceOk) {
         cudaMemset(ctx->device_status, 0, sizeof(int));
+        if (status == ribn::kDevicePositionOutOfRange)
+            return record(ctx, fail(RIBN_E_INVALID_ARGUMENT,
+                                    "a KV-cache position read from device memory lay outside the cache; nothing was stored there and the "
+                                    "attention of that member is invalid"));
         return record(ctx, fail(RIBN_E_TIMEOUT, "a bounded device-side wait ran out; results of this stream are invalid"));
     }
+    return RIBN_OK;
+}
+
+int ribn_selftest_bounded_wait(ribn_ctx* ctx, uint32_t polls) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (polls == 0 || polls > 65536) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "polls must be 1..65536"));
+    DeviceGuard guard(ctx->device);
+    const cudaError_t e = ribn::launch_bounded_wait_selftest(ctx->device_status, polls, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "self-test launch");
     return RIBN_OK;
 }
 
@@ -916,9 +931,7 @@ int ribn_gemv_host(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* we
                    uint64_t x_len, void* y_host, int y_dtype, uint64_t y_len, uint32_t members) {
     const int status = ribn_gemv_host_async(ctx, expected_type, weight, x_host, x_dtype, x_len, y_host, y_dtype, y_len, members);
     if (status != RIBN_OK) return status;
-    const cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
-    return RIBN_OK;
+    return ribn_synchronize(ctx);   // also reports a bounded device wait that ran out
 }
 
 int ribn_gemv_host_async(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const void* x_host, int x_dtype,

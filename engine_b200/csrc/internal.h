@@ -43,6 +43,7 @@ cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
 // Device status word values written by kernels whose bounded waits ran out.
 constexpr int kDeviceOk = 0;
 constexpr int kDeviceWaitTimeout = 1;
+constexpr int kDevicePositionOutOfRange = 2;   // a KV-cache position read from device memory lay outside the cache (or the planned context)
 
 struct GemvArgs {
     const uint8_t* weights;   // GGUF blocks, 16-byte aligned
@@ -145,6 +146,7 @@ struct TmemGemvArgs {
     int stages;               // raw ring depth, 0 = as deep as fits
     int* device_status;
     int sm_count;
+    long long* trace;         // diagnostics buffer (builds with -DRIBN_TRACE), or null
     cudaStream_t stream;
 };
 bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_bf16, const void* weights);
@@ -201,6 +203,7 @@ struct LayerAttentionArgs {
     void* v_cache;
     long long max_context;    // tokens the cache holds per (member, head)
     long long active_context; // upper bound on positions + 1 in this call (plans the KV splits)
+    int* device_status;       // status word of the context: kernels report positions outside the cache here
     cudaStream_t stream;
 };
 cudaError_t launch_embedding(const uint8_t* weights, uint32_t value_type, int k, unsigned int vocabulary, const uint32_t* tokens,
@@ -213,6 +216,9 @@ cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint
                             int sm_count, cudaStream_t stream);
 cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream);
 cudaError_t launch_argmax(const float* logits, int members, uint64_t length, uint32_t* out, cudaStream_t stream);
+
+// One CTA polls an mbarrier nobody arrives at, at most `polls` times, then records kDeviceWaitTimeout in *status.
+cudaError_t launch_bounded_wait_selftest(int* status, uint32_t polls, cudaStream_t stream);
 
 cudaError_t launch_rms_norm(const void* x, bool x_bf16, const float* weight, void* y, bool y_bf16, int members,
                             int length, float eps, cudaStream_t stream);

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
                                                                   const float* __restrict__ k_norm, float eps,
                                                                   const int* __restrict__ positions, int q_heads, int kv_heads,
                                                                   int head_dim, int rot_pairs, float base, __half* __restrict__ k_cache,
-                                                                  __half* __restrict__ v_cache, long long max_context) {
+                                                                  __half* __restrict__ v_cache, long long max_context, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     __shared__ float values[256];
@@ -120,8 +120,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
     }
     if (in_place != nullptr) {
         in_place[t] = x;
-    } else {
+    } else if (position >= 0 && position < max_context) {
         cache[((static_cast<long long>(member) * kv_heads + head) * max_context + position) * head_dim + t] = __float2half_rn(x);
+    } else if (t == 0) {
+        // The position comes from device memory (a replayed graph advances it): outside the cache nothing is
+        // stored and the context's status word says so.
+        atomicExch(status, kDevicePositionOutOfRange);
     }
 }
 
@@ -138,7 +142,8 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              const __half* __restrict__ v_cache,
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
-                                                                             long long max_context, int chunk, float scale) {
+                                                                             long long max_context, int chunk, float scale, int active_context,
+                                                                             int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     // Two tiles of each: the next one streams in (cp.async) while the warps work on the current one.
@@ -153,7 +158,13 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int q_head = kv_head * group + warp;
-    const int tokens = positions[member] + 1;
+    // positions[] is device memory: the walk is clamped to the context the splits were planned for (at most the
+    // cache size), and a position outside it is reported through the status word
+    int tokens = positions[member] + 1;
+    if (tokens < 1 || tokens > active_context) {
+        if (threadIdx.x == 0 && split == 0 && kv_head == 0) atomicExch(status, kDevicePositionOutOfRange);
+        tokens = max(0, min(tokens, active_context));
+    }
     const int begin = split * chunk;
     const int end = min(tokens, begin + chunk);
 
@@ -376,7 +387,7 @@ cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& a) {
     const dim3 grid(a.q_heads + 2 * a.kv_heads, a.members);
     return launch_kernel_if(pdl_switch() == 1, qk_norm_rope_append_kernel, grid, dim3(a.head_dim), 0, a.stream, a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions,
                          a.q_heads, a.kv_heads, a.head_dim, a.rot_dims / 2, a.rope_base, static_cast<__half*>(a.k_cache),
-                         static_cast<__half*>(a.v_cache), a.max_context);
+                         static_cast<__half*>(a.v_cache), a.max_context, a.device_status);
 }
 
 int attention_splits(int members, int kv_heads, long long active_context, int sm_count) {
@@ -404,7 +415,8 @@ cudaError_t launch_attention_decode(const LayerAttentionArgs& a, float* out, voi
     const float scale = 1.0f / sqrtf(static_cast<float>(a.head_dim));
     cudaError_t e = launch_kernel_if(pdl_switch() == 1, attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
                                   static_cast<const float*>(a.q), static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache),
-                                  a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale);
+                                  a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale,
+                                  static_cast<int>(a.active_context), a.device_status);
     if (e != cudaSuccess) return e;
     return launch_kernel_if(pdl_switch() == 1, attention_combine_kernel, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
                          static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);

@@ -18,6 +18,7 @@
 // and must be serialised by the caller.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/ribn_b200.h"
@@ -35,8 +36,21 @@ constexpr unsigned long long kScratchBytes = kStatusBytes + kMaxActivations * 2 
 static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 constexpr int kMaxDevices = 64;
-unsigned char* g_scratch_address[kMaxDevices] = {};  // per device, filled by the first call on that device
+// Per device, filled by the first call on that device.  The address is published last (release) and read first
+// (acquire), so a thread that sees it also sees the SM count; two threads racing through the set-up write the same values.
+std::atomic<unsigned char*> g_scratch_address[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
+
+// Every buffer must be device (or managed) memory of `device`: a host pointer handed to the kernels would fault.
+// cudaPointerGetAttributes allocates nothing.
+bool on_device(const void* p, int device) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) && attr.device == device;
+}
 
 
 }  // namespace
@@ -81,9 +95,13 @@ int ribn_gemv_noalloc(int device, void* cuda_stream, const ribn_qweight* weight,
     int previous = -1;
     cudaGetDevice(&previous);
     if (previous != device && cudaSetDevice(device) != cudaSuccess) return fail(RIBN_E_DRIVER, "cannot select the device");
+    if (!on_device(weight->data, device) || !on_device(x_device, device) || !on_device(y_device, device)) {
+        if (previous >= 0 && previous != device) cudaSetDevice(previous);
+        return fail(RIBN_E_CONTEXT_MISMATCH, "quantized GEMV buffers and stream belong to different CUDA contexts");
+    }
     int status = RIBN_OK;
     // Set-up, once per device, with that device current: resolve the device address of the array.
-    if (g_scratch_address[device] == nullptr) {
+    if (g_scratch_address[device].load(std::memory_order_acquire) == nullptr) {
         unsigned char* address = nullptr;
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_scratch);
         int sm_count = 0;
@@ -93,12 +111,12 @@ int ribn_gemv_noalloc(int device, void* cuda_stream, const ribn_qweight* weight,
             status = RIBN_E_DRIVER;
         } else {
             g_sm_count[device] = sm_count;
-            g_scratch_address[device] = address;
+            g_scratch_address[device].store(address, std::memory_order_release);
         }
     }
     if (status == RIBN_OK) {
         cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-        unsigned char* scratch = g_scratch_address[device];
+        unsigned char* scratch = g_scratch_address[device].load(std::memory_order_acquire);
         int* device_status = reinterpret_cast<int*>(scratch);
         unsigned char* packed = scratch + kStatusBytes;
         // The array keeps the previous call's contents.  The packed rows are fully rewritten below;
@@ -145,6 +163,21 @@ int ribn_gemv_noalloc(int device, void* cuda_stream, const ribn_qweight* weight,
     }
     if (previous >= 0 && previous != device) cudaSetDevice(previous);
     return status;
+}
+
+int ribn_noalloc_status(int device, void* cuda_stream) {
+    if (device < 0 || device >= kMaxDevices) return RIBN_E_INVALID_ARGUMENT;
+    unsigned char* scratch = g_scratch_address[device].load(std::memory_order_acquire);
+    if (scratch == nullptr) return RIBN_OK;   // no call was ever made on this device
+    int previous = -1;
+    cudaGetDevice(&previous);
+    if (previous != device && cudaSetDevice(device) != cudaSuccess) return RIBN_E_DRIVER;
+    int flag = 0;
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
+    if (e == cudaSuccess) e = cudaMemcpy(&flag, scratch, sizeof flag, cudaMemcpyDeviceToHost);
+    if (previous >= 0 && previous != device) cudaSetDevice(previous);
+    if (e != cudaSuccess) return RIBN_E_DRIVER;
+    return flag == ribn::kDeviceOk ? RIBN_OK : RIBN_E_TIMEOUT;
 }
 
 }  // extern "C"

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 
 #include "internal.h"
+#include "pipeline.cuh"
 
 namespace ribn {
 namespace {
@@ -132,6 +133,24 @@ cudaError_t launch_rms_norm(const void* x, bool x_bf16, const float* weight, voi
     else
         rms_norm_kernel<float, float><<<members, kNormThreads, 0, stream>>>(static_cast<const float*>(x), weight,
                                                                               static_cast<float*>(y), length, vecs, eps);
+    return cudaGetLastError();
+}
+
+namespace {
+__global__ void bounded_wait_selftest_kernel(int* status, uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        bool arrived = false;
+        for (uint32_t spin = 0; spin < polls && !arrived; ++spin) arrived = mbar_try_wait(&bar, 0);
+        if (!arrived) atomicExch(status, kDeviceWaitTimeout);
+    }
+}
+}  // namespace
+
+cudaError_t launch_bounded_wait_selftest(int* status, uint32_t polls, cudaStream_t stream) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, polls);
     return cudaGetLastError();
 }
 

@@ -84,7 +84,21 @@ struct TmemParams {
     int k, n, nsb, members, planes, ksplit, raw_stages;
     int b_sb;                   // super-blocks the resident B tiles are laid out for (the largest K range of a CTA)
     int* status;
+    long long* trace;           // diagnostics (builds with -DRIBN_TRACE): SM clock stamps of CTA 0, or null
 };
+
+// trace[(warp * 16 + superblock) * 16 + event] = clock64(), CTA (0,0), lane 0.  Compiled in with -DRIBN_TRACE only.
+__device__ __forceinline__ void stamp(const TmemParams& p, int warp, int sb, int event) {
+#ifdef RIBN_TRACE
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && sb < 16 && event < 16)
+        p.trace[(warp * 16 + sb) * 16 + event] = clock64();
+#else
+    (void)p;
+    (void)warp;
+    (void)sb;
+    (void)event;
+#endif
+}
 
 template <uint32_t FMT>
 struct TmemPlan {
@@ -356,6 +370,7 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&a_full[j], i & 1));
                 if (!ok) break;
                 tcgen05_fence_after_sync();
+                stamp(p, warp, i, j * 2);
                 // pair j = K step j of the super-block (64 elements): B tile i * 4 + j, four K slices of 16
                 const uint64_t desc_b = desc_b0 + static_cast<uint64_t>((i * 4 + j) * (P::kBTileBytes >> 4));
 #pragma unroll
@@ -363,6 +378,7 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
                     umma_f16_tmem_a_elected(d_main, tmem_base + j * kPairColumns + slice * 8, desc_b + 2 * slice, idesc,
                                             (j > 0 || slice > 0) ? 1u : 0u);
                 umma_commit_elected(&a_empty[j]);
+                stamp(p, warp, i, j * 2 + 1);
             }
             if (!ok) break;
             // minimum term: A = the eight 6-bit minima twice, B = block sums hi | lo of this super-block
@@ -466,6 +482,7 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
                 atomicExch(p.status, kDeviceWaitTimeout);
                 ok = false;
             }
+            stamp(p, warp, i, 0);
             const uint32_t blk = raw_addr + static_cast<uint32_t>(s) * P::kRawStageBytes;
             const uint4 header = lds128(blk);   // d | dmin, 12 scale bytes
             uint32_t sc_lo, sc_hi, m_lo, m_hi;
@@ -490,18 +507,24 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
                     ok = false;
                 }
                 tcgen05_fence_after_sync();
+                stamp(p, warp, i, 1 + 4 * jj);
                 uint32_t out_lo[16], out_hi[16];
                 unpack_pair<FMT>(blk + kQuantOffset + 32 * j, blk + 16, j, byte_pair_half2(sc_word, jj != 0), out_lo, out_hi);
+                stamp(p, warp, i, 2 + 4 * jj);
                 tmem_st16(lane_base + j * kPairColumns, out_lo);
                 tmem_st16(lane_base + j * kPairColumns + 16, out_hi);
+                stamp(p, warp, i, 3 + 4 * jj);
                 tmem_st_wait();
+                stamp(p, warp, i, 4 + 4 * jj);
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[j]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[s]);
+            stamp(p, warp, i, 9);
             if (i > 0) read_back(i - 1, d_prev, dmin_prev);
+            stamp(p, warp, i, 10);
             d_prev = f16_bits_to_f32(header.x & 0xffffu);
             dmin_prev = f16_bits_to_f32(header.x >> 16);
         }
@@ -643,6 +666,7 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.ksplit = ksplit;
     p.raw_stages = raw_stages;
     p.b_sb = b_sb;
+    p.trace = a.trace;
     p.status = a.device_status;
     return launch_kernel(kernel, dim3(tiles, ksplit), dim3(kTmemThreads), smem, a.stream, wmap, p);
 }

@@ -84,9 +84,17 @@ typedef struct ribn_ctx ribn_ctx;
 int ribn_create(int device, void *cuda_stream, ribn_ctx **out);
 void ribn_destroy(ribn_ctx *ctx);
 
-/* Block until everything enqueued on the context's stream has finished and
- * report any bounded device wait that timed out (RIBN_E_TIMEOUT). */
+/* Block until everything enqueued on the context's stream has finished and report what the kernels flagged in
+ * the context's status word (then cleared): a bounded device wait that ran out (RIBN_E_TIMEOUT), or a KV-cache
+ * position read from device memory that lay outside the cache (RIBN_E_INVALID_ARGUMENT; nothing was stored
+ * there, the attention walk was clamped). */
 int ribn_synchronize(ribn_ctx *ctx);
+
+/* Self-test of the bounded-wait machinery, no counterpart in the reference: launches one small kernel that polls,
+ * at most `polls` times (1..65536), an mbarrier at which nothing ever arrives and that no copy targets; it gives
+ * up, sets the status word and returns.  The next ribn_synchronize must answer RIBN_E_TIMEOUT (and clear it).
+ * Nothing is left waiting on the GPU. */
+int ribn_selftest_bounded_wait(ribn_ctx *ctx, uint32_t polls);
 
 const char *ribn_status_string(int status);
 /* Message of the last failing call on `ctx`, worded like the Display impl of
@@ -215,13 +223,18 @@ int ribn_rms_norm(ribn_ctx *ctx, const void *x_device, int x_dtype, uint64_t x_l
  * host threads) race on the array: the caller serialises them.
  *
  * wait != 0: synchronise the stream before returning and report a bounded
- * device wait that ran out as RIBN_E_TIMEOUT.  error_message (may be NULL)
- * receives the text of a failure. */
+ * device wait that ran out as RIBN_E_TIMEOUT.  With wait == 0 nothing reads the status word in this call:
+ * ribn_noalloc_status(device, stream) synchronises the stream later and reports it.  error_message (may be NULL)
+ * receives the text of a failure.  Buffers that are not device memory of `device` are refused
+ * (RIBN_E_CONTEXT_MISMATCH) before anything is enqueued. */
 #define RIBN_NOALLOC_MAX_ACTIVATIONS 65536ull
 int ribn_gemv_noalloc(int device, void *cuda_stream, const ribn_qweight *weight,
                       const void *x_device, int x_dtype, uint64_t x_len,
                       void *y_device, int y_dtype, uint64_t y_len, uint32_t members, int wait,
                       char *error_message, uint64_t error_capacity);
+/* Synchronises `cuda_stream` and reports the status word the last ribn_gemv_noalloc call on `device` left:
+ * RIBN_OK, RIBN_E_TIMEOUT after a bounded device wait that ran out.  Allocates nothing.  No counterpart in the reference. */
+int ribn_noalloc_status(int device, void *cuda_stream);
 
 /* ribn_gemv_fused: several projections of the same activations behind one activation pre-pass, with the
  * operators the reference launches around them folded in -- the sequences of decode.rs:929-1052:
