@@ -275,10 +275,59 @@ def decode_leg(args, ctx, device, rank, world, peak):
             }
             del decoder
             torch.cuda.empty_cache()
-        results["reference_cuda_decode"] = "not measured (the reference's layer forward is Rust host code; only its GEMV kernels are timed here)"
+        if world == 1:
+            results["reference_cuda_decode"] = reference_decode_leg(ctx, geometry, weights, device)
     except Exception as exc:   # the sweep line must still be printed
         results["error"] = f"{type(exc).__name__}: {exc}"
     return results
+
+
+def reference_decode_leg(ctx, geometry, weights, device):
+    """The reference's own decode step on this GPU: its unmodified kernels in its launch order (oracle/ref_decode.py,
+    which also lists the substitutions), one CUDA graph per step, Qwen3-8B shape, 2048 tokens of context, batch 1 and 8
+    (its batch kernels serve at most eight members)."""
+    import torch
+    from oracle import ref_cuda, ref_decode
+
+    if not ref_cuda.available() or not os.path.exists(ref_cuda.MODEL_OPS_CUBIN):
+        return {"unavailable": "reference cubins not built here (oracle/build_ref.py needs the reference tree)"}
+    out = {"substitutions": "strided_rms_norm for the q head norm (q_gate_norm expects a gated q projection); a constant gate buffer of +88 so that "
+                            "attn_score_gqa's sigmoid gate is exactly 1; gate and up as two launches over one stored matrix; every timed step "
+                            "runs at one position (the middle of the generated range) because token and position are kernel arguments",
+           "source": "the reference's .cu sources compiled with nvcc for sm_100a, launched in the order of decode.rs:544-632, :929-1052, :678-696 "
+                     "(batch: :1990-2140, :2868-3036) with the geometry of model_ops.rs / quantized.rs"}
+    context_tokens, generated = 2048, 256
+    try:
+        for members in (1, 8):
+            reference = ref_decode.ReferenceDenseDecode(geometry, weights, members, context_tokens + generated + 8, device)
+            reference.fill_context(context_tokens + generated // 2)
+            position = context_tokens + generated // 2
+            with torch.cuda.stream(ctx.stream):
+                reference.step(7, position)
+            torch.cuda.synchronize()
+            launches = reference.ops.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=ctx.stream):
+                reference.step(7, position)
+            with torch.cuda.stream(ctx.stream):
+                for _ in range(2):
+                    graph.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ctx.stream)
+                steps = 20
+                for _ in range(steps):
+                    graph.replay()
+                b.record(ctx.stream)
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            out[f"batch{members}"] = {"tokens_per_s": members / (ms * 1e-3), "ms_per_step": ms, "launches_per_step": launches, "members": members,
+                                      "context": context_tokens, "position": position, "cuda_graph": True}
+            del reference, graph
+            torch.cuda.empty_cache()
+    except Exception as exc:
+        out["error"] = f"{type(exc).__name__}: {exc}"
+    return out
 
 
 def time_reference_cuda(cases, rings, acts, outs, capture, stream, step_bytes, reps):

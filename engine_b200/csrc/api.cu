@@ -344,7 +344,7 @@ bool mma_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t
 }
 
 int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
-                float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready) {
+                float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready, bool shared_image = false) {
     const bool x_bf16 = x_dtype == RIBN_BF16;
     const uint64_t x_row_bytes = k * (mode == 2 ? 2 : 1) * dtype_bytes(x_dtype);
     uint64_t image_offset = 0;
@@ -374,7 +374,9 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
         const uint64_t image_bytes = ribn::gemv_mma_image_bytes(a.members, a.k, a.planes);
         // Narrow launches convert their activations inside the kernel (no second launch on the critical path); from
         // about four slices per warp on, the conversion is worth a launch of its own (measured: two rows over K = 12288).
-        const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24);
+        // Several projections of one normalised or gated input share the image: the norm / activation runs once.
+        const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
+                          (shared_image && ctx->mma_image_members <= 8);
         if (wide && image_offset + image_bytes <= ctx->workspace_bytes) {
             void* image = static_cast<uint8_t*>(ctx->workspace) + image_offset;
             image_offset += image_bytes;
@@ -531,7 +533,7 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
         for (uint32_t j = 0; j < job_count; ++j) {
             const int rc = enqueue_mma(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
-                                       jobs[j].accumulate != 0, j > 0);
+                                       jobs[j].accumulate != 0, j > 0, job_count > 1 && mode != 0);
             if (rc != RIBN_OK) return rc;
         }
         return RIBN_OK;

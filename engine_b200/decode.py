@@ -191,8 +191,19 @@ class CudaDenseDecode:
         self.tokens = torch.zeros(m, dtype=torch.int32, device=dev)       # u32 on the device side
         self.positions = torch.zeros(m, dtype=torch.int32, device=dev)
         self.hidden = torch.zeros(m, g.hidden, **f32)
-        self.q = torch.zeros(m, s["q_heads"] * g.head_dim, **f32)
-        self.k = torch.zeros(m, s["kv_heads"] * g.head_dim, **f32)
+        # One sequence: q and k projections of the same format run as one GEMV over their concatenated rows
+        # ([q | k] is then contiguous in the output, which the one-member layout of q and k allows).
+        q_dim, k_dim = s["q_heads"] * g.head_dim, s["kv_heads"] * g.head_dim
+        self.qk_weights = {}
+        if m == 1:
+            for i in range(g.layers):
+                wq, wk = weights.matrices.get(f"blk.{i}.attn_q"), weights.matrices.get(f"blk.{i}.attn_k")
+                if wq is not None and wk is not None and wq.value_type() == wk.value_type():
+                    joined = torch.cat([wq.encoded_data(), wk.encoded_data()])
+                    self.qk_weights[i] = CudaQuantizedWeight(WeightTensorSpec.new(f"blk.{i}.attn_qk", [g.hidden, q_dim + k_dim]), wq.value_type(), joined)
+        self.qk = torch.zeros(m, q_dim + k_dim, **f32)
+        self.q = self.qk[:, :q_dim] if m == 1 else torch.zeros(m, q_dim, **f32)
+        self.k = self.qk[:, q_dim:] if m == 1 else torch.zeros(m, k_dim, **f32)
         self.v = torch.zeros(m, s["kv_heads"] * g.head_dim, **f32)
         self.attended = torch.zeros(m, s["q_heads"] * g.head_dim, **f32)
         self.projected = torch.zeros(m, g.hidden, **f32)
@@ -213,7 +224,11 @@ class CudaDenseDecode:
     def _fused(self, names_outputs, x: torch.Tensor, norm: torch.Tensor | None = None, swiglu: bool = False, accumulate: bool = False) -> None:
         jobs = [(self.weights.matrices[name], y, accumulate) for name, y in names_outputs]
         gemv_fused(self.context, jobs, x, self.members, norm, self.geometry.eps, swiglu)
-        self.launches_per_step += 1 + len(jobs) * (1 if self.members > 4 else (self.members + 3) // 4)
+        # one launch per projection, plus the activation pre-pass where one runs (from three members on, for wide
+        # two-member inputs, and whenever several projections share a normalised or gated input)
+        shared = len(jobs) > 1 and (norm is not None or swiglu)
+        prepass = self.members >= 3 or shared or (self.members == 2 and x.shape[-1] // (2 if swiglu else 1) // 256 > 24)
+        self.launches_per_step += len(jobs) + (1 if prepass else 0)
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         torch.distributed.all_reduce(t, group=self.group)
@@ -222,14 +237,19 @@ class CudaDenseDecode:
     def _layer(self, i: int) -> None:
         g, s, w = self.geometry, self.shapes, self.weights
         parallel = self.group is not None and self.world > 1
-        self._fused([(f"blk.{i}.attn_q", self.q), (f"blk.{i}.attn_k", self.k), (f"blk.{i}.attn_v", self.v)], self.hidden,
-                    norm=w.vectors[f"blk.{i}.attn_norm"])
+        if i in self.qk_weights:
+            jobs = [(self.qk_weights[i], self.qk, False), (w.matrices[f"blk.{i}.attn_v"], self.v, False)]
+            gemv_fused(self.context, jobs, self.hidden, self.members, w.vectors[f"blk.{i}.attn_norm"], g.eps, False)
+            self.launches_per_step += 3
+        else:
+            self._fused([(f"blk.{i}.attn_q", self.q), (f"blk.{i}.attn_k", self.k), (f"blk.{i}.attn_v", self.v)], self.hidden,
+                        norm=w.vectors[f"blk.{i}.attn_norm"])
         attention = attention_descriptor(g, self.members, s["q_heads"], s["kv_heads"], w.vectors[f"blk.{i}.attn_q_norm"],
                                          w.vectors[f"blk.{i}.attn_k_norm"], self.positions, self.k_cache[i], self.v_cache[i],
                                          self.max_context, self.active_context)
         self.ops.qk_norm_rope_append(attention, self.q, self.k, self.v)
         self.ops.attention_decode(attention, self.q, self.attended)
-        self.launches_per_step += 3
+        self.launches_per_step += 3   # head norm + rope + cache append; split-KV attention; merge of the splits
         if parallel:
             # partial sums of the column-split projection: all-reduce, then the residual
             self._fused([(f"blk.{i}.attn_output", self.projected)], self.attended)

@@ -99,6 +99,10 @@ class RibnContext:
     def synchronize(self) -> None:
         self.check(self._lib.ribn_synchronize(self.handle))
 
+    def selftest_bounded_wait(self, polls: int = 1000) -> None:
+        """Launches a kernel whose bounded wait runs out by design; the next synchronize() must raise kind 'Timeout'."""
+        self.check(self._lib.ribn_selftest_bounded_wait(self.handle, polls))
+
     def set_option(self, name: str, value: int) -> None:
         self.check(self._lib.ribn_set_option(self.handle, name.encode(), value))
 

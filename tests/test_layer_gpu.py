@@ -81,6 +81,55 @@ def test_qk_norm_rope_append(ctx, ops, members, q_heads, kv_heads):
         assert not k_cache[m][:, untouched].any() and not v_cache[m][:, untouched].any()
 
 
+# ---- a position outside the cache (they live in device memory; a replayed graph advances them): nothing is written
+# past the cache, the attention walk is clamped, and the context reports it
+def test_positions_outside_the_cache_are_refused_on_the_device(ctx, ops):
+    d, max_context, members, q_heads, kv_heads = 128, 16, 2, 4, 2
+    rng = np.random.default_rng(0)
+    q = device(ctx, rng.standard_normal((members, q_heads, d)).astype(np.float32))
+    k = device(ctx, rng.standard_normal((members, kv_heads, d)).astype(np.float32))
+    v = device(ctx, rng.standard_normal((members, kv_heads, d)).astype(np.float32))
+    # caches with a guard band of canary values on both sides
+    band = 4 * kv_heads * max_context * d
+    storage_k = torch.full((band + members * kv_heads * max_context * d + band,), 3.0, dtype=torch.float16, device=ctx.device)
+    storage_v = torch.full_like(storage_k, 3.0)
+    k_cache = storage_k[band:-band].view(members, kv_heads, max_context, d)
+    v_cache = storage_v[band:-band].view(members, kv_heads, max_context, d)
+    out = torch.zeros(members, q_heads * d, device=ctx.device)
+    for bad in (max_context, max_context + 1000, -1):
+        positions = device(ctx, np.array([3, bad], np.int32))
+        attention = _lib.Attention(members, q_heads, kv_heads, d, d, 1e6, 1e-6, None, None, positions.data_ptr(), k_cache.data_ptr(),
+                                   v_cache.data_ptr(), max_context, max_context)
+        ops.qk_norm_rope_append(attention, q, k, v)
+        with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+            ctx.synchronize()
+        assert e.value.kind == "InvalidArgument" and "outside the cache" in str(e.value)
+        ctx.synchronize()   # the status word was cleared
+        assert torch.all(storage_k[:band] == 3.0) and torch.all(storage_k[-band:] == 3.0)
+        assert torch.all(storage_v[:band] == 3.0) and torch.all(storage_v[-band:] == 3.0)
+        assert torch.all(k_cache[1] == 3.0)            # nothing stored for the member with the bad position
+        assert not torch.all(k_cache[0, :, 3] == 3.0)  # the good member was appended
+        ops.attention_decode(attention, q, out)
+        with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+            ctx.synchronize()
+        assert e.value.kind == "InvalidArgument"
+        ctx.synchronize()
+
+
+def test_bounded_wait_selftest_reports_a_timeout(ctx):
+    ctx.selftest_bounded_wait(500)
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:
+        ctx.synchronize()
+    assert e.value.kind == "Timeout"
+    ctx.synchronize()   # cleared, and the context is still usable
+    x = torch.ones(8, 256, device=ctx.device)
+    y = torch.empty_like(x)
+    decode.CudaDenseOps(ctx)   # constructs without error
+    engine_b200.CudaQwen35Ops.from_context(ctx).rms_norm_batch(x, torch.ones(256, device=ctx.device), y, 256, 1e-6)
+    ctx.synchronize()
+    assert torch.allclose(y, torch.ones_like(y), atol=1e-5)
+
+
 # ---- attention over the cache
 @pytest.mark.parametrize("members,q_heads,kv_heads,tokens", [(1, 4, 2, 1), (1, 32, 8, 2048), (3, 8, 2, 77), (2, 8, 1, 300), (32, 32, 8, 64)])
 def test_attention_decode(ctx, ops, members, q_heads, kv_heads, tokens):

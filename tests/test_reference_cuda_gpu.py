@@ -75,3 +75,36 @@ def test_dequantize_matches_reference_gemv_on_unit_vectors(ctx, reference):
         reference.gemv_warp(vt, wd, x, y, k, n)
         torch.cuda.synchronize()
         assert np.array_equal(y.cpu().numpy(), ours[:, column])
+
+
+# ---- the reference's decode step, composed from its own kernels (oracle/ref_decode.py), against ours on the same model
+@pytest.mark.parametrize("members", [1, 3])
+def test_decode_step_matches_the_reference_kernels_composition(members):
+    from engine_b200 import decode
+    from oracle import ref_decode
+
+    if not ref_cuda.available():
+        pytest.skip("reference cubins not built (oracle/build_ref.py needs the reference tree)")
+    stream = torch.cuda.Stream()
+    context = engine_b200.RibnContext(0, stream=stream)
+    try:
+        geometry = decode.DenseGeometry(hidden=1024, layers=2, q_heads=8, kv_heads=2, head_dim=128, intermediate=1536, vocabulary=777)
+        weights = decode.random_weights(context, geometry, seed=5)
+        ours = decode.CudaDenseDecode(context, geometry, weights, members, 16)
+        theirs = ref_decode.ReferenceDenseDecode(geometry, weights, members, 16, context.device)
+        token = 123
+        for position in range(4):
+            ours.tokens.fill_(token)
+            ours.positions.fill_(position)
+            ours.run_step()
+            context.synchronize()
+            with torch.cuda.stream(stream):
+                theirs.step(token, position)
+            torch.cuda.synchronize()
+            a, b = ours.logits.cpu().numpy(), theirs.logits.cpu().numpy()
+            scale = np.max(np.abs(b))
+            assert np.max(np.abs(a - b)) <= 2e-3 * scale, (position, float(np.max(np.abs(a - b)) / scale))
+            assert np.array_equal(ours.next_tokens.cpu().numpy(), theirs.selected.cpu().numpy())
+            token = int(theirs.selected[0])
+    finally:
+        context.close()

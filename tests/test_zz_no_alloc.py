@@ -71,3 +71,35 @@ def test_refuses_sizes_beyond_the_fixed_scratch():
     assert status == _lib.RIBN_E_INVALID_WEIGHT
     torch.cuda.synchronize()
     assert torch.all(y == 7.0)
+
+
+def test_refuses_buffers_that_are_not_device_memory():
+    """A host pointer handed to the kernels would fault the GPU: it is refused before anything is enqueued."""
+    device = torch.device("cuda", 0)
+    k, n = 512, 32
+    w = torch.from_numpy(synth.random_weight(12, k, n, seed=2)).to(device)
+    weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [k, n]), 12, w)
+    y = torch.full((n,), 7.0, device=device)
+    host_x = torch.zeros(k).pin_memory()
+    lib = _lib.load()
+    message = ctypes.create_string_buffer(256)
+    descriptor = weight.descriptor()
+    status = lib.ribn_gemv_noalloc(0, ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream), ctypes.byref(descriptor),
+                                   host_x.data_ptr(), _lib.RIBN_F32, k, y.data_ptr(), _lib.RIBN_F32, n, 1, 1, message, len(message))
+    assert status == _lib.RIBN_E_CONTEXT_MISMATCH, message.value
+    torch.cuda.synchronize()
+    assert torch.all(y == 7.0)
+
+
+def test_status_reader_after_an_enqueue_only_call():
+    device = torch.device("cuda", 0)
+    k, n = 1024, 64
+    w = torch.from_numpy(synth.random_weight(12, k, n, seed=3)).to(device)
+    weight = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [k, n]), 12, w)
+    x = torch.randn(2, k, device=device)
+    y = torch.full((2, n), float("nan"), device=device)
+    status, message = call_noalloc(weight, x, y, 2, wait=0)
+    assert status == _lib.RIBN_OK, message
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    assert _lib.load().ribn_noalloc_status(0, stream) == _lib.RIBN_OK
+    assert torch.isfinite(y).all()
