@@ -206,6 +206,105 @@ def gemv_input(k: int) -> np.ndarray:
     return np.array([(i % 17) * 0.125 - 1.0 for i in range(k)], np.float32)
 
 
+def lcg_eighths(state: int, count: int) -> tuple[np.ndarray, int]:
+    """The reference tests' value generator (crates/nvidia/tests/cuda_reference.rs:1669-1673): a 32-bit
+    linear congruential step, then bits 16..21 as multiples of 0.125 in [-4, 4) - exact in f16."""
+    values = np.empty(count, np.float32)
+    for i in range(count):
+        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
+        values[i] = np.float32(((state >> 16) & 0x3F) * 0.125 - 4.0)
+    return values, state
+
+
+def layer_fixtures() -> dict[str, np.ndarray]:
+    """Inputs and host-replay expectations of three reference device tests, restated with sequential
+    float32 arithmetic as the tests' own host loops do:
+      rope        cuda_reference.rs:1996-2038  4 heads x 256 dims, 64 rotary dims, base 1e7, position 3, tolerance 1e-5
+      attention   cuda_reference.rs:2062-2160  6 q heads over 2 kv heads, head size 32, 3 cached tokens, sigmoid output gate
+                                                read from the second half of each 2*head_dim slice, tolerance 1e-3
+      kv append   cuda_reference.rs:3435-3500  4 kv heads x 256 dims appended at tokens 0 and 3 of a 5-token f16 cache
+    """
+    f32 = np.float32
+    out: dict[str, np.ndarray] = {}
+    heads, head_dim, rot, base, position = 4, 256, 64, f32(1.0e7), 3
+    x = np.array([f32(i % 97) * f32(0.03) - f32(1.4) for i in range(heads * head_dim)], np.float32)
+    expect = x.copy()
+    for head in range(heads):
+        for pair in range(rot // 2):
+            exponent = -(f32(2.0) * f32(pair)) / f32(rot)
+            theta = f32(position) * f32(np.power(base, exponent, dtype=np.float32))
+            sin, cos = f32(np.sin(theta)), f32(np.cos(theta))
+            x0, x1 = expect[head * head_dim + pair], expect[head * head_dim + rot // 2 + pair]
+            expect[head * head_dim + pair] = x0 * cos - x1 * sin
+            expect[head * head_dim + rot // 2 + pair] = x0 * sin + x1 * cos
+    out["rope_input"], out["rope_expect"] = x.reshape(heads, head_dim), expect.reshape(heads, head_dim)
+    out["rope_params"] = np.array([rot, position, 1.0e7], np.float64)
+
+    q_heads, kv_heads, d, tokens = 6, 2, 32, 3
+    state = 12345
+    q, state = lcg_eighths(state, q_heads * d)
+    gate, state = lcg_eighths(state, q_heads * 2 * d)
+    keys, state = lcg_eighths(state, tokens * kv_heads * d)
+    values, state = lcg_eighths(state, tokens * kv_heads * d)
+    scale = f32(1.0) / f32(np.sqrt(f32(d)))
+    plain = np.zeros(q_heads * d, np.float32)
+    gated = np.zeros(q_heads * d, np.float32)
+    for head in range(q_heads):
+        kv = head // (q_heads // kv_heads)
+        scores = []
+        for token in range(tokens):
+            start = (token * kv_heads + kv) * d
+            total = f32(0.0)
+            for i in range(d):
+                total = f32(total + q[head * d + i] * keys[start + i])
+            scores.append(f32(total * scale))
+        top = max(scores)
+        exps = [f32(np.exp(f32(s - top))) for s in scores]
+        denom = f32(0.0)
+        for e in exps:
+            denom = f32(denom + e)
+        for dim in range(d):
+            acc = f32(0.0)
+            for token, e in enumerate(exps):
+                acc = f32(acc + f32(e / denom) * values[(token * kv_heads + kv) * d + dim])
+            g = gate[head * 2 * d + d + dim]
+            plain[head * d + dim] = acc
+            gated[head * d + dim] = f32(acc * f32(f32(1.0) / f32(f32(1.0) + f32(np.exp(-g)))))
+    out["attn_q"] = q.reshape(q_heads, d)
+    out["attn_gate"] = gate.reshape(q_heads, 2 * d)
+    out["attn_keys"] = keys.reshape(tokens, kv_heads, d)
+    out["attn_values"] = values.reshape(tokens, kv_heads, d)
+    out["attn_expect_ungated"] = plain.reshape(q_heads, d)
+    out["attn_expect"] = gated.reshape(q_heads, d)
+
+    kv_heads, d, tokens = 4, 256, 5
+    state = 909
+    keys, state = lcg_eighths(state, kv_heads * d)
+    values, state = lcg_eighths(state, kv_heads * d)
+    cache = np.zeros((tokens, kv_heads * d), np.uint16)
+    bits = f16_bits_of_eighths(keys)
+    cache[0], cache[3] = bits, bits
+    out["append_keys"], out["append_values"] = keys.reshape(kv_heads, d), values.reshape(kv_heads, d)
+    out["append_key_cache_bits"] = cache.reshape(tokens, kv_heads, d)
+    return out
+
+
+def f16_bits_of_eighths(values: np.ndarray) -> np.ndarray:
+    """Binary16 patterns of multiples of 0.125 below 4 in magnitude, composed from sign, exponent and
+    fraction without a half-precision type (cuda_reference.rs:1679-1703)."""
+    bits = np.zeros(values.shape, np.uint16)
+    for i, value in enumerate(values):
+        if value == 0.0:
+            continue
+        magnitude, exponent = abs(float(value)), 0
+        while magnitude >= 2.0:
+            magnitude, exponent = magnitude * 0.5, exponent + 1
+        while magnitude < 1.0:
+            magnitude, exponent = magnitude * 2.0, exponent - 1
+        bits[i] = (0x8000 if value < 0 else 0) | ((exponent + 15) * 1024 + int((magnitude - 1.0) * 1024.0))
+    return bits
+
+
 def main() -> None:
     import sys
 
@@ -238,6 +337,7 @@ def main() -> None:
     out["rms_input"], out["rms_weight"] = x, w
     out["rms_eps"] = np.array([1e-5], np.float32)
     out["rms_expect"] = (x.astype(np.float64) * inv * w.astype(np.float64))
+    out.update(layer_fixtures())
     path = os.path.join(HERE, "golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")

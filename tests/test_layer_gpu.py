@@ -162,6 +162,68 @@ def test_attention_decode(ctx, ops, members, q_heads, kv_heads, tokens):
             assert np.max(np.abs(got - ref)) <= 2e-5 * max(1.0, np.max(np.abs(ref)))
 
 
+# ---- the reference's device-test inputs (tests/cuda_reference.rs:1996-2038, :2062-2160, :3435-3500 of the reference
+# project), regenerated by its own value generator at the head size this library serves (128; the reference tests use
+# 256 and 32); expectations come from the restatement that the CPU suite pins to the reference's host replays
+def _eighths(state, count):
+    values = np.empty(count, np.float32)
+    for i in range(count):
+        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
+        values[i] = ((state >> 16) & 0x3F) * 0.125 - 4.0
+    return values, state
+
+
+def test_reference_rope_and_append_inputs_at_the_served_head_size(ctx, ops):
+    d, rot, base, position, max_context, eps = 128, 64, 1.0e7, 3, 5, 1e-6
+    q = np.array([(i % 97) * 0.03 - 1.4 for i in range(d)], np.float32).reshape(1, 1, d)
+    state = 909
+    k, state = _eighths(state, d)
+    v, state = _eighths(state, d)
+    k, v = k.reshape(1, 1, d), v.reshape(1, 1, d)
+    # one head of each kind and a constant weight equal to its root mean square turn the fused norm into the identity
+    q_norm = np.full(d, np.sqrt(np.mean(q.astype(np.float64) ** 2) + eps), np.float32)
+    k_norm = np.full(d, np.sqrt(np.mean(k.astype(np.float64) ** 2) + eps), np.float32)
+    qd, kd, vd = device(ctx, q), device(ctx, k), device(ctx, v)
+    k_cache = torch.zeros(1, 1, max_context, d, dtype=torch.float16, device=ctx.device)
+    v_cache = torch.zeros_like(k_cache)
+    qn, kn = device(ctx, q_norm), device(ctx, k_norm)
+    for token in (0, 3):                                     # the reference test appends at tokens 0 and 3 of five
+        pos = device(ctx, np.array([token], np.int32))
+        attention = _lib.Attention(1, 1, 1, d, rot, base, eps, qn.data_ptr(), kn.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                                   v_cache.data_ptr(), max_context, max_context)
+        qd.copy_(device(ctx, q))
+        ops.qk_norm_rope_append(attention, qd, kd, vd)
+        ctx.synchronize()
+    expect = layer_np.rope_neox(q[0], position, rot, base)
+    assert np.max(np.abs(qd[0].cpu().numpy() - expect)) < 1e-5 + 2e-6          # the reference's 1e-5 and the norm's rounding
+    bits = v_cache[0, 0].cpu().numpy().view(np.uint16)
+    exact = v[0, 0].astype(np.float16).view(np.uint16)                          # eighths: the f16 pattern is the value itself
+    assert np.array_equal(bits[0], exact) and np.array_equal(bits[3], exact) and not bits[[1, 2, 4]].any()
+    assert not k_cache[0, 0, [1, 2, 4]].any()
+
+
+def test_reference_attention_inputs_at_the_served_head_size(ctx, ops):
+    q_heads, kv_heads, d, tokens, max_context = 6, 2, 128, 3, 16
+    state = 12345
+    q, state = _eighths(state, q_heads * d)
+    _, state = _eighths(state, q_heads * 2 * d)              # the output gate of the reference's hybrid model: not on this path
+    keys, state = _eighths(state, tokens * kv_heads * d)
+    values, state = _eighths(state, tokens * kv_heads * d)
+    keys, values = keys.reshape(tokens, kv_heads, d), values.reshape(tokens, kv_heads, d)
+    k_cache = torch.zeros(1, kv_heads, max_context, d, dtype=torch.float16, device=ctx.device)
+    v_cache = torch.zeros_like(k_cache)
+    k_cache[0, :, :tokens] = device(ctx, keys.transpose(1, 0, 2), torch.float16)
+    v_cache[0, :, :tokens] = device(ctx, values.transpose(1, 0, 2), torch.float16)
+    positions = device(ctx, np.array([tokens - 1], np.int32))
+    out = torch.full((1, q_heads * d), float("nan"), device=ctx.device)
+    attention = _lib.Attention(1, q_heads, kv_heads, d, d, 1e6, 1e-6, None, None, positions.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                               max_context, max_context)
+    ops.attention_decode(attention, device(ctx, q.reshape(1, q_heads, d)), out)
+    ctx.synchronize()
+    expect = layer_np.attention(q.reshape(q_heads, d), keys, values)
+    assert np.max(np.abs(out[0].cpu().numpy().reshape(q_heads, d) - expect)) < 1e-3      # the reference test's tolerance
+
+
 # ---- elementwise and argmax
 def test_silu_mul_and_residual_add(ctx, ops):
     rng = np.random.default_rng(0)

@@ -56,3 +56,42 @@ def test_dense_model_cache_grows_and_is_deterministic():
     for position, token in enumerate([3, 7, 7]):
         assert np.array_equal(a.step(token, position), b.step(token, position))
     assert a.keys[0].shape == (3, kv, d)
+
+
+def _golden():
+    import os
+
+    return np.load(os.path.join(os.path.dirname(__file__), "golden", "golden.npz"))
+
+
+def test_rope_matches_the_reference_device_test_expectation():
+    """Input and host replay of executes_rope_sigmoid_against_host_equations (tests/cuda_reference.rs:1996-2038
+    of the reference project), with that test's tolerance."""
+    g = _golden()
+    rot, position, base = g["rope_params"]
+    out = layer_np.rope_neox(g["rope_input"], int(position), int(rot), float(base))
+    assert np.abs(out - g["rope_expect"]).max() < 1e-5
+    assert np.array_equal(out[:, int(rot):], g["rope_input"][:, int(rot):])
+
+
+def test_attention_matches_the_reference_device_test_expectation():
+    """executes_attn_score_gqa_against_host_equations (tests/cuda_reference.rs:2062-2160): grouped heads over an
+    f16 cache; the reference kernel's output gate is applied outside the restated function."""
+    g = _golden()
+    keys, values = layer_np.to_f16(g["attn_keys"]), layer_np.to_f16(g["attn_values"])
+    assert np.array_equal(keys, g["attn_keys"]) and np.array_equal(values, g["attn_values"])     # eighths are exact in f16
+    out = layer_np.attention(g["attn_q"], keys, values)
+    assert np.abs(out - g["attn_expect_ungated"]).max() < 1e-3
+    d = out.shape[1]
+    gated = out * (1.0 / (1.0 + np.exp(-g["attn_gate"][:, d:])))
+    assert np.abs(gated - g["attn_expect"]).max() < 1e-3
+
+
+def test_cache_rounding_matches_the_reference_device_test_expectation():
+    """executes_kv_append_f16_against_host_rounding (tests/cuda_reference.rs:3435-3500): the appended rows hold the
+    binary16 pattern of each value, composed there without a half type; untouched rows stay zero."""
+    g = _golden()
+    bits = g["append_key_cache_bits"]
+    rounded = layer_np.to_f16(g["append_keys"]).astype(np.float16).view(np.uint16)
+    assert np.array_equal(bits[0], rounded) and np.array_equal(bits[3], rounded)
+    assert not bits[[1, 2, 4]].any()
