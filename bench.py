@@ -241,9 +241,29 @@ def decode_leg(args, ctx, device, rank, world, peak):
         for name, members, context_tokens in plans:
             decoder = decode.CudaDenseDecode(ctx, geometry, weights, members, context_tokens + generated + 8, process_group=group,
                                              world=world, rank=rank)
-            decoder.fill_context(context_tokens)
-            decoder.capture(advance=True)
-            decoder.fill_context(context_tokens)   # the eager step inside capture() advanced nothing but wrote one cache slot
+            prefill = None
+            if world == 1:
+                # the context is a real prompt: random tokens through the prefill path (tensor-core GEMM, shared-cache
+                # attention), which leaves the KV entries and the first generated token of every sequence
+                prompt_generator = torch.Generator(device="cpu")
+                prompt_generator.manual_seed(members)
+                prompts = torch.randint(0, geometry.vocabulary, (members, context_tokens), generator=prompt_generator, dtype=torch.int32)
+                decoder.prefill(prompts[0][:64], sequence=0)                       # warm-up: first launches set kernel attributes
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ctx.stream)
+                for m in range(members):
+                    decoder.prefill(prompts[m], sequence=m)
+                b.record(ctx.stream)
+                ctx.synchronize()
+                prefill_ms = a.elapsed_time(b)
+                prefill = {"tokens_per_s": members * context_tokens / (prefill_ms * 1e-3), "ms": prefill_ms, "chunk": 512,
+                           "prompt_tokens": members * context_tokens}
+                decoder.capture(advance=True)            # its eager step writes slot `context_tokens` again and advances nothing
+            else:
+                decoder.fill_context(context_tokens)
+                decoder.capture(advance=True)
+                decoder.fill_context(context_tokens)   # the eager step inside capture() advanced nothing but wrote one cache slot
             for _ in range(3):
                 decoder.replay()
             if world > 1:
@@ -271,8 +291,11 @@ def decode_leg(args, ctx, device, rank, world, peak):
                 "weight_bytes_per_step_per_gpu": weight_bytes, "kv_bytes_per_step_per_gpu": kv_bytes,
                 "hbm_GBps_per_gpu": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9,
                 "hbm_frac_of_peak": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / peak,
-                "data": "random-init weights (Q4_K_M mix), random KV context, greedy decoding", "n_gpus": world,
+                "data": "random-init weights (Q4_K_M mix), " + ("context prefilled from random prompt tokens" if prefill else "random KV context")
+                        + ", greedy decoding", "n_gpus": world,
             }
+            if prefill:
+                results[name]["prefill"] = prefill
             del decoder
             torch.cuda.empty_cache()
         if world == 1:

@@ -9,6 +9,8 @@ from .quantized import (
     CudaQ5KGemv,
     CudaQ6KGemv,
     CudaQ8_0Gemv,
+    CudaQ8_1Gemv,
+    CudaQ8_1Quantizer,
     CudaQuantizedKernelError,
     CudaQuantizedWeight,
     CudaQwen35Ops,
@@ -24,7 +26,7 @@ from .quantized import (
 )
 
 __all__ = [
-    "CudaQ4KGemv", "CudaQ5KGemv", "CudaQ6KGemv", "CudaQ8_0Gemv", "CudaQuantizedKernelError",
+    "CudaQ4KGemv", "CudaQ5KGemv", "CudaQ6KGemv", "CudaQ8_0Gemv", "CudaQ8_1Gemv", "CudaQ8_1Quantizer", "CudaQuantizedKernelError",
     "CudaQuantizedWeight", "CudaQwen35Ops", "CudaWeightStore", "QwenGemvKernel", "RibnContext",
     "WeightTensorSpec", "dequantize", "gemm", "tensor_layout", "validate_geometry_raw",
     "validate_quantized_geometry",

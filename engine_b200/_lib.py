@@ -57,6 +57,20 @@ class Attention(ctypes.Structure):
         ("v_cache", ctypes.c_void_p),
         ("max_context", ctypes.c_uint64),
         ("active_context", ctypes.c_uint64),
+        ("shared_cache", ctypes.c_uint32),
+        ("out_dtype", ctypes.c_uint32),
+    ]
+
+
+class GgufTensor(ctypes.Structure):
+    """struct ribn_gguf_tensor"""
+
+    _fields_ = [
+        ("name", ctypes.c_char_p),
+        ("value_type", ctypes.c_uint32),
+        ("n_dims", ctypes.c_uint32),
+        ("dims", ctypes.c_uint64 * 16),
+        ("offset", ctypes.c_uint64),
     ]
 
 
@@ -74,6 +88,8 @@ class GemvJob(ctypes.Structure):
 
 
 RIBN_FUSED_SWIGLU = 1
+RIBN_SHARD_NONE, RIBN_SHARD_ROWS, RIBN_SHARD_INPUT = 0, 1, 2
+RIBN_GGUF_SCALAR = 2 ** 64 - 1
 
 _u64p = ctypes.POINTER(ctypes.c_uint64)
 _vp = ctypes.c_void_p
@@ -112,9 +128,33 @@ SIGNATURES = {
     "ribn_embedding": (ctypes.c_int, [_vp, _qwp, _vp, ctypes.c_uint32, _vp, ctypes.c_uint64]),
     "ribn_qk_norm_rope_append": (ctypes.c_int, [_vp, _attp, _vp, _vp, _vp]),
     "ribn_attention_decode": (ctypes.c_int, [_vp, _attp, _vp, _vp]),
+    "ribn_quantize_q8_1": (ctypes.c_int, [_vp, _vp, ctypes.c_uint64, _vp, ctypes.c_uint64]),
+    "ribn_gemv_q8_1": (ctypes.c_int, [_vp, ctypes.c_uint32, ctypes.POINTER(QWeight), _vp, ctypes.c_uint64, _vp, ctypes.c_uint64, ctypes.c_uint32]),
     "ribn_silu_mul": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64]),
+    "ribn_silu_mul_typed": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64]),
     "ribn_residual_add": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_uint64]),
     "ribn_argmax": (ctypes.c_int, [_vp, _vp, ctypes.c_uint32, ctypes.c_uint64, _vp]),
+    "ribn_context_stream": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(_vp)]),
+    "ribn_gguf_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "ribn_gguf_close": (None, [_vp]),
+    "ribn_gguf_last_error": (ctypes.c_char_p, [_vp]),
+    "ribn_gguf_version": (ctypes.c_uint32, [_vp]),
+    "ribn_gguf_tensor_count": (ctypes.c_uint64, [_vp]),
+    "ribn_gguf_metadata_count": (ctypes.c_uint64, [_vp]),
+    "ribn_gguf_tensor_data_offset": (ctypes.c_uint64, [_vp]),
+    "ribn_gguf_metadata_key": (ctypes.c_char_p, [_vp, ctypes.c_uint64]),
+    "ribn_gguf_metadata_type": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32), _u64p]),
+    "ribn_gguf_metadata_u64": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, _u64p]),
+    "ribn_gguf_metadata_i64": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int64)]),
+    "ribn_gguf_metadata_f64": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_double)]),
+    "ribn_gguf_metadata_bool": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int)]),
+    "ribn_gguf_metadata_string": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(_vp), _u64p]),
+    "ribn_gguf_tensor_info": (ctypes.c_int, [_vp, ctypes.c_uint64, ctypes.POINTER(GgufTensor)]),
+    "ribn_gguf_find_tensor": (ctypes.c_int, [_vp, ctypes.c_char_p, _u64p]),
+    "ribn_gguf_tensor_data_range": (ctypes.c_int, [_vp, ctypes.c_char_p, _u64p, _u64p]),
+    "ribn_gguf_read_tensor": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_uint64, _vp, ctypes.c_uint64, _u64p]),
+    "ribn_gguf_shard_bytes": (ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64, _u64p, _u64p, _u64p]),
+    "ribn_materialize_quantized": (ctypes.c_int, [_vp, _vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64, _vp, ctypes.c_uint64]),
     "ribn_rms_norm": (ctypes.c_int, [_vp, _vp, ctypes.c_int, ctypes.c_uint64, _vp, ctypes.c_uint64, _vp, ctypes.c_int,
                                      ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float]),
 }

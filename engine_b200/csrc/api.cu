@@ -596,6 +596,9 @@ Failure validate_attention(const ribn_attention* a) {
     if (a->max_context == 0 || a->active_context == 0 || a->active_context > a->max_context)
         return fail(RIBN_E_INVALID_ARGUMENT, "the active context must be 1..max_context");
     if (a->max_context > (1ull << 31)) return fail(RIBN_E_SHAPE_OVERFLOW, "context does not fit CUDA launch arguments");
+    if (a->shared_cache > 1) return fail(RIBN_E_INVALID_ARGUMENT, "shared_cache is 0 or 1");
+    if (a->members > 65535) return fail(RIBN_E_SHAPE_OVERFLOW, "at most 65535 members per attention call");
+    if (!valid_dtype(static_cast<int>(a->out_dtype))) return fail(RIBN_E_INVALID_ARGUMENT, "unknown attention output dtype");
     return Failure{};
 }
 
@@ -618,6 +621,7 @@ ribn::LayerAttentionArgs attention_args(const ribn_ctx* ctx, const ribn_attentio
     r.v_cache = a->v_cache;
     r.max_context = static_cast<long long>(a->max_context);
     r.active_context = static_cast<long long>(a->active_context);
+    r.shared_cache = a->shared_cache == 1;
     r.device_status = ctx->device_status;
     r.stream = ctx->stream;
     return r;
@@ -673,6 +677,13 @@ void ribn_destroy(ribn_ctx* ctx) {
     if (ctx->tickets != nullptr) cudaFree(ctx->tickets);
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
     delete ctx;
+}
+
+int ribn_context_stream(const ribn_ctx* ctx, int* device, void** cuda_stream) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (device != nullptr) *device = ctx->device;
+    if (cuda_stream != nullptr) *cuda_stream = ctx->stream;
+    return RIBN_OK;
 }
 
 int ribn_synchronize(ribn_ctx* ctx) {
@@ -1002,6 +1013,63 @@ int ribn_rms_norm(ribn_ctx* ctx, const void* x_device, int x_dtype, uint64_t x_l
     return RIBN_OK;
 }
 
+// ---------------------------------------------------------------- the reference's Q8_1 activation format
+
+int ribn_quantize_q8_1(ribn_ctx* ctx, const float* x_device, uint64_t x_len, uint32_t* packed_device, uint64_t packed_len) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    // CudaQ8_1Quantizer::execute (activation.rs:43-69): empty and partial blocks, then the output size, then the
+    // 32-bit indexing limit of the device side.
+    if (x_len == 0 || x_len % 32 != 0) {
+        const uint64_t expected = ((x_len == 0 ? 1 : x_len) + 31) / 32 * 32;
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH, fmt("Q8_1 input has %" PRIu64 " values, expected %" PRIu64, x_len, expected), expected, x_len));
+    }
+    const uint64_t blocks = x_len / 32;
+    if (packed_len != blocks * 9)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH, fmt("Q8_1 output has %" PRIu64 " words, expected %" PRIu64, packed_len, blocks * 9),
+                                blocks * 9, packed_len));
+    if (x_len > std::numeric_limits<uint32_t>::max()) return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "Q8_1 input does not fit 32-bit indexing"));
+    DeviceGuard guard(ctx->device);
+    Failure f = check_device_pointer(ctx, x_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, packed_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const cudaError_t e = ribn::launch_quantize_q8_1(x_device, packed_device, blocks, ctx->sm_count, ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "Q8_1 packer launch");
+    return RIBN_OK;
+}
+
+int ribn_gemv_q8_1(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const uint32_t* packed_device, uint64_t packed_len,
+                   float* y_device, uint64_t y_len, uint32_t members) {
+    if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    // CudaQ4KQ8_1Gemv::execute_batch and its twins: members == 0 is an input-length error, more than eight an
+    // invalid-weight error, both before geometry (tests/q4_q8_1.rs:412-445).
+    if (members == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "quantized GEMV input has 0 values, expected 1", 1, 0));
+    if (members > 8) return record(ctx, fail(RIBN_E_INVALID_WEIGHT, "invalid quantized weight: batch variant supports at most 8 members"));
+    uint64_t k = 0, n = 0;
+    Failure f = validate_geometry(weight, expected_type, &k, &n);
+    if (f.status != RIBN_OK) return record(ctx, f);
+    const uint64_t expected_in = k / 32 * 9 * members, expected_out = n * members;
+    if (packed_len != expected_in)
+        return record(ctx, fail(RIBN_E_INPUT_LENGTH, fmt("packed GEMV input has %" PRIu64 " words, expected %" PRIu64, packed_len, expected_in),
+                                expected_in, packed_len));
+    if (y_len != expected_out)
+        return record(ctx, fail(RIBN_E_OUTPUT_LENGTH, fmt("quantized GEMV output has %" PRIu64 " values, expected %" PRIu64, y_len, expected_out),
+                                expected_out, y_len));
+    if (k > static_cast<uint64_t>(std::numeric_limits<int32_t>::max()) || n > static_cast<uint64_t>(std::numeric_limits<int32_t>::max()) / 8)
+        return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "quantized GEMV shape does not fit CUDA launch arguments"));
+    DeviceGuard guard(ctx->device);
+    f = check_device_pointer(ctx, weight->data, "weight");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, packed_device, "input");
+    if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
+    if (f.status != RIBN_OK) return record(ctx, f);
+    if ((reinterpret_cast<uintptr_t>(weight->data) & 15u) != 0)
+        return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "weight data must be 16-byte aligned"));
+    const cudaError_t e = ribn::launch_gemv_q8_1(weight->value_type, static_cast<const uint8_t*>(weight->data), packed_device, y_device,
+                                                 static_cast<int>(k), static_cast<int>(n), static_cast<int>(members), weight->encoded_bytes / n,
+                                                 ctx->stream);
+    if (e != cudaSuccess) return record_cuda(ctx, e, "packed GEMV launch");
+    return RIBN_OK;
+}
+
 // ---------------------------------------------------------------- decoder-layer operators between the GEMVs
 
 int ribn_embedding(ribn_ctx* ctx, const ribn_qweight* weight, const uint32_t* tokens_device, uint32_t members, float* out_device,
@@ -1049,7 +1117,7 @@ int ribn_qk_norm_rope_append(ribn_ctx* ctx, const ribn_attention* attention, flo
     return RIBN_OK;
 }
 
-int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, float* out_device) {
+int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, void* out_device) {
     if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
     Failure f = validate_attention(attention);
     if (f.status != RIBN_OK) return record(ctx, f);
@@ -1065,14 +1133,20 @@ int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const 
     while (splits > 1 && ribn::attention_scratch_bytes(args.members, args.q_heads, splits) > ctx->workspace_bytes) --splits;
     if (ribn::attention_scratch_bytes(args.members, args.q_heads, splits) > ctx->workspace_bytes)
         return record(ctx, fail(RIBN_E_SHAPE_OVERFLOW, "attention partial results do not fit the context workspace"));
-    const cudaError_t e = ribn::launch_attention_decode(args, out_device, ctx->workspace, splits);
+    const cudaError_t e = ribn::launch_attention_decode(args, out_device, attention->out_dtype == RIBN_BF16, ctx->workspace, splits);
     if (e != cudaSuccess) return record_cuda(ctx, e, "attention launch");
     return RIBN_OK;
 }
 
 int ribn_silu_mul(ribn_ctx* ctx, const float* gate_device, const float* up_device, float* out_device, uint32_t members,
                   uint64_t length, uint64_t input_row_stride) {
+    return ribn_silu_mul_typed(ctx, gate_device, up_device, out_device, RIBN_F32, members, length, input_row_stride);
+}
+
+int ribn_silu_mul_typed(ribn_ctx* ctx, const float* gate_device, const float* up_device, void* out_device, int out_dtype, uint32_t members,
+                        uint64_t length, uint64_t input_row_stride) {
     if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
+    if (!valid_dtype(out_dtype)) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "unknown output dtype"));
     if (members == 0 || length == 0) return record(ctx, fail(RIBN_E_INPUT_LENGTH, "silu_mul needs at least one value", 1, 0));
     if (input_row_stride < length) return record(ctx, fail(RIBN_E_INVALID_ARGUMENT, "input rows overlap"));
     DeviceGuard guard(ctx->device);
@@ -1080,7 +1154,7 @@ int ribn_silu_mul(ribn_ctx* ctx, const float* gate_device, const float* up_devic
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, up_device, "up");
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, out_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
-    const cudaError_t e = ribn::launch_silu_mul(gate_device, up_device, out_device, members, length, input_row_stride, ctx->sm_count, ctx->stream);
+    const cudaError_t e = ribn::launch_silu_mul(gate_device, up_device, out_device, out_dtype == RIBN_BF16, members, length, input_row_stride, ctx->sm_count, ctx->stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "silu_mul launch");
     return RIBN_OK;
 }

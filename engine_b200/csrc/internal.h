@@ -187,6 +187,11 @@ cudaError_t launch_qgemv_tc(const TcArgs& args);
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);
 
+// The reference's Q8_1 activation format and the integer-dot GEMV over it (q8_1.cu).
+cudaError_t launch_quantize_q8_1(const float* input, uint32_t* output, uint64_t blocks, int sm_count, cudaStream_t stream);
+cudaError_t launch_gemv_q8_1(uint32_t value_type, const uint8_t* weights, const uint32_t* packed, float* output, int k, int n, int members,
+                             uint64_t row_bytes, cudaStream_t stream);
+
 // Decoder-layer operators between the GEMVs (layer_ops.cu).  KV cache: [member][kv_head][max_context][head_dim] f16.
 struct LayerAttentionArgs {
     float* q;                 // [members][q_heads * head_dim], rewritten in place by the norm/rope step
@@ -203,6 +208,7 @@ struct LayerAttentionArgs {
     void* v_cache;
     long long max_context;    // tokens the cache holds per (member, head)
     long long active_context; // upper bound on positions + 1 in this call (plans the KV splits)
+    bool shared_cache;        // the members are consecutive tokens of ONE sequence (a prefill chunk): all use cache slot 0
     int* device_status;       // status word of the context: kernels report positions outside the cache here
     cudaStream_t stream;
 };
@@ -211,8 +217,8 @@ cudaError_t launch_embedding(const uint8_t* weights, uint32_t value_type, int k,
 cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& args);
 int attention_splits(int members, int kv_heads, long long active_context, int sm_count);
 size_t attention_scratch_bytes(int members, int q_heads, int splits);
-cudaError_t launch_attention_decode(const LayerAttentionArgs& args, float* out, void* scratch, int splits);
-cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t members, uint64_t length, uint64_t in_stride,
+cudaError_t launch_attention_decode(const LayerAttentionArgs& args, void* out, bool out_bf16, void* scratch, int splits);
+cudaError_t launch_silu_mul(const float* gate, const float* up, void* out, bool out_bf16, uint64_t members, uint64_t length, uint64_t in_stride,
                             int sm_count, cudaStream_t stream);
 cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream);
 cudaError_t launch_argmax(const float* logits, int members, uint64_t length, uint32_t* out, cudaStream_t stream);

@@ -21,6 +21,7 @@
 //
 // Positions are read from device memory (one int per member), so that a captured CUDA graph can be
 // replayed for every decode step.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "formats.cuh"
@@ -64,7 +65,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
                                                                   const float* __restrict__ k_norm, float eps,
                                                                   const int* __restrict__ positions, int q_heads, int kv_heads,
                                                                   int head_dim, int rot_pairs, float base, __half* __restrict__ k_cache,
-                                                                  __half* __restrict__ v_cache, long long max_context, int* __restrict__ status) {
+                                                                  __half* __restrict__ v_cache, long long max_context, int shared_cache,
+                                                                  int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     __shared__ float values[256];
@@ -121,7 +123,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
     if (in_place != nullptr) {
         in_place[t] = x;
     } else if (position >= 0 && position < max_context) {
-        cache[((static_cast<long long>(member) * kv_heads + head) * max_context + position) * head_dim + t] = __float2half_rn(x);
+        // a prefill chunk: the members are consecutive tokens of one sequence and append to the same cache
+        const long long sequence = shared_cache ? 0 : member;
+        cache[((sequence * kv_heads + head) * max_context + position) * head_dim + t] = __float2half_rn(x);
     } else if (t == 0) {
         // The position comes from device memory (a replayed graph advances it): outside the cache nothing is
         // stored and the context's status word says so.
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
                                                                              long long max_context, int chunk, float scale, int active_context,
-                                                                             int* __restrict__ status) {
+                                                                             int shared_cache, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     // Two tiles of each: the next one streams in (cp.async) while the warps work on the current one.
@@ -171,8 +175,9 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     for (int i = threadIdx.x; i < group * kAttnHeadDim; i += blockDim.x)
         q_rows[i] = q[(static_cast<size_t>(member) * q_heads + kv_head * group) * kAttnHeadDim + i];
 
-    const __half* k_base = k_cache + (static_cast<long long>(member) * kv_heads + kv_head) * max_context * kAttnHeadDim;
-    const __half* v_base = v_cache + (static_cast<long long>(member) * kv_heads + kv_head) * max_context * kAttnHeadDim;
+    const long long sequence = shared_cache ? 0 : member;
+    const __half* k_base = k_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
+    const __half* v_base = v_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
     float running_max = -INFINITY, running_sum = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
@@ -272,8 +277,9 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
 }
 
 // grid (q_heads, members), 128 threads: merges the splits of one query head.
+template <bool OUT_BF16>
 __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                                         float* __restrict__ out, int q_heads, int splits) {
+                                                                         void* __restrict__ out, int q_heads, int splits) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
     const size_t base = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * splits;
@@ -286,13 +292,16 @@ __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const f
         total = fmaf(part_ml[(base + s) * 2 + 1], weight, total);
         value = fmaf(part_o[(base + s) * kAttnHeadDim + threadIdx.x], weight, value);
     }
-    out[(static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * kAttnHeadDim + threadIdx.x] = value / total;
+    const size_t index = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * kAttnHeadDim + threadIdx.x;
+    if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value / total);
+    else static_cast<float*>(out)[index] = value / total;
 }
 
 // ---------------------------------------------------------------- elementwise
 // out[m][i] = silu(gate[m][i]) * up[m][i]; gate and up rows are `in_stride` floats apart (they may be the two
 // halves of one [members][2 * length] GEMV output), out rows are `length` apart.
-__global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out,
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, void* __restrict__ out,
                                                        unsigned long long length, unsigned long long in_stride, unsigned long long total) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
@@ -301,7 +310,9 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
         const unsigned long long member = i / length;
         const unsigned long long column = i - member * length;
         const float value = gate[member * in_stride + column];
-        out[i] = (value / (1.0f + expf(-value))) * up[member * in_stride + column];
+        const float product = (value / (1.0f + expf(-value))) * up[member * in_stride + column];
+        if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(product);
+        else static_cast<float*>(out)[i] = product;
     }
 }
 
@@ -387,7 +398,7 @@ cudaError_t launch_qk_norm_rope_append(const LayerAttentionArgs& a) {
     const dim3 grid(a.q_heads + 2 * a.kv_heads, a.members);
     return launch_kernel_if(pdl_switch() == 1, qk_norm_rope_append_kernel, grid, dim3(a.head_dim), 0, a.stream, a.q, a.k, a.v, a.q_norm, a.k_norm, a.eps, a.positions,
                          a.q_heads, a.kv_heads, a.head_dim, a.rot_dims / 2, a.rope_base, static_cast<__half*>(a.k_cache),
-                         static_cast<__half*>(a.v_cache), a.max_context, a.device_status);
+                         static_cast<__half*>(a.v_cache), a.max_context, a.shared_cache ? 1 : 0, a.device_status);
 }
 
 int attention_splits(int members, int kv_heads, long long active_context, int sm_count) {
@@ -405,7 +416,7 @@ size_t attention_scratch_bytes(int members, int q_heads, int splits) {
     return static_cast<size_t>(members) * q_heads * splits * (kAttnHeadDim + 2) * sizeof(float);
 }
 
-cudaError_t launch_attention_decode(const LayerAttentionArgs& a, float* out, void* scratch, int splits) {
+cudaError_t launch_attention_decode(const LayerAttentionArgs& a, void* out, bool out_bf16, void* scratch, int splits) {
     if (a.head_dim != kAttnHeadDim || a.q_heads % a.kv_heads != 0 || a.q_heads / a.kv_heads > kAttnMaxGroup) return cudaErrorInvalidValue;
     const int group = a.q_heads / a.kv_heads;
     long long chunk = (a.active_context + splits - 1) / splits;
@@ -416,19 +427,26 @@ cudaError_t launch_attention_decode(const LayerAttentionArgs& a, float* out, voi
     cudaError_t e = launch_kernel_if(pdl_switch() == 1, attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
                                   static_cast<const float*>(a.q), static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache),
                                   a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale,
-                                  static_cast<int>(a.active_context), a.device_status);
+                                  static_cast<int>(a.active_context), a.shared_cache ? 1 : 0, a.device_status);
     if (e != cudaSuccess) return e;
-    return launch_kernel_if(pdl_switch() == 1, attention_combine_kernel, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
-                         static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);
+    if (out_bf16)
+        return launch_kernel_if(pdl_switch() == 1, attention_combine_kernel<true>, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
+                                static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);
+    return launch_kernel_if(pdl_switch() == 1, attention_combine_kernel<false>, dim3(a.q_heads, a.members), dim3(kAttnHeadDim), 0, a.stream,
+                            static_cast<const float*>(part_o), static_cast<const float*>(part_ml), out, a.q_heads, splits);
 }
 
-cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t members, uint64_t length, uint64_t in_stride,
+cudaError_t launch_silu_mul(const float* gate, const float* up, void* out, bool out_bf16, uint64_t members, uint64_t length, uint64_t in_stride,
                             int sm_count, cudaStream_t stream) {
     const unsigned long long total = members * length;
     unsigned long long blocks = (total + 255) / 256;
     if (blocks > static_cast<unsigned long long>(sm_count) * 8) blocks = static_cast<unsigned long long>(sm_count) * 8;
-    return launch_kernel_if(pdl_switch() == 1, silu_mul_kernel, dim3(static_cast<unsigned>(blocks ? blocks : 1)), dim3(256), 0, stream, gate, up, out,
-                         static_cast<unsigned long long>(length), static_cast<unsigned long long>(in_stride), total);
+    const dim3 grid(static_cast<unsigned>(blocks ? blocks : 1));
+    if (out_bf16)
+        return launch_kernel_if(pdl_switch() == 1, silu_mul_kernel<true>, grid, dim3(256), 0, stream, gate, up, out,
+                                static_cast<unsigned long long>(length), static_cast<unsigned long long>(in_stride), total);
+    return launch_kernel_if(pdl_switch() == 1, silu_mul_kernel<false>, grid, dim3(256), 0, stream, gate, up, out,
+                            static_cast<unsigned long long>(length), static_cast<unsigned long long>(in_stride), total);
 }
 
 cudaError_t launch_residual_add(float* y, const float* x, uint64_t total, int sm_count, cudaStream_t stream) {

@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib, synth
-from .quantized import CudaQuantizedWeight, QwenGemvKernel, RibnContext, WeightTensorSpec
+from .quantized import CudaQuantizedWeight, CudaQwen35Ops, QwenGemvKernel, RibnContext, WeightTensorSpec, gemm
 from .sharding import split_even
 
 Q4_K, Q6_K = 12, 14
@@ -74,8 +74,9 @@ class CudaDenseOps:
         self.context.check(self._lib.ribn_attention_decode(self.context.handle, ctypes.byref(attention), q.data_ptr(), output.data_ptr()))
 
     def silu_mul(self, gate: torch.Tensor, up: torch.Tensor, output: torch.Tensor, members: int, length: int, input_row_stride: int) -> None:
-        self.context.check(self._lib.ribn_silu_mul(self.context.handle, gate.data_ptr(), up.data_ptr(), output.data_ptr(), members, length,
-                                                   input_row_stride))
+        dtype = _lib.RIBN_F32 if output.dtype == torch.float32 else _lib.RIBN_BF16
+        self.context.check(self._lib.ribn_silu_mul_typed(self.context.handle, gate.data_ptr(), up.data_ptr(), output.data_ptr(), dtype, members,
+                                                         length, input_row_stride))
 
     def residual_add(self, accumulator: torch.Tensor, addend: torch.Tensor) -> None:
         self.context.check(self._lib.ribn_residual_add(self.context.handle, accumulator.data_ptr(), addend.data_ptr(), accumulator.numel()))
@@ -214,6 +215,7 @@ class CudaDenseDecode:
         self.k_cache = torch.zeros(cache_shape, dtype=torch.float16, device=dev)
         self.v_cache = torch.zeros(cache_shape, dtype=torch.float16, device=dev)
         self.active_context = max_context
+        self.prefill_scratch: dict | None = None
         self.graph = None
         self.launches_per_step = 0
         if members > 4:
@@ -278,18 +280,106 @@ class CudaDenseDecode:
             self.ops.argmax(self.logits, self.members, self.next_tokens)
             self.launches_per_step += 1
 
-    def _select_tokens_tensor_parallel(self) -> None:
+    def _select_tokens_tensor_parallel(self, logits: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
         """Each rank holds a slice of the logits: local argmax, then the best (value, index) over the ranks."""
-        local = torch.empty(self.members, dtype=torch.int32, device=self.context.device)
-        self.ops.argmax(self.logits, self.members, local)
-        values = self.logits.gather(1, local.long().unsqueeze(1)).squeeze(1)
+        logits = self.logits if logits is None else logits
+        out = self.next_tokens if out is None else out
+        rows = logits.shape[0]
+        local = torch.empty(rows, dtype=torch.int32, device=self.context.device)
+        self.ops.argmax(logits, rows, local)
+        values = logits.gather(1, local.long().unsqueeze(1)).squeeze(1)
         gathered_values = [torch.empty_like(values) for _ in range(self.world)]
         gathered_indices = [torch.empty_like(local) for _ in range(self.world)]
         torch.distributed.all_gather(gathered_values, values, group=self.group)
         torch.distributed.all_gather(gathered_indices, local + self.shapes["vocab_begin"], group=self.group)
         all_values = torch.stack(gathered_values)            # [world][members]
         best = all_values.argmax(dim=0)                        # first rank wins ties: the lowest index
-        self.next_tokens.copy_(torch.stack(gathered_indices).gather(0, best.unsqueeze(0)).squeeze(0))
+        out.copy_(torch.stack(gathered_indices).gather(0, best.unsqueeze(0)).squeeze(0))
+
+    # -- prefill ------------------------------------------------------------------------------------
+    def _prefill_buffers(self, chunk: int) -> dict:
+        if self.prefill_scratch is not None and self.prefill_scratch["chunk"] >= chunk:
+            return self.prefill_scratch
+        g, s, dev = self.geometry, self.shapes, self.context.device
+        f32, bf16 = dict(dtype=torch.float32, device=dev), dict(dtype=torch.bfloat16, device=dev)
+        q_dim, kv_dim = s["q_heads"] * g.head_dim, s["kv_heads"] * g.head_dim
+        self.prefill_scratch = {
+            "chunk": chunk, "tokens": torch.zeros(chunk, dtype=torch.int32, device=dev), "positions": torch.zeros(chunk, dtype=torch.int32, device=dev),
+            "hidden": torch.zeros(chunk, g.hidden, **f32), "normed": torch.zeros(chunk, g.hidden, **bf16),
+            "q": torch.zeros(chunk, q_dim, **f32), "k": torch.zeros(chunk, kv_dim, **f32), "v": torch.zeros(chunk, kv_dim, **f32),
+            "attended": torch.zeros(chunk, q_dim, **bf16), "projected": torch.zeros(chunk, g.hidden, **f32),
+            "gate_up": torch.zeros(chunk, 2 * s["intermediate"], **f32), "activated": torch.zeros(chunk, s["intermediate"], **bf16),
+        }
+        return self.prefill_scratch
+
+    def _prefill_chunk(self, tokens: torch.Tensor, sequence: int, start: int) -> torch.Tensor:
+        """One chunk of consecutive prompt tokens of one sequence through every layer (run_prefill_chunk,
+        decode.rs:2149-2267; attention per token over the shared cache, :2945-3021).  The projections are
+        ribn_gemm over the whole chunk instead of eight-row GEMVs.  Returns the chunk's hidden rows."""
+        g, s, w, ctx = self.geometry, self.shapes, self.weights, self.context
+        count = tokens.numel()
+        b = self._prefill_buffers(count)
+        rows = lambda name: b[name][:count]                                        # leading rows: contiguous
+        norms = CudaQwen35Ops(ctx)
+        parallel = self.group is not None and self.world > 1
+        b["tokens"][:count].copy_(tokens)
+        torch.arange(start, start + count, dtype=torch.int32, device=ctx.device, out=b["positions"][:count])
+        hidden, normed, projected, gate_up = rows("hidden"), rows("normed"), rows("projected"), rows("gate_up")
+        self.ops.embedding(w.matrices["token_embd"], b["tokens"][:count], hidden)
+        for i in range(g.layers):
+            norms.rms_norm_batch(hidden, w.vectors[f"blk.{i}.attn_norm"], normed, g.hidden, g.eps)
+            for name, out in (("attn_q", rows("q")), ("attn_k", rows("k")), ("attn_v", rows("v"))):
+                gemm(ctx, w.matrices[f"blk.{i}.{name}"], normed, out)
+            attention = attention_descriptor(g, count, s["q_heads"], s["kv_heads"], w.vectors[f"blk.{i}.attn_q_norm"],
+                                             w.vectors[f"blk.{i}.attn_k_norm"], b["positions"], self.k_cache[i][sequence],
+                                             self.v_cache[i][sequence], self.max_context, start + count)
+            attention.shared_cache, attention.out_dtype = 1, _lib.RIBN_BF16
+            self.ops.qk_norm_rope_append(attention, rows("q"), rows("k"), rows("v"))
+            self.ops.attention_decode(attention, rows("q"), rows("attended"))
+            gemm(ctx, w.matrices[f"blk.{i}.attn_output"], rows("attended"), projected)
+            if parallel:
+                torch.distributed.all_reduce(projected, group=self.group)
+            self.ops.residual_add(hidden, projected)
+            norms.rms_norm_batch(hidden, w.vectors[f"blk.{i}.ffn_norm"], normed, g.hidden, g.eps)
+            gemm(ctx, w.matrices[f"blk.{i}.ffn_gate_up"], normed, gate_up)
+            inter = s["intermediate"]
+            self.ops.silu_mul(gate_up[:, :inter], gate_up[:, inter:], rows("activated"), count, inter, 2 * inter)
+            gemm(ctx, w.matrices[f"blk.{i}.ffn_down"], rows("activated"), projected)
+            if parallel:
+                torch.distributed.all_reduce(projected, group=self.group)
+            self.ops.residual_add(hidden, projected)
+        return hidden
+
+    def prefill(self, tokens, sequence: int = 0, start: int = 0, chunk: int = 512) -> None:
+        """Fill the KV cache of `sequence` from prompt `tokens` at positions start.. (run_prefill_chunks,
+        crates/nvidia/src/serving.rs:136 over decode.rs:1953-1977), `chunk` tokens per pass.  Afterwards the
+        sequence is ready for run_step: positions[sequence] is the first free slot and tokens[sequence] the
+        token chosen from the last prompt token's logits (also left in next_tokens[sequence])."""
+        tokens = torch.as_tensor(tokens, dtype=torch.int32).to(self.context.device)
+        if tokens.numel() == 0:
+            raise ValueError("a prompt needs at least one token")
+        if start + tokens.numel() > self.max_context:
+            raise ValueError(f"prompt end {start + tokens.numel()} exceeds the cache of {self.max_context} tokens")
+        with torch.cuda.stream(self.context.stream):
+            for begin in range(0, tokens.numel(), chunk):
+                part = tokens[begin:begin + chunk]
+                hidden = self._prefill_chunk(part, sequence, start + begin)
+            last = hidden[part.numel() - 1:part.numel()]
+            logits = self.logits[sequence:sequence + 1]
+            if logits.data_ptr() % 16:                                # a row of an odd vocabulary: go through an aligned row
+                logits = torch.empty_like(logits)
+            gemv_fused(self.context, [(self.weights.matrices["output"], logits, False)], last, 1, self.weights.vectors["output_norm"],
+                       self.geometry.eps)
+            chosen = self._prefill_buffers(1)["tokens"][:1]          # an aligned word of its own: entry points want 16-byte alignment
+            if self.world > 1:
+                self._select_tokens_tensor_parallel(logits, chosen)
+            else:
+                self.ops.argmax(logits, 1, chosen)
+            if logits.data_ptr() != self.logits[sequence:sequence + 1].data_ptr():
+                self.logits[sequence:sequence + 1].copy_(logits)
+            self.next_tokens[sequence:sequence + 1].copy_(chosen)
+            self.tokens[sequence:sequence + 1].copy_(chosen)
+            self.positions[sequence:sequence + 1].fill_(start + tokens.numel())
 
     # -- public ------------------------------------------------------------------------------------
     def run_step(self) -> None:

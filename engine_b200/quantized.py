@@ -326,6 +326,39 @@ class CudaQwen35Ops:
                                          output.numel(), members, length, ctypes.c_float(epsilon)))
 
 
+class CudaQ8_1Quantizer:
+    """CudaQ8_1Quantizer (crates/nvidia/src/activation.rs:15-88): f32 values -> the reference's Q8_1 words, nine per
+    block of 32, bit-identical to its quantize_q8_1 kernel."""
+
+    def __init__(self, context: RibnContext):
+        self.context = context
+
+    def execute(self, input: torch.Tensor, output: torch.Tensor) -> None:
+        if input.dtype != torch.float32 or output.dtype not in (torch.int32, torch.uint32):
+            raise TypeError("the Q8_1 packer takes float32 values and writes 32-bit words")
+        ctx = self.context
+        ctx.check(ctx._lib.ribn_quantize_q8_1(ctx.handle, input.data_ptr(), input.numel(), output.data_ptr(), output.numel()))
+
+
+class CudaQ8_1Gemv:
+    """The integer-dot GEMV family over Q8_1 activations: CudaQ4KQ8_1Gemv (crates/nvidia/src/q4_q8_1.rs) and its
+    Q5_K / Q6_K / Q8_0 twins, `execute` for one packed vector and `execute_batch` for up to eight."""
+
+    def __init__(self, context: RibnContext, value_type: int):
+        self.context, self.value_type = context, value_type
+
+    def execute(self, weight: CudaQuantizedWeight, packed: torch.Tensor, output: torch.Tensor) -> None:
+        self.execute_batch(weight, packed, output, 1)
+
+    def execute_batch(self, weight: CudaQuantizedWeight, packed: torch.Tensor, output: torch.Tensor, members: int) -> None:
+        if output.dtype != torch.float32:
+            raise TypeError("the integer-dot GEMV writes float32")
+        ctx = self.context
+        descriptor = weight.descriptor()
+        ctx.check(ctx._lib.ribn_gemv_q8_1(ctx.handle, self.value_type, ctypes.byref(descriptor), packed.data_ptr(), packed.numel(),
+                                          output.data_ptr(), output.numel(), members))
+
+
 def gemm(context: RibnContext, weight: CudaQuantizedWeight, input: torch.Tensor, output: torch.Tensor,
          expected_type: int = 0) -> None:
     """Prefill GEMM on the tensor cores: input bf16 [tokens, K] -> output bf16/f32 [tokens, N] (ribn_gemm)."""

@@ -259,6 +259,110 @@ int ribn_gemv_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count
                     uint64_t x_len, const float* norm_weight_device, uint64_t norm_weight_len, float eps, uint32_t members,
                     uint32_t flags);
 
+/* ---- GGUF v3 files: directory reader and staged upload ------------------------------------------
+ * GgufFile::open / read_from, tensor_data_range, TensorDataReader (crates/gguf/src/lib.rs:191-280, :324-343,
+ * :400-505) and CudaWeightStore::materialize_quantized (crates/nvidia/src/cuda.rs:321-387).  Opening parses the
+ * header, the metadata and the tensor directory with the reference's bounds (strings <= 16 MiB, arrays <= 10^6
+ * items and 16 levels, <= 16 dimensions, <= 10^7 tensors) and never reads tensor data.  The functions return RIBN_OK,
+ * a ribn_status, or one of the codes below, which name the reference's GgufError variants. */
+typedef struct ribn_gguf ribn_gguf;
+
+typedef enum ribn_gguf_status {
+    RIBN_GGUF_E_IO = 100,
+    RIBN_GGUF_E_INVALID_MAGIC = 101,
+    RIBN_GGUF_E_UNSUPPORTED_VERSION = 102,
+    RIBN_GGUF_E_UNEXPECTED_EOF = 103,
+    RIBN_GGUF_E_INVALID_UTF8 = 104,
+    RIBN_GGUF_E_INVALID_VALUE_TYPE = 105,
+    RIBN_GGUF_E_INVALID_BOOL = 106,
+    RIBN_GGUF_E_INVALID_LENGTH = 107,
+    RIBN_GGUF_E_ARRAY_NESTING_TOO_DEEP = 108,
+    RIBN_GGUF_E_DUPLICATE_METADATA = 109,
+    RIBN_GGUF_E_INVALID_DIMENSION_COUNT = 110,
+    RIBN_GGUF_E_INVALID_ALIGNMENT = 111,
+    RIBN_GGUF_E_TRUNCATED = 112,
+    RIBN_GGUF_E_TENSOR_OFFSET_OUT_OF_BOUNDS = 113,
+    RIBN_GGUF_E_MISSING_METADATA = 114,
+    RIBN_GGUF_E_METADATA_TYPE_MISMATCH = 115,
+    RIBN_GGUF_E_MISSING_TENSOR = 116,
+    RIBN_GGUF_E_UNSUPPORTED_TENSOR_TYPE = 117,
+    RIBN_GGUF_E_ELEMENT_COUNT_OVERFLOW = 118,
+    RIBN_GGUF_E_TENSOR_BYTE_LENGTH_OVERFLOW = 119,
+    RIBN_GGUF_E_QUANTIZATION_BLOCK_MISMATCH = 120,
+    RIBN_GGUF_E_QUANTIZATION_DIMENSION_MISMATCH = 121
+} ribn_gguf_status;
+
+#define RIBN_GGUF_MAX_DIMS 16u
+#define RIBN_GGUF_SCALAR UINT64_MAX /* `index` of the metadata getters: the value itself, not an array element */
+
+typedef struct ribn_gguf_tensor {
+    const char* name;          /* owned by the file object */
+    uint32_t value_type;       /* raw GGML type id; unknown ids are kept (lib.rs:103-108) */
+    uint32_t n_dims;
+    uint64_t dims[RIBN_GGUF_MAX_DIMS];
+    uint64_t offset;           /* relative to the aligned tensor-data section */
+} ribn_gguf_tensor;
+
+int ribn_gguf_open(const char* path, ribn_gguf** out);
+void ribn_gguf_close(ribn_gguf* file);
+/* Message of the last failed call on `file`; with NULL, of the last failed ribn_gguf_open on this thread. */
+const char* ribn_gguf_last_error(const ribn_gguf* file);
+uint32_t ribn_gguf_version(const ribn_gguf* file);
+uint64_t ribn_gguf_tensor_count(const ribn_gguf* file);
+uint64_t ribn_gguf_metadata_count(const ribn_gguf* file);
+uint64_t ribn_gguf_tensor_data_offset(const ribn_gguf* file);
+const char* ribn_gguf_metadata_key(const ribn_gguf* file, uint64_t index);   /* keys in sorted order */
+/* GGUF value type (0..12) of a key; for arrays (9) also the element type and the item count. */
+int ribn_gguf_metadata_type(ribn_gguf* file, const char* key, uint32_t* type, uint32_t* element_type, uint64_t* count);
+/* Typed getters with the reference's widening rules (MetadataValue::as_u64 / as_i32 / as_str / as_bool, lib.rs:49-85):
+ * u64 takes the unsigned integer types, i64 the signed ones, f64 both float types.  `index` selects an array element,
+ * RIBN_GGUF_SCALAR the value itself.  A missing key is RIBN_GGUF_E_MISSING_METADATA, any other miss
+ * RIBN_GGUF_E_METADATA_TYPE_MISMATCH. */
+int ribn_gguf_metadata_u64(ribn_gguf* file, const char* key, uint64_t index, uint64_t* out);
+int ribn_gguf_metadata_i64(ribn_gguf* file, const char* key, uint64_t index, int64_t* out);
+int ribn_gguf_metadata_f64(ribn_gguf* file, const char* key, uint64_t index, double* out);
+int ribn_gguf_metadata_bool(ribn_gguf* file, const char* key, uint64_t index, int* out);
+int ribn_gguf_metadata_string(ribn_gguf* file, const char* key, uint64_t index, const char** data, uint64_t* length);
+int ribn_gguf_tensor_info(ribn_gguf* file, uint64_t index, ribn_gguf_tensor* out);
+int ribn_gguf_find_tensor(ribn_gguf* file, const char* name, uint64_t* index);
+/* Absolute byte range [begin, end) of a tensor's encoding; checks the block layout and the file bounds. */
+int ribn_gguf_tensor_data_range(ribn_gguf* file, const char* name, uint64_t* begin, uint64_t* end);
+/* Bounded read of a tensor's encoding from byte `offset` of it: never past the tensor's end (*read_out may be short or
+ * zero there).  The file is opened for the call and closed before it returns, so no descriptor is held between reads. */
+int ribn_gguf_read_tensor(ribn_gguf* file, const char* name, uint64_t offset, void* host_dst, uint64_t bytes, uint64_t* read_out);
+
+/* Shards of a [K, N] tensor for tensor-parallel loading (the reference has one GPU and no shards). */
+#define RIBN_SHARD_NONE 0   /* the whole tensor */
+#define RIBN_SHARD_ROWS 1   /* output rows [begin, end): one contiguous byte range */
+#define RIBN_SHARD_INPUT 2  /* super-blocks of 256 inputs [begin, end) of every row, packed row after row */
+int ribn_gguf_shard_bytes(ribn_gguf* file, const char* name, int axis, uint64_t begin, uint64_t end, uint64_t* bytes,
+                          uint64_t* k_out, uint64_t* n_out);
+/* Copies a tensor's encoding (or a shard of it) from the file to device memory on the context's stream, through two
+ * pinned buffers of 8 MiB: the file read of one piece overlaps the copy of the previous one.  dst_bytes must equal the
+ * encoding's size (RIBN_E_OUTPUT_LENGTH); an empty encoding is RIBN_E_INVALID_WEIGHT; a file that ends early is
+ * RIBN_GGUF_E_UNEXPECTED_EOF (SourceIncomplete in the reference).  On return every piece has left the host buffers;
+ * the device copy completes in stream order.  Errors are read with ribn_gguf_last_error(file). */
+int ribn_materialize_quantized(ribn_ctx* ctx, ribn_gguf* file, const char* name, int axis, uint64_t begin, uint64_t end,
+                               void* device_dst, uint64_t dst_bytes);
+/* The device and the stream a context was created on. */
+int ribn_context_stream(const ribn_ctx* ctx, int* device, void** cuda_stream);
+
+/* ---- the reference's Q8_1 activation format (compatibility mode) ------------------------------
+ * CudaQ8_1Quantizer::execute (crates/nvidia/src/activation.rs:15-88 over activation.cu:3-28): every block of 32
+ * floats becomes nine words -- half(max|x|/127) | half(sum x) << 16, then 32 signed bytes round(x / scale).  The
+ * output is bit-identical to the reference kernel's (same division, roundf, shuffle tree and cvt.rn).  A batch is one
+ * linear stream of blocks.  x_len empty or not a multiple of 32 -> RIBN_E_INPUT_LENGTH; packed_len != x_len/32*9 ->
+ * RIBN_E_OUTPUT_LENGTH; more than 2^32-1 values -> RIBN_E_SHAPE_OVERFLOW. */
+int ribn_quantize_q8_1(ribn_ctx* ctx, const float* x_device, uint64_t x_len, uint32_t* packed_device, uint64_t packed_len);
+
+/* CudaQ4KQ8_1Gemv::execute / execute_batch and the Q5_K, Q6_K, Q8_0 twins (crates/nvidia/src/q4_q8_1.rs,
+ * kernels/quantized/q4_k_q8_1.cu:40-144, q5_k_q8_1.cu, q6_k_q8_1.cu, q8_0_q8_1.cu; CudaIntDotProjector,
+ * decode.rs:1341-1478): y[m][n] from Q8_1-packed activations [members][K/32*9] words by exact integer dots, the
+ * reference's lossy arithmetic.  members 1..8; 0 -> RIBN_E_INPUT_LENGTH, 9+ -> RIBN_E_INVALID_WEIGHT, both before
+ * geometry.  ribn_gemv is the accurate path; this one serves hosts that hold Q8_1 activations already. */
+int ribn_gemv_q8_1(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight, const uint32_t* packed_device,
+                   uint64_t packed_len, float* y_device, uint64_t y_len, uint32_t members);
+
 /* ---- decoder-layer operators between the GEMVs -------------------------------------------
  * The launches crates/nvidia/src/decode.rs:929-1052 (full_attention_layer) and :544-632 (run_step) make
  * between its projections, for a dense-attention layer with grouped-query attention.  All buffers are
@@ -288,6 +392,10 @@ typedef struct ribn_attention {
     void* v_cache;
     uint64_t max_context;      /* tokens the cache holds per (member, head) */
     uint64_t active_context;   /* upper bound of positions[m] + 1 in this call; plans the split of the KV range */
+    uint32_t shared_cache;     /* 0: member m owns cache slot m.  1: the members are consecutive tokens of ONE sequence (the
+                                * prefill chunk of decode.rs:2149-2267, whose attention loop :2945-3021 walks one cache): every
+                                * member appends to and reads slot 0 of k_cache / v_cache, causally through positions[m] */
+    uint32_t out_dtype;        /* RIBN_F32 or RIBN_BF16: element type of ribn_attention_decode's output */
 } ribn_attention;
 
 /* strided_rms_norm (model_ops.rs:660-684) on the query and key heads, rope_neox (:393-422) on both, and
@@ -298,12 +406,15 @@ int ribn_qk_norm_rope_append(ribn_ctx* ctx, const ribn_attention* attention, flo
 /* attn_score_gqa (model_ops.rs:439-562) without its output gate: softmax(q.K / sqrt(head_dim)).V over tokens
  * 0..positions[m] of every member, f32 accumulation; out is [members][q_heads * head_dim].  The KV range is
  * split over CTAs and merged (partials in the context workspace). */
-int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, float* out_device);
+int ribn_attention_decode(ribn_ctx* ctx, const ribn_attention* attention, const float* q_device, void* out_device);
 
 /* silu_mul (model_ops.rs:316-328): out[m][i] = silu(gate[m][i]) * up[m][i].  gate and up rows are
  * input_row_stride floats apart (so they can be the halves of one [members][2 * length] GEMV output). */
 int ribn_silu_mul(ribn_ctx* ctx, const float* gate_device, const float* up_device, float* out_device, uint32_t members,
                   uint64_t length, uint64_t input_row_stride);
+/* The same with a typed output (RIBN_F32 or RIBN_BF16): bf16 feeds ribn_gemm in a prefill chunk. */
+int ribn_silu_mul_typed(ribn_ctx* ctx, const float* gate_device, const float* up_device, void* out_device, int out_dtype,
+                        uint32_t members, uint64_t length, uint64_t input_row_stride);
 
 /* residual_add (model_ops.rs:600-610): y[i] += x[i]. */
 int ribn_residual_add(ribn_ctx* ctx, float* y_device, const float* x_device, uint64_t length);

@@ -87,6 +87,9 @@ class DenseModel:
     def __init__(self, weights: dict, layers: int, q_heads: int, kv_heads: int, head_dim: int, rope_base: float, eps: float,
                  rot_dims: int | None = None):
         self.w = weights
+        # True models a prefill chunk on the tensor-core GEMM, whose activation operands are bf16: the inputs of the
+        # seven projections are rounded to bf16 (the reference computes prefill in f32 like decode)
+        self.bf16_activations = False
         self.layers, self.q_heads, self.kv_heads, self.head_dim = layers, q_heads, kv_heads, head_dim
         self.rope_base, self.eps = rope_base, eps
         self.rot_dims = head_dim if rot_dims is None else rot_dims
@@ -97,9 +100,16 @@ class DenseModel:
     def _matvec(matrix: np.ndarray, x: np.ndarray) -> np.ndarray:
         return (matrix.astype(np.float64) @ x.astype(np.float64)).astype(np.float32)
 
+    def _operand(self, x: np.ndarray) -> np.ndarray:
+        if not self.bf16_activations:
+            return x
+        bits = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+        rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16 << 16).astype(np.uint32)      # round to nearest even on the top 16 bits
+        return rounded.view(np.float32).reshape(np.shape(x))
+
     def layer(self, i: int, hidden: np.ndarray, position: int) -> np.ndarray:
         w, d = self.w, self.head_dim
-        x = rms_norm_raw(hidden, w[f"blk.{i}.attn_norm"], self.eps)
+        x = self._operand(rms_norm_raw(hidden, w[f"blk.{i}.attn_norm"], self.eps))
         q = self._matvec(w[f"blk.{i}.attn_q"], x).reshape(self.q_heads, d)
         k = self._matvec(w[f"blk.{i}.attn_k"], x).reshape(self.kv_heads, d)
         v = self._matvec(w[f"blk.{i}.attn_v"], x).reshape(self.kv_heads, d)
@@ -107,10 +117,10 @@ class DenseModel:
         k = rope_neox(rms_norm_raw(k, w[f"blk.{i}.attn_k_norm"], self.eps), position, self.rot_dims, self.rope_base)
         self.keys[i] = np.concatenate([self.keys[i], to_f16(k)[None]], axis=0)
         self.values[i] = np.concatenate([self.values[i], to_f16(v)[None]], axis=0)
-        attended = attention(q, self.keys[i], self.values[i]).reshape(-1)
+        attended = self._operand(attention(q, self.keys[i], self.values[i]).reshape(-1))
         hidden = hidden + self._matvec(w[f"blk.{i}.attn_output"], attended)
-        x = rms_norm_raw(hidden, w[f"blk.{i}.ffn_norm"], self.eps)
-        act = silu_mul(self._matvec(w[f"blk.{i}.ffn_gate"], x), self._matvec(w[f"blk.{i}.ffn_up"], x))
+        x = self._operand(rms_norm_raw(hidden, w[f"blk.{i}.ffn_norm"], self.eps))
+        act = self._operand(silu_mul(self._matvec(w[f"blk.{i}.ffn_gate"], x), self._matvec(w[f"blk.{i}.ffn_up"], x)))
         return (hidden + self._matvec(w[f"blk.{i}.ffn_down"], act)).astype(np.float32)
 
     def step(self, token: int, position: int) -> np.ndarray:

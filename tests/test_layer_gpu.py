@@ -299,7 +299,17 @@ def test_gemv_fused_equals_the_separate_calls(ctx, members, x_dtype):
 
 
 # ---- the decode loop on a small random model
-def small_model(ctx, geometry, seed=0):
+def damp_block_scales(encoded: np.ndarray, vt: int, factor: float) -> np.ndarray:
+    """Multiplies the f16 super-block scales of an encoded tensor (the generator's weights have a gain of hundreds
+    per projection, which makes a deep random model chaotic)."""
+    blocks = encoded.reshape(-1, synth.BLOCK_LAYOUT[vt][1]).copy()
+    for offset in {8: (0,), 12: (0, 2), 13: (0, 2), 14: (208,)}[vt]:
+        d = blocks[:, offset:offset + 2].copy().view(np.float16).astype(np.float32) * factor
+        blocks[:, offset:offset + 2] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(-1)
+
+
+def small_model(ctx, geometry, seed=0, damp=None):
     shapes = decode.local_shapes(geometry, 1, 0)
     weights, host = decode.DenseWeights(), {}
     rng = np.random.default_rng(seed)
@@ -308,6 +318,8 @@ def small_model(ctx, geometry, seed=0):
         k, n = shapes[kind]
         vt = decode.VALUE_TYPES[kind]
         encoded = synth.random_weight(vt, k, n, seed=seed * 100 + salt)
+        if damp and kind in damp:
+            encoded = damp_block_scales(encoded, vt, damp[kind])
         weights.matrices[name] = engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new(name, [k, n]), vt, device(ctx, encoded))
         host[name] = oracle.dequantize(vt, encoded, k, n).reshape(n, k)
         if kind == "ffn_gate_up":   # the decoder stores gate rows then up rows as one matrix; the host model keeps them apart
@@ -366,3 +378,92 @@ def test_decode_loop_matches_host_model(members, graph):
         decoder.advance()
     assert decoder.positions.cpu().tolist() == [steps] * members
     context.close()
+
+
+# ---- prefill through the tensor-core GEMM, then decode from the cache it filled
+def test_prefill_then_decode_matches_serial_host_model():
+    """The reference requires chunked prefill to equal serial prefill (tests/cuda_reference.rs:5243-5337 of the reference
+    project compares them bit for bit on its float kernels).  Here a chunk runs through ribn_gemm, whose activation
+    operands are bf16, so the serial side is the host model fed one token at a time with the same seven operands rounded
+    to bf16."""
+    context = engine_b200.RibnContext(0, stream=torch.cuda.Stream())
+    geometry = decode.DenseGeometry(hidden=512, layers=2, q_heads=4, kv_heads=2, head_dim=128, intermediate=768, vocabulary=1000)
+    # projections damped so that every layer adds an update of the size of the residual stream itself
+    weights, host = small_model(context, geometry, seed=11, damp={"attn_v": 2.0 ** -6, "attn_output": 2.0 ** -7, "ffn_gate_up": 2.0 ** -6,
+                                                                  "ffn_down": 2.0 ** -8})
+    members = 2
+    decoder = decode.CudaDenseDecode(context, geometry, weights, members, max_context=64)
+    models = [layer_np.DenseModel(host, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.head_dim, geometry.rope_base, geometry.eps)
+              for _ in range(members)]
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, geometry.vocabulary, 5).tolist(), rng.integers(0, geometry.vocabulary, 37).tolist()]
+    refs = []
+    for m, prompt in enumerate(prompts):
+        models[m].bf16_activations = True
+        for position, token in enumerate(prompt):
+            ref = models[m].step(token, position)
+        models[m].bf16_activations = False                    # the output head of the last token and the decode steps run in f32
+        refs.append(ref)
+        decoder.prefill(prompt, sequence=m, chunk=16)       # 37 tokens: two full chunks and a ragged one
+    context.synchronize()
+    assert decoder.positions.cpu().tolist() == [5, 37]
+    logits = decoder.logits.cpu().numpy()
+    tokens = decoder.tokens.cpu().tolist()
+    for m in range(members):
+        scale = np.max(np.abs(refs[m]))
+        assert np.max(np.abs(logits[m] - refs[m])) <= 3e-2 * scale
+        top = np.sort(refs[m])[-2:]
+        if top[1] - top[0] > 6e-2 * scale:
+            assert tokens[m] == int(np.argmax(refs[m]))
+        # the cache the chunks left behind: every prompt position, nothing beyond
+        for layer in range(geometry.layers):
+            n = len(prompts[m])
+            got = decoder.k_cache[layer, m, :, :n].float().cpu().numpy().transpose(1, 0, 2)
+            want = models[m].keys[layer]
+            assert np.max(np.abs(got - want)) <= 2e-2 * np.max(np.abs(want))
+            assert not decoder.k_cache[layer, m, :, n:].any() and not decoder.v_cache[layer, m, :, n:].any()
+    # decode from there: both sequences together, at their own positions
+    for step in range(3):
+        decoder.run_step()
+        context.synchronize()
+        logits = decoder.logits.cpu().numpy()
+        chosen = decoder.next_tokens.cpu().tolist()
+        for m in range(members):
+            ref = models[m].step(tokens[m], len(prompts[m]) + step)
+            scale = np.max(np.abs(ref))
+            assert np.max(np.abs(logits[m] - ref)) <= 3e-2 * scale, f"step {step} member {m}"
+            top = np.sort(ref)[-2:]
+            if top[1] - top[0] > 6e-2 * scale:
+                assert chosen[m] == int(np.argmax(ref))
+            tokens[m] = chosen[m]
+        decoder.advance()
+    context.close()
+
+
+def test_shared_cache_attention_is_causal_over_one_sequence(ctx, ops):
+    """A prefill chunk: member t is token t of one sequence; it appends at its own position of the one cache and
+    attends to tokens 0..t."""
+    q_heads, kv_heads, d, count, max_context = 4, 2, 128, 40, 48
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((count, q_heads, d)).astype(np.float32)
+    k = rng.standard_normal((count, kv_heads, d)).astype(np.float32)
+    v = rng.standard_normal((count, kv_heads, d)).astype(np.float32)
+    ones = device(ctx, np.ones(d, np.float32))
+    positions = device(ctx, np.arange(count, dtype=np.int32))
+    k_cache = torch.zeros(1, kv_heads, max_context, d, dtype=torch.float16, device=ctx.device)
+    v_cache = torch.zeros_like(k_cache)
+    attention = _lib.Attention(count, q_heads, kv_heads, d, d, 1e6, 1e-6, ones.data_ptr(), ones.data_ptr(), positions.data_ptr(), k_cache.data_ptr(),
+                               v_cache.data_ptr(), max_context, count, 1, _lib.RIBN_BF16)
+    qd = device(ctx, q)
+    ops.qk_norm_rope_append(attention, qd, device(ctx, k), device(ctx, v))
+    out = torch.zeros(count, q_heads * d, dtype=torch.bfloat16, device=ctx.device)
+    ops.attention_decode(attention, qd, out)
+    ctx.synchronize()
+    keys = k_cache[0].float().cpu().numpy().transpose(1, 0, 2)       # [token][kv_head][d]
+    values = v_cache[0].float().cpu().numpy().transpose(1, 0, 2)
+    assert np.array_equal(values[:count], v.astype(np.float16).astype(np.float32)) and not values[count:].any()
+    rotated = qd.cpu().numpy()
+    for t in (0, 1, 17, count - 1):
+        ref = layer_np.attention(rotated[t], keys[:t + 1], values[:t + 1])
+        got = out[t].float().cpu().numpy().reshape(q_heads, d)
+        assert np.max(np.abs(got - ref)) <= 2 ** -8 * max(1.0, np.max(np.abs(ref)))       # one bf16 rounding of the output
