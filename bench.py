@@ -469,7 +469,7 @@ def cpu_baseline_leg(ctx=None):
             return yd.cpu().numpy().astype(np.float64), xd.float().cpu().numpy()
         finally:
             for name, _ in options:
-                ctx.set_option(name, {"mma_gemv": 1, "gemv_path": 0}[name])
+                ctx.set_option(name, {"mma_gemv": 1, "gemv_path": 0, "tmem_gemv": 1}[name])
 
     for vt in FORMATS:
         for n, k in SHAPES:
@@ -493,7 +493,9 @@ def cpu_baseline_leg(ctx=None):
                 observe("mma_f16 (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
                 x16 = synth.random_activations(16, k, seed=16)
                 y, seen = gpu_gemv(vt, w, k, n, x16, torch.bfloat16)
-                observe("tcgen05_f16_tile (16 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                observe("tcgen05_weights_in_tmem (16 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                y, seen = gpu_gemv(vt, w, k, n, x16, torch.bfloat16, options=(("tmem_gemv", 0),))
+                observe("tcgen05_f16_tile (16 rows, bf16 in; tmem_gemv = 0)", vt, n, k, w, seen, y, norms=norms)
                 y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("mma_gemv", 0),))
                 observe("integer_dot (1 row, f32 in)", vt, n, k, w, seen, y, norms=norms)
                 y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("gemv_path", 1),))

@@ -38,7 +38,7 @@ struct ribn_ctx {
     int tc_f32_activations = 0;     // 1 = f32 activation batches may use the tensor-core kernel too (they are rounded to f16)
     int64_t tc_four_row_bytes = 8 << 20;   // batches of four rows use the tensor-core kernel too when the weights are at least this large
     int tc_min_members = 9;         // batches of at least this many rows go to the tcgen05 decode kernel
-    int tmem_gemv = 0;              // 1 = Q4_K / Q5_K calls of up to 8 f32 / 16 bf16 rows use the kernel that unpacks the weights into tensor memory
+    int tmem_gemv = 1;              // 1 = Q4_K / Q5_K batches of nine or more rows use the kernel that unpacks the weights into tensor memory
     int mma_gemv = 1;               // 1 = batches of up to eight rows use the half2-unpack + mma.sync kernel where it serves the shape
     int mma_image_members = 3;      // launches of at least this many rows convert their activations in a pre-pass, fewer inside the kernel
     int mma_stages = 0;             // ring depth of that kernel, 0 = as many stages as fit
@@ -298,13 +298,16 @@ int enqueue_tc(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, con
 
 // The tcgen05 kernel with the weight operand in tensor memory.
 bool tmem_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, uint32_t members, int x_dtype) {
-    if (ctx->tmem_gemv == 0 || ctx->gemv_path != 0) return false;
+    // Batches of nine or more rows (tc_min_members) of Q4_K / Q5_K: weights unpacked into tensor memory.  f32 batches
+    // come here only on request, like the f16-tile kernel (their default keeps every row bit-identical to a batch of one).
+    if (ctx->tmem_gemv == 0 || ctx->gemv_path != 0 || members < static_cast<uint32_t>(ctx->tc_min_members)) return false;
+    if (x_dtype != RIBN_BF16 && ctx->tc_f32_activations == 0) return false;
     return ribn::qgemv_tmem_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), static_cast<int>(members), x_dtype == RIBN_BF16,
                                      w->data);
 }
 
 int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
-                 float eps, void* y, int y_dtype, uint32_t members, bool accumulate) {
+                 float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready = false) {
     ribn::TmemGemvArgs a{};
     a.weights = static_cast<const uint8_t*>(w->data);
     a.value_type = w->value_type;
@@ -325,9 +328,11 @@ int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.ticket_count = kTicketCount;
     a.force_ksplit = ctx->tc_ksplit;
     a.stages = ctx->mma_stages;
+    a.image_ready = image_ready;
+    a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
+    if (a.trace != nullptr) a.scratch_bytes -= kTraceBytes;
     a.device_status = ctx->device_status;
     a.sm_count = ctx->sm_count;
-    a.trace = ctx->tc_trace != 0 ? reinterpret_cast<long long*>(static_cast<uint8_t*>(ctx->workspace) + ctx->workspace_bytes - kTraceBytes) : nullptr;
     a.stream = ctx->stream;
     const cudaError_t e = ribn::launch_qgemv_tmem(a);
     if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
@@ -503,7 +508,7 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
         for (uint32_t j = 0; j < job_count; ++j) {
             const int rc = enqueue_tmem(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
-                                        jobs[j].accumulate != 0);
+                                        jobs[j].accumulate != 0, /*image_ready=*/j > 0);
             if (rc != RIBN_OK) return rc;
         }
         return RIBN_OK;
@@ -696,6 +701,10 @@ int ribn_synchronize(ribn_ctx* ctx) {
     if (e != cudaSuccess) return record_cuda(ctx, e, "status readback");
     if (status != ribn::kDeviceOk) {
         cudaMemset(ctx->device_status, 0, sizeof(int));
+        if (status == ribn::kDeviceScaleRange)
+            return record(ctx, fail(RIBN_E_INVALID_WEIGHT,
+                                    "invalid quantized weight: a super-block scale of 32 or more cannot be folded into f16 weights; results of this "
+                                    "stream are invalid (set option tmem_gemv to 0 for such tensors)"));
         if (status == ribn::kDevicePositionOutOfRange)
             return record(ctx, fail(RIBN_E_INVALID_ARGUMENT,
                                     "a KV-cache position read from device memory lay outside the cache; nothing was stored there and the "

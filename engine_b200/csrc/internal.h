@@ -43,6 +43,7 @@ cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
 // Device status word values written by kernels whose bounded waits ran out.
 constexpr int kDeviceOk = 0;
 constexpr int kDeviceWaitTimeout = 1;
+constexpr int kDeviceScaleRange = 3;           // a super-block scale of 32 or more met the kernel that folds it into f16 weights
 constexpr int kDevicePositionOutOfRange = 2;   // a KV-cache position read from device memory lay outside the cache (or the planned context)
 
 struct GemvArgs {
@@ -138,15 +139,16 @@ struct TmemGemvArgs {
     bool y_bf16;
     bool accumulate;          // y += W x
     int members;
-    void* scratch;            // split-K partial tiles
+    void* scratch;            // the activation tiles, then split-K partial tiles
     size_t scratch_bytes;
     unsigned int* tickets;    // zero-initialised counters, one per row tile
     int ticket_count;
     int force_ksplit;         // 0 = choose
     int stages;               // raw ring depth, 0 = as deep as fits
+    bool image_ready;         // the activation tiles of this x are in the scratch already (an earlier projection of the same call)
+    long long* trace;         // diagnostics buffer (builds with -DRIBN_TRACE), or null
     int* device_status;
     int sm_count;
-    long long* trace;         // diagnostics buffer (builds with -DRIBN_TRACE), or null
     cudaStream_t stream;
 };
 bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_bf16, const void* weights);
@@ -167,7 +169,7 @@ struct TcArgs {
     bool accumulate;          // launch_qgemv_tc only: y += W x
     void* y;                  // [m][n]
     bool y_bf16;
-    void* scratch;            // split-K partial tiles
+    void* scratch;            // the activation tiles, then split-K partial tiles
     size_t scratch_bytes;
     unsigned int* tickets;    // zero-initialised counters, one per output tile
     int ticket_count;

@@ -1,40 +1,49 @@
-// Quantized GEMV / skinny GEMM on the 5th-generation tensor cores with the weight operand unpacked straight
-// into tensor memory.
+// Quantized skinny GEMM (9..64 member rows) on the 5th-generation tensor cores with the weight operand unpacked
+// straight into tensor memory.
 //
-//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]          m = 1..16 member rows per launch
+//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]          Q4_K / Q5_K / Q6_K, up to 64 bf16 or 32 f32 member rows per launch
 //
 // The path is bound by HBM: a 4.5-bit weight arrives every ~0.025 SM clocks, which leaves about three thread
 // instructions per weight, and the integer pipe -- where the bit manipulation of the unpacking runs -- issues
 // at half rate.  Two things decide whether a kernel keeps up: instructions per weight, and where the
 // dequantised operand lives.  Writing an f16 tile to shared memory for the tensor pipe costs 2 bytes written
-// and 2 read per weight against 0.56 streamed; the warp-level mma.sync keeps the operand in registers but makes
-// every thread unpack for a 2-row x 4-element fragment and fetch its own B fragment (about three instructions
-// per weight).  Here
+// and 2 read per weight against 0.56 streamed; the warp-level mma.sync keeps the operand in registers but pays
+// its issue rate per eight member rows.  Here
 //   * a thread owns one weight row (one TMEM lane).  It reads the row's raw super-block bytes from the
 //     shared-memory ring (tiled TMA boxes of 128 rows x one super-block) and expands two quants at a time
-//     with one logic op and one HFMA2:  (q | 0x6400) is the half 1024 + q, and (1024 + q) * sc - 1024 * sc
-//     = q * sc is exact in f16 for Q4_K / Q5_K (q * sc <= 1953 < 2048);
-//   * the expanded values go to tensor memory with tcgen05.st (32 K elements per instruction and row) and are
-//     the A operand of tcgen05.mma (M = 128 rows, K = 16 per instruction, N = 16 columns), so they never
-//     pass through shared memory;
-//   * the B operand -- the activations as f16, two planes (hi + lo) for f32 inputs -- is a small K-major
-//     tile set in shared memory that the CTA converts for its own K range only (CTAs split K), scaled by a
-//     power of two per (member, super-block);
-//   * the super-block scale d, and dmin times the activations' block sums (one more MMA with the eight
-//     6-bit minima as A), are applied in f32 once per super-block and row when the accumulator is read back.
-// About 1.3 thread instructions per weight, 0.7 of them on the integer pipe.
+//     with one logic op and one HFMA2:  (q | 0x6400) is the half 1024 + q, and with s = f16(d * sc)
+//     (1024 + q) * s - 1024 * s = q * s in one rounding;
+//   * the expanded values -- the complete weight d * sc * q, so that every super-block accumulates into the
+//     same accumulator -- go to tensor memory with tcgen05.st (32 K elements per instruction and row) and are
+//     the A operand of tcgen05.mma (M = 128 rows, K = 16 per instruction, N = 16 / 32 / 64 columns); they never
+//     pass through shared memory.  The minimum term -dmin * m[g] * sum_g(x) is one more MMA per super-block with
+//     the eight products -dmin * m[g] as A and the activations' block sums as B;
+//   * the B operand -- the activations as f16, scaled by one power of two per member row, two planes (hi + lo)
+//     for f32 inputs -- is made once per call by a pre-pass in exactly the swizzled K-major tiles the MMA
+//     reads, and streamed from L2 into a shared-memory ring with bulk copies next to the weights;
+//   * the accumulator is read back once, at the end of the CTA's K range.
+// About 1.5 thread instructions per weight whatever the number of member rows.
+//
+// Q6_K (210-byte super-blocks, no minima): the quant under the magic byte is 1024 + 4 q; minus 1152 it is 4 (q - 32)
+// exactly, and one HMUL2 with f16(d * sc / 4) makes the weight.  A TMA box must start on a 16-byte boundary, so its
+// boxes are 240 bytes wide from the boundary below each super-block and the lanes read at the (uniform) remainder.
+//
+// Range: f16(d * sc) and 1024 * f16(d * sc) must be finite, i.e. |d| * 63 < 64.  Rows whose super-block scale
+// is larger (up to 32) take a second multiply per pair; beyond that the context's status word reports it.
+// Super-block scales below 1e-6 lose bits to f16 subnormals (the product d * sc * q itself is an f16).
 //
 // CTA = 128 rows x a K range; grid = row tiles x K splits.  Warps 0..7 are workers (thread = row; warps 0..3
-// expand the first 128 weights of every super-block, warps 4..7 the second 128, and each half reads back
-// half of the accumulator columns), warp 8 streams the raw weights, warp 9 issues the MMAs and owns the TMEM
-// allocation.  Partial results of K splits meet in global scratch: the CTA that draws the last ticket of a
-// row tile adds them in split order (deterministic).
+// expand the first 128 weights of every super-block, warps 4..7 the second 128), warp 8 streams the raw
+// weights and the activation tiles, warp 9 issues the MMAs and owns the TMEM allocation.  Partial results of
+// K splits meet in global scratch: the CTA that draws the last ticket of a row tile adds them in split order
+// (deterministic).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets the status word and every warp still
 // reaches the teardown that frees TMEM.
 //
-// Reference counterparts: q*_gemv_warp / _warp_batch (crates/nvidia/src/kernels/quantized/q4_k.cu:103-258,
-// q5_k.cu) for the contract; rms_norm (crates/nvidia/src/model_ops.rs:106-147) and silu_mul
+// Reference counterparts: q*_gemv_warp_batch (crates/nvidia/src/kernels/quantized/q4_k.cu:161-258, q5_k.cu)
+// for the contract -- the reference serves wider batches as several launches of eight rows
+// (crates/nvidia/src/decode.rs:1953-1977); rms_norm (crates/nvidia/src/model_ops.rs:106-147) and silu_mul
 // (model_ops.rs:316-328) for the fused prologues.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -55,20 +64,12 @@ constexpr int kRows = 128;                 // weight rows per CTA = UMMA M = TME
 constexpr int kWorkerWarps = 8;
 constexpr int kWorkers = kWorkerWarps * 32;
 constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;
-constexpr int kTmemThreads = 320;
-constexpr int kNT = 16;                    // accumulator columns (UMMA N)
+constexpr int kIssuerWarp = 9;             // issues pairs 0 and 1 of every super-block and the minimum term into accumulator 0; owns TMEM
+constexpr int kIssuerWarp2 = 10;           // issues pairs 2 and 3 into accumulator 1
+constexpr int kTmemThreads = 352;
 constexpr int kPairs = 4;                  // 64-weight pairs of sub-blocks per super-block = A slots in TMEM
 constexpr int kPairColumns = 32;           // TMEM columns of one pair: 64 halves per row
-constexpr int kDBuffers = 2;
-constexpr int kMaxLocalSb = 16;            // super-blocks of one CTA's K range (its B tiles stay resident: 8 KB each)
-constexpr int kMaxRawStages = 4;
-
-// TMEM columns: [A pairs: 4 x 32][A minima: 2 x 8][D: 2 buffers x (16 main + 16 minimum term)]
-constexpr int kColAMin = kPairs * kPairColumns;
-constexpr int kColD = kColAMin + kDBuffers * 8;
-constexpr int kTmemColumns = 256;
-static_assert(kColD + kDBuffers * 2 * kNT <= kTmemColumns, "TMEM plan");
+constexpr int kMaxStages = 4;
 
 struct TmemParams {
     const void* x;              // [members][k] (swiglu: [members][2k]) f32 or bf16
@@ -76,43 +77,63 @@ struct TmemParams {
     int mode;                   // 0 plain, 1 RMSNorm first, 2 silu(gate) * up
     const float* norm_weight;
     float eps;
+    uint8_t* image;             // the activations as MMA tiles (layout below), written by the pre-pass
     void* y;
     int y_bf16;
     int accumulate;
     float* partial;             // split-K scratch [ksplit][members][n]
     unsigned int* tickets;      // one zero-initialised counter per row tile
-    int k, n, nsb, members, planes, ksplit, raw_stages;
-    int b_sb;                   // super-blocks the resident B tiles are laid out for (the largest K range of a CTA)
+    int k, n, nsb, members, planes, ksplit, raw_stages, b_stages;
     int* status;
-    long long* trace;           // diagnostics (builds with -DRIBN_TRACE): SM clock stamps of CTA 0, or null
+    long long* trace;           // diagnostics (builds with -DRIBN_TRACE): wall-clock stamps of CTA (0, 0), or null
 };
 
-// trace[(warp * 16 + superblock) * 16 + event] = clock64(), CTA (0,0), lane 0.  Compiled in with -DRIBN_TRACE only.
-__device__ __forceinline__ void stamp(const TmemParams& p, int warp, int sb, int event) {
+// trace[role * 32 + event] = globaltimer (ns) of CTA (0, 0); roles: 0 producer, 1 issuer, 2 worker warp 0, 3 worker warp 4.
+__device__ __forceinline__ void stamp(const TmemParams& p, int role, int event) {
 #ifdef RIBN_TRACE
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && sb < 16 && event < 16)
-        p.trace[(warp * 16 + sb) * 16 + event] = clock64();
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && event < 32) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace[role * 32 + event] = static_cast<long long>(t);
+    }
 #else
     (void)p;
-    (void)warp;
-    (void)sb;
+    (void)role;
     (void)event;
 #endif
 }
 
-template <uint32_t FMT>
+// Activation image, per super-block one stage of five K-major tiles of NT rows (columns of the product) x 128 bytes
+// with the 128-byte swizzle: four tiles of 64 K elements each, then a tile whose first 32 bytes per row hold the
+// eight block sums (sum of 32 scaled values) as f16 hi parts, then their f16 lo parts (unused by Q6_K, which has no minima).  Member m of plane p is
+// row 2 m + p (one plane: row m).  Behind the stages: float up[NT], the inverse of each row's scale factor.
+template <int NT, int TILES>
+struct ImagePlan {
+    static constexpr int kTileBytes = NT * 128;
+    static constexpr int kStageBytes = TILES * kTileBytes;
+    __host__ __device__ static constexpr size_t scales_offset(int nsb) { return static_cast<size_t>(nsb) * kStageBytes; }
+    __host__ __device__ static constexpr size_t bytes(int nsb) { return scales_offset(nsb) + NT * sizeof(float); }
+};
+
+template <uint32_t FMT, int NT>
 struct TmemPlan {
+    using I = ImagePlan<NT, 5>;
     static constexpr int kSbBytes = Format<FMT>::kBytes;
-    static constexpr int kRawStageBytes = kRows * kSbBytes;
-    static constexpr int kBTileBytes = kNT * 128;            // 16 columns x 64 K elements, f16
-    static_assert(kSbBytes % 16 == 0, "rows of a raw stage must stay 16-byte aligned");
-    // shared memory: [raw ring][B tiles: 4 per super-block][sum tiles: 1 per 4 super-blocks][scale: f32 [sb][16]]
-    //                [norm scratch][barriers]
-    __host__ __device__ static constexpr size_t b_bytes(int local_sb) { return static_cast<size_t>(local_sb) * 4 * kBTileBytes; }
-    __host__ __device__ static constexpr size_t sums_bytes(int local_sb) { return static_cast<size_t>((local_sb + 3) / 4) * kBTileBytes; }
-    __host__ __device__ static constexpr size_t smem_bytes(int raw_stages, int local_sb) {
-        return 1024 + static_cast<size_t>(raw_stages) * kRawStageBytes + b_bytes(local_sb) + sums_bytes(local_sb) +
-               static_cast<size_t>(local_sb) * kNT * 4 + (kWorkerWarps + 1) * 16 * 4 + 256;
+    // Q6_K super-blocks are 210 bytes: a TMA box must start on a 16-byte boundary and be a multiple of 16 bytes wide, so
+    // the box is 240 bytes from the boundary below the super-block; the data starts (sb * 210) % 16 bytes into every row
+    static constexpr int kRowPitch = FMT == kQ6_K ? 240 : kSbBytes;
+    static constexpr int kRawStageBytes = kRows * kRowPitch;
+    // A operand: one or two sets of four pair slots; two when the accumulator leaves room and one CTA owns the SM anyway
+    static constexpr int kABuffers = NT >= 64 ? 2 : 1;
+    static constexpr int kColAMin = kABuffers * kPairs * kPairColumns;
+    static constexpr int kColD = kColAMin + 2 * 8;
+    // two accumulators, one per issuing warp (MMAs of different threads into one accumulator are not ordered)
+    static constexpr int kColumnsUsed = kColD + 2 * NT;
+    static constexpr int kTmemColumns = kColumnsUsed <= 256 ? 256 : 512;
+    static_assert(kColumnsUsed <= 512, "TMEM plan");
+    static_assert(kRowPitch % 16 == 0 && kRawStageBytes % 128 == 0, "rows of a raw stage stay 16-byte aligned, stages 128-byte aligned");
+    __host__ __device__ static constexpr size_t smem_bytes(int raw_stages, int b_stages) {
+        return 1024 + static_cast<size_t>(b_stages) * I::kStageBytes + static_cast<size_t>(raw_stages) * kRawStageBytes + NT * 4 + 512;
     }
 };
 
@@ -144,6 +165,35 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "memory");
 }
 
+
+// The four MMAs of one pair (64 K elements): A slices 8 TMEM columns apart, B slices 32 bytes apart along the swizzled
+// rows (+2 in the descriptor's address field); one election for the four.  `accumulate_first` = 0 makes the first
+// slice overwrite D.
+__device__ __forceinline__ void umma_f16_tmem_a_pair_elected(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pf, pt, pe;\n\t"
+        ".reg .b64 b1, b2, b3;\n\t"
+        ".reg .b32 a1, a2, a3, leader;\n\t"
+        "elect.sync leader|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pf, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "add.u32 a1, %1, 8;\n\t"
+        "add.u32 a2, %1, 16;\n\t"
+        "add.u32 a3, %1, 24;\n\t"
+        "add.s64 b1, %2, 2;\n\t"
+        "add.s64 b2, %2, 4;\n\t"
+        "add.s64 b3, %2, 6;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, pt;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: 128 rows x 16 K elements from tensor memory (lane = row, 8 columns), B as a
 // shared-memory descriptor; issued by the elected lane of a converged warp.
 __device__ __forceinline__ void umma_f16_tmem_a_elected(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -160,75 +210,7 @@ __device__ __forceinline__ void umma_f16_tmem_a_elected(uint32_t tmem_d, uint32_
         : "memory");
 }
 
-// ---------------------------------------------------------------- activations -> B tiles (this CTA's K range)
-// One warp converts super-block `sb` (global index) of member row m: 256 values, eight per lane, scaled by a
-// power of two that brings the largest magnitude into [512, 1024) and rounded to f16 (plane 0; plane 1 holds
-// the remainder for f32 inputs).  Column of plane p of member m: p * 8 + m.  Within a group of four K
-// elements the tile holds them in the order [e0, e2, e1, e3], the order the weight unpacking produces.
-struct BTiles {
-    uint8_t* tiles;     // [local sb][4][kNT x 128 B]
-    uint8_t* sums;      // [local sb / 4][kNT x 128 B]: per column 4 x (8 block sums hi | 8 block sums lo)
-    float* scale;       // [local sb][kNT]
-};
-
-__device__ __forceinline__ void convert_to_tiles(const TmemParams& p, const float (&raw)[8], int m, int local_sb, int lane, const BTiles& b) {
-    float v[8];
-    float amax = 0.0f;
-    bool bad = false;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        v[j] = raw[j];
-        const float a = fabsf(v[j]);
-        bad = bad || !(a <= 3.0e38f);
-        amax = fmaxf(amax, a);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    bad = __any_sync(0xffffffffu, bad);
-    int e = 9 - (static_cast<int>(__float_as_uint(amax) >> 23) - 127);
-    e = max(-100, min(100, e));
-    float down = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
-    float up = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    if (amax == 0.0f) up = 0.0f;
-    if (bad) {
-        down = 0.0f;
-        up = __int_as_float(0x7fc00000);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= down;
-    // lane's eight elements: chunk (lane & 7) of K step (lane >> 3) of the super-block
-    const uint32_t tile = static_cast<uint32_t>(local_sb * 4 + (lane >> 3)) * (kNT * 128);
-    const uint32_t sum_tile = static_cast<uint32_t>(local_sb >> 2) * (kNT * 128);
-    const uint32_t sum_chunk = static_cast<uint32_t>(local_sb & 3) * 2;
-#pragma unroll
-    for (int plane = 0; plane < 2; ++plane) {
-        if (plane == 1 && p.planes == 1) break;
-        const uint32_t column = static_cast<uint32_t>(plane * 8 + m);
-        float h[8];
-        float sum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            h[j] = __half2float(__float2half_rn(v[j]));
-            sum += h[j];
-            v[j] -= h[j];   // what plane 1 holds
-        }
-        *reinterpret_cast<uint4*>(b.tiles + tile + swizzled_chunk(column, lane & 7)) =
-            make_uint4(half2_bits(h[0], h[2]), half2_bits(h[1], h[3]), half2_bits(h[4], h[6]), half2_bits(h[5], h[7]));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if ((lane & 3) == 0) {
-            const __half hi = __float2half_rn(sum);
-            const __half lo = __float2half_rn(sum - __half2float(hi));
-            uint8_t* base = b.sums + sum_tile;
-            *reinterpret_cast<__half*>(base + swizzled_chunk(column, sum_chunk) + (lane >> 2) * 2) = hi;
-            *reinterpret_cast<__half*>(base + swizzled_chunk(column, sum_chunk + 1) + (lane >> 2) * 2) = lo;
-        }
-        if (lane == 0) b.scale[local_sb * kNT + column] = up;
-    }
-}
-
+// ---------------------------------------------------------------- pre-pass: activations -> MMA tiles in global memory
 __device__ __forceinline__ void load_activation_slice(const TmemParams& p, int m, int sb, int lane, float inv_rms, float (&v)[8]) {
     const int k0 = sb * kSuperBlock + lane * 8;
     const size_t row_elements = static_cast<size_t>(p.k) * (p.mode == 2 ? 2 : 1);
@@ -247,16 +229,110 @@ __device__ __forceinline__ void load_activation_slice(const TmemParams& p, int m
     }
 }
 
+// grid (members), 256 threads.  Three sweeps over the member's row (it stays in L1/L2): sum of squares when an RMSNorm
+// is fused, the largest magnitude of the values that enter the product, then the conversion: every value times the
+// power of two that brings that magnitude into [512, 1024), as f16 (plane 0) and, for f32 inputs, the f16 of what
+// plane 0 lost (plane 1).  Within a group of four K elements the tiles hold [e0, e2, e1, e3], the order the weight
+// unpacking produces.
+template <int NT>
+__global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p) {
+    using I = ImagePlan<NT, 5>;
+    __shared__ float red[8];
+    __shared__ uint32_t red_bits[8];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.x;
+    float inv_rms = 1.0f;
+    if (p.mode == 1) {
+        const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * p.k * (p.x_bf16 ? 2 : 4), p.x_bf16};
+        float part = 0.0f;
+        for (int c = threadIdx.x; c < p.k / 8; c += 256) {
+            float v[8];
+            load_row8(row + c * 8, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) part = fmaf(v[j], v[j], part);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) total += red[w];
+        inv_rms = 1.0f / sqrtf(total / static_cast<float>(p.k) + p.eps);
+    }
+    // non-negative floats order like their bit patterns; infinities and NaNs (0x7f800000 and above) come out on top
+    uint32_t biggest = 0u;
+    for (int sb = warp; sb < p.nsb; sb += 8) {
+        float v[8];
+        load_activation_slice(p, m, sb, lane, inv_rms, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) biggest = max(biggest, __float_as_uint(fabsf(v[j])));
+    }
+    biggest = __reduce_max_sync(0xffffffffu, biggest);
+    if (lane == 0) red_bits[warp] = biggest;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < 8; ++w) biggest = max(biggest, red_bits[w]);
+    const bool bad = biggest >= 0x7f800000u;
+    const float amax = __uint_as_float(biggest);
+    int e = 9 - (static_cast<int>(biggest >> 23) - 127);
+    e = max(-100, min(100, e));
+    float down = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
+    float up = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+    if (amax == 0.0f) up = 0.0f;
+    if (bad) {
+        down = 0.0f;
+        up = __int_as_float(0x7fc00000);
+    }
+    float* scales = reinterpret_cast<float*>(p.image + I::scales_offset(p.nsb));
+    for (int sb = warp; sb < p.nsb; sb += 8) {
+        float v[8];
+        load_activation_slice(p, m, sb, lane, inv_rms, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = bad ? 0.0f : v[j] * down;
+        uint8_t* stage = p.image + static_cast<size_t>(sb) * I::kStageBytes;
+        // lane's eight elements: chunk (lane & 7) of K step (lane >> 3) of the super-block
+        uint8_t* tile = stage + (lane >> 3) * I::kTileBytes;
+        uint8_t* sums = stage + 4 * I::kTileBytes;
+#pragma unroll
+        for (int plane = 0; plane < 2; ++plane) {
+            if (plane == 1 && p.planes == 1) break;
+            const uint32_t column = static_cast<uint32_t>(p.planes == 2 ? 2 * m + plane : m);
+            float h[8];
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                h[j] = __half2float(__float2half_rn(v[j]));
+                sum += h[j];
+                v[j] -= h[j];   // what plane 1 holds
+            }
+            *reinterpret_cast<uint4*>(tile + swizzled_chunk(column, lane & 7)) =
+                make_uint4(half2_bits(h[0], h[2]), half2_bits(h[1], h[3]), half2_bits(h[4], h[6]), half2_bits(h[5], h[7]));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((lane & 3) == 0) {
+                const __half hi = __float2half_rn(sum);
+                const __half lo = __float2half_rn(sum - __half2float(hi));
+                *reinterpret_cast<__half*>(sums + swizzled_chunk(column, 0) + (lane >> 2) * 2) = hi;
+                *reinterpret_cast<__half*>(sums + swizzled_chunk(column, 1) + (lane >> 2) * 2) = lo;
+            }
+        }
+    }
+    if (threadIdx.x == 0) scales[m] = up;   // per member
+}
+
 // ---------------------------------------------------------------- weight unpacking: one row, one pair of sub-blocks
 // A pair is 32 quant bytes: the low nibbles are sub-block 2j (32 weights), the high nibbles sub-block 2j+1.
 // out_lo / out_hi: 16 registers = 32 halves each, K order [e0, e2, e1, e3] within every group of four.
+// mul_a / mul_b: the factor of each sub-block as a half pair; every quant is brought to the low mantissa bits of the
+// half 1024, so that one HFMA2 with -1024 * factor as addend leaves q * factor.
 template <uint32_t FMT>
-__device__ __forceinline__ void unpack_pair(uint32_t quant_addr, uint32_t fifth_addr, int j, uint32_t scale_pair, uint32_t (&out_lo)[16],
+__device__ __forceinline__ void unpack_pair(uint32_t quant_addr, uint32_t fifth_addr, int j, uint32_t mul_a, uint32_t mul_b, uint32_t (&out_lo)[16],
                                             uint32_t (&out_hi)[16]) {
-    const uint32_t mul_a = dup_low(scale_pair), mul_b = dup_high(scale_pair);
-    const uint32_t add_a = hmul2(mul_a, 0xe400e400u);    // -1024 * sc
-    const uint32_t add_b = hmul2(mul_b, 0xd400d400u);    // -64 * sc:  (1024 + 16 q) * sc/16 - 64 sc = q sc
-    const uint32_t mul_bh = hmul2(mul_b, 0x2c002c00u);   // sc / 16
+    const uint32_t add_a = hmul2(mul_a, 0xe400e400u);    // -1024 * factor
+    const uint32_t add_b = hmul2(mul_b, 0xe400e400u);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const uint4 q = lds128(quant_addr + 16 * half);
@@ -266,126 +342,193 @@ __device__ __forceinline__ void unpack_pair(uint32_t quant_addr, uint32_t fifth_
         const uint32_t fw[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t w = qw[i], ws = w >> 8;
-            uint32_t a0 = and_or(w, 0x000f000fu, kMagic), a1 = and_or(ws, 0x000f000fu, kMagic);
-            uint32_t b0 = and_or(w, 0x00f000f0u, kMagic), b1 = and_or(ws, 0x00f000f0u, kMagic);
+            const uint32_t w = qw[i];
+            uint32_t a0 = and_or(w, 0x000f000fu, kMagic), a1 = and_or(w >> 8, 0x000f000fu, kMagic);
+            uint32_t b0 = and_or(w >> 4, 0x000f000fu, kMagic), b1 = and_or(w >> 12, 0x000f000fu, kMagic);
             if (FMT == kQ5_K) {
                 // byte p of the fifth-bit bytes carries, in bit s, the fifth bit of position p of sub-block s
                 const uint32_t bits = fw[i] >> (2 * j);
                 a0 = and_or(bits << 4, 0x00100010u, a0);
                 a1 = and_or(bits >> 4, 0x00100010u, a1);
-                b0 = and_or(bits << 7, 0x01000100u, b0);
-                b1 = and_or(bits >> 1, 0x01000100u, b1);
+                b0 = and_or(bits << 3, 0x00100010u, b0);
+                b1 = and_or(bits >> 5, 0x00100010u, b1);
             }
             out_lo[half * 8 + i * 2 + 0] = hfma2(a0, mul_a, add_a);
             out_lo[half * 8 + i * 2 + 1] = hfma2(a1, mul_a, add_a);
-            out_hi[half * 8 + i * 2 + 0] = hfma2(b0, mul_bh, add_b);
-            out_hi[half * 8 + i * 2 + 1] = hfma2(b1, mul_bh, add_b);
+            out_hi[half * 8 + i * 2 + 0] = hfma2(b0, mul_b, add_b);
+            out_hi[half * 8 + i * 2 + 1] = hfma2(b1, mul_b, add_b);
+        }
+    }
+}
+
+// Q6_K: one group pair of a 128-weight chunk.  `la`, `lb`: the chunk's two runs of 32 low-nibble bytes, `qh` its 32
+// two-bit bytes (all at 2-byte alignment); V0 / V0 + 1 are the groups that go to out_lo / out_hi.  A quant byte
+// (q << 2) under the magic byte is the half 1024 + 4 q; minus 1152 that is 4 (q - 32), exactly; times f16(factor / 4) it is
+// the weight with one rounding relative to its own size (folding the offset into the addend of one HFMA2 would round
+// relative to 4 q, twice as coarse at the centre of the range, and 1152 f is not exact).
+template <int V0>
+__device__ __forceinline__ void unpack_pair_q6(uint32_t la, uint32_t lb, uint32_t qh, const float (&factor)[4], uint32_t (&out_lo)[16],
+                                               uint32_t (&out_hi)[16]) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const uint4 a = lds128_unaligned(la + 16 * half), b = lds128_unaligned(lb + 16 * half), h = lds128_unaligned(qh + 16 * half);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w}, hw[4] = {h.x, h.y, h.z, h.w};
+        const float f0 = factor[half], f1 = factor[2 + half];      // the scale of each run of 16 weights
+        const uint32_t mul0 = half2_bits(f0 * 0.25f, f0 * 0.25f);
+        const uint32_t mul1 = half2_bits(f1 * 0.25f, f1 * 0.25f);
+        constexpr uint32_t kCentre = 0x64806480u;   // 1152 = 1024 + 4 * 32
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t b0 = q6_bytes<V0>(aw[i], bw[i], hw[i]), b1 = q6_bytes<V0 + 1>(aw[i], bw[i], hw[i]);
+            out_lo[half * 8 + i * 2 + 0] = hmul2(hsub2(__byte_perm(b0, kMagicBytes, 0x4240), kCentre), mul0);   // positions 0, 2
+            out_lo[half * 8 + i * 2 + 1] = hmul2(hsub2(__byte_perm(b0, kMagicBytes, 0x4341), kCentre), mul0);   // positions 1, 3
+            out_hi[half * 8 + i * 2 + 0] = hmul2(hsub2(__byte_perm(b1, kMagicBytes, 0x4240), kCentre), mul1);
+            out_hi[half * 8 + i * 2 + 1] = hmul2(hsub2(__byte_perm(b1, kMagicBytes, 0x4341), kCentre), mul1);
         }
     }
 }
 
 // ---------------------------------------------------------------- the kernel
-template <uint32_t FMT>
-__global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const TmemParams p) {
-    using P = TmemPlan<FMT>;
+template <uint32_t FMT, int NT>
+__global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const TmemParams p) {
+    using P = TmemPlan<FMT, NT>;
+    using I = typename P::I;
     constexpr uint32_t kQuantOffset = FMT == kQ5_K ? 48 : 16;
+    constexpr int AB = P::kABuffers;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const int sb_begin = static_cast<int>(static_cast<long long>(p.nsb) * blockIdx.y / p.ksplit);
     const int sb_end = static_cast<int>(static_cast<long long>(p.nsb) * (blockIdx.y + 1) / p.ksplit);
     const int local_sb = sb_end - sb_begin;
-    // B tiles first: they need the 1024-byte alignment
-    BTiles b;
-    b.tiles = smem;
-    b.sums = b.tiles + P::b_bytes(p.b_sb);
-    uint8_t* raw = b.sums + P::sums_bytes(p.b_sb);
-    b.scale = reinterpret_cast<float*>(raw + static_cast<size_t>(p.raw_stages) * P::kRawStageBytes);
-    float* norm = b.scale + p.b_sb * kNT;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(norm + (kWorkerWarps + 1) * 16);
+    uint8_t* b_ring = smem;                                                          // 1024-byte aligned stages
+    uint8_t* raw = b_ring + static_cast<size_t>(p.b_stages) * I::kStageBytes;
+    float* up = reinterpret_cast<float*>(raw + static_cast<size_t>(p.raw_stages) * P::kRawStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(up + NT);
     uint64_t* raw_full = bars;
-    uint64_t* raw_empty = raw_full + kMaxRawStages;
-    uint64_t* a_full = raw_empty + kMaxRawStages;
-    uint64_t* a_empty = a_full + kPairs;
-    uint64_t* d_full = a_empty + kPairs;
-    uint64_t* d_empty = d_full + kDBuffers;
-    uint64_t* b_ready = d_empty + kDBuffers;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(b_ready + 1);
+    uint64_t* raw_empty = raw_full + kMaxStages;
+    uint64_t* b_full = raw_empty + kMaxStages;
+    uint64_t* b_empty = b_full + kMaxStages;
+    uint64_t* a_full = b_empty + kMaxStages;          // [AB * 4]
+    uint64_t* a_empty = a_full + 2 * kPairs;
+    uint64_t* min_full = a_empty + 2 * kPairs;        // [2]
+    uint64_t* min_empty = min_full + 2;
+    uint64_t* d_full = min_empty + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_full + 1);
     uint32_t* last_flag = tmem_holder + 1;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kRows;
     pdl_launch_dependents();
+    if (warp == 0) stamp(p, 2, 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.raw_stages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&raw_full[s], 1);
             mbar_init(&raw_empty[s], kWorkerWarps);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_empty[s], 2);            // tcgen05.commit of both issuing warps
         }
-        for (int j = 0; j < kPairs; ++j) {
-            mbar_init(&a_full[j], 4);      // the four warps of the half that writes the pair
-            mbar_init(&a_empty[j], 1);     // tcgen05.commit
+        for (int j = 0; j < 2 * kPairs; ++j) {
+            mbar_init(&a_full[j], 4);              // the four warps of the half that writes the pair
+            mbar_init(&a_empty[j], 1);             // tcgen05.commit
         }
-        for (int d = 0; d < kDBuffers; ++d) {
-            mbar_init(&d_full[d], 1);
-            mbar_init(&d_empty[d], kWorkerWarps);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&min_full[b], 4);
+            mbar_init(&min_empty[b], 1);
         }
-        mbar_init(b_ready, kWorkerWarps);
+        mbar_init(d_full, 2);
         mbar_fence_init();
         tma_prefetch_descriptor(&wmap);
     }
-    if (warp == kIssuerWarp) tmem_alloc(tmem_holder, kTmemColumns);
+    if (warp == kIssuerWarp) tmem_alloc(tmem_holder, P::kTmemColumns);
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    if (warp == 0) stamp(p, 2, 1);
 
     if (warp == kProducerWarp) {
-        // ---------------- raw weights: one tiled TMA box (128 rows x one super-block) per stage ----------------
+        // ---------------- one lane streams both rings; the weights do not depend on the kernel before this one ----------------
         if (lane == 0) {
-            for (int i = 0; i < local_sb; ++i) {
+            bool ok = true;
+            auto issue_raw = [&](int i) {
                 const int s = i % p.raw_stages;
-                if (i >= p.raw_stages && !mbar_wait_bounded(&raw_empty[s], ((i / p.raw_stages) - 1) & 1)) {
-                    atomicExch(p.status, kDeviceWaitTimeout);
-                    break;
-                }
+                if (i >= p.raw_stages && !mbar_wait_bounded(&raw_empty[s], ((i / p.raw_stages) - 1) & 1)) return false;
                 mbar_arrive_expect_tx(&raw_full[s], P::kRawStageBytes);
-                tma_load_2d(raw + static_cast<size_t>(s) * P::kRawStageBytes, &wmap, (sb_begin + i) * (P::kSbBytes / 2), n0, &raw_full[s]);
+                // x in 16-bit elements: the super-block's first byte, rounded down to a 16-byte boundary for Q6_K
+                const int x = FMT == kQ6_K ? (((sb_begin + i) * P::kSbBytes) & ~15) / 2 : (sb_begin + i) * (P::kSbBytes / 2);
+                tma_load_2d(raw + static_cast<size_t>(s) * P::kRawStageBytes, &wmap, x, n0, &raw_full[s]);
+                return true;
+            };
+            auto issue_b = [&](int i) {
+                const int s = i % p.b_stages;
+                if (i >= p.b_stages && !mbar_wait_bounded(&b_empty[s], ((i / p.b_stages) - 1) & 1)) return false;
+                mbar_arrive_expect_tx(&b_full[s], I::kStageBytes);
+                const uint8_t* src = p.image + static_cast<size_t>(sb_begin + i) * I::kStageBytes;
+                uint8_t* dst = b_ring + static_cast<size_t>(s) * I::kStageBytes;
+#pragma unroll 1
+                for (uint32_t done = 0; done < static_cast<uint32_t>(I::kStageBytes); done += 10240u)
+                    bulk_copy_g2s(dst + done, src + done, min(10240u, static_cast<uint32_t>(I::kStageBytes) - done), &b_full[s]);
+                return true;
+            };
+            int raw_i = 0, b_i = 0;
+            stamp(p, 0, 0);
+            for (; raw_i < min(p.raw_stages, local_sb) && ok; ++raw_i) ok = issue_raw(raw_i);
+            stamp(p, 0, 1);
+            pdl_wait_prior();   // the activation tiles are the pre-pass's output
+            stamp(p, 0, 2);
+            for (; b_i < min(p.b_stages, local_sb) && ok; ++b_i) ok = issue_b(b_i);
+            stamp(p, 0, 3);
+            while (ok && (raw_i < local_sb || b_i < local_sb)) {
+                if (b_i < local_sb) ok = issue_b(b_i++);
+                if (ok && raw_i < local_sb) ok = issue_raw(raw_i++);
             }
+            stamp(p, 0, 4);
+            if (!ok) atomicExch(p.status, kDeviceWaitTimeout);
         }
         __syncwarp();
-    } else if (warp == kIssuerWarp) {
-        // ---------------- MMA issuer: the warp runs converged, an elected lane issues ----------------
-        constexpr uint32_t idesc = umma_instr_desc(kRows, kNT, /*A f16*/ 0, /*B f16*/ 0);
-        const uint64_t desc_b0 = umma_smem_desc_sw128(smem_addr(b.tiles));
-        const uint64_t desc_s0 = umma_smem_desc_sw128(smem_addr(b.sums));
-        bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(b_ready, 0));
+    } else if (warp == kIssuerWarp || warp == kIssuerWarp2) {
+        // ---------------- MMA issuers: each warp runs converged, an elected lane issues ----------------
+        // Issuing is the serial part of the pipeline (about 50 clocks per instruction for one thread), so two warps share
+        // it: the first takes pairs 0, 1 and the minimum term, the second pairs 2, 3, each into its own accumulator.
+        constexpr uint32_t idesc = umma_instr_desc(kRows, NT, /*A f16*/ 0, /*B f16*/ 0);
+        const int which = warp == kIssuerWarp ? 0 : 1;
+        const uint32_t d_tmem = tmem_base + P::kColD + which * NT;
+        bool ok = true;
         for (int i = 0; i < local_sb && ok; ++i) {
-            const int buf = i % kDBuffers;
-            if (i >= kDBuffers) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&d_empty[buf], ((i / kDBuffers) - 1) & 1));
+            const int bs = i % p.b_stages;
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&b_full[bs], (i / p.b_stages) & 1));
             if (!ok) break;
-            const uint32_t d_main = tmem_base + kColD + buf * 2 * kNT;
-            for (int j = 0; j < kPairs && ok; ++j) {
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&a_full[j], i & 1));
-                if (!ok) break;
-                tcgen05_fence_after_sync();
-                stamp(p, warp, i, j * 2);
-                // pair j = K step j of the super-block (64 elements): B tile i * 4 + j, four K slices of 16
-                const uint64_t desc_b = desc_b0 + static_cast<uint64_t>((i * 4 + j) * (P::kBTileBytes >> 4));
+            if (i < 4 && which == 0) stamp(p, 1, i * 4);
+            const uint64_t desc_b0 = umma_smem_desc_sw128(smem_addr(b_ring + static_cast<size_t>(bs) * I::kStageBytes));
+            const int abuf = i % AB;
 #pragma unroll
-                for (int slice = 0; slice < 4; ++slice)
-                    umma_f16_tmem_a_elected(d_main, tmem_base + j * kPairColumns + slice * 8, desc_b + 2 * slice, idesc,
-                                            (j > 0 || slice > 0) ? 1u : 0u);
-                umma_commit_elected(&a_empty[j]);
-                stamp(p, warp, i, j * 2 + 1);
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = which * 2 + jj;
+                ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(&a_full[abuf * kPairs + j], (i / AB) & 1));
+                if (!ok) break;
+                if (i < 4 && which == 0) stamp(p, 1, i * 4 + 1 + jj);
+                tcgen05_fence_after_sync();
+                // pair j = K step j of the super-block (64 elements): tile j of the stage, four K slices of 16
+                umma_f16_tmem_a_pair_elected(d_tmem, tmem_base + (abuf * kPairs + j) * kPairColumns, desc_b0 + static_cast<uint64_t>(j * (I::kTileBytes >> 4)),
+                                             idesc, (i > 0 || jj > 0) ? 1u : 0u);
+                umma_commit_elected(&a_empty[abuf * kPairs + j]);
             }
             if (!ok) break;
-            // minimum term: A = the eight 6-bit minima twice, B = block sums hi | lo of this super-block
-            umma_f16_tmem_a_elected(d_main + kNT, tmem_base + kColAMin + buf * 8,
-                                    desc_s0 + static_cast<uint64_t>((i >> 2) * (P::kBTileBytes >> 4)) + 2 * (i & 3), idesc, 0u);
-            umma_commit_elected(&d_full[buf]);
+            if (FMT != kQ6_K && which == 0) {
+                // minimum term: A = -dmin * m[g] twice (K slots 0..7 meet the block sums' hi parts, 8..15 their lo parts)
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&min_full[i & 1], (i >> 1) & 1));
+                if (!ok) break;
+                tcgen05_fence_after_sync();
+                umma_f16_tmem_a_elected(d_tmem, tmem_base + P::kColAMin + (i & 1) * 8, desc_b0 + static_cast<uint64_t>(4 * (I::kTileBytes >> 4)), idesc, 1u);
+                umma_commit_elected(&min_empty[i & 1]);
+            }
+            umma_commit_elected(&b_empty[bs]);
+            if (i < 4 && which == 0) stamp(p, 1, i * 4 + 3);
         }
+        if (ok) umma_commit_elected(d_full);
+        if (which == 0) stamp(p, 1, 16);
         if (!ok && lane == 0) atomicExch(p.status, kDeviceWaitTimeout);
         __syncwarp();
     } else {
@@ -394,86 +537,8 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
         const int quadrant = warp & 3;                   // a warp reaches TMEM lanes 32 * (warp % 4) .. + 31
         const int row_in_tile = quadrant * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16);
+        const uint32_t raw_addr = smem_addr(raw) + static_cast<uint32_t>(row_in_tile) * P::kRowPitch;
         bool ok = true;
-
-        // B tiles of this CTA's K range: the activations may be the previous kernel's output
-        pdl_wait_prior();
-        if (p.mode == 1) {
-            for (int m = 0; m < p.members; ++m) {
-                const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * p.k * (p.x_bf16 ? 2 : 4), p.x_bf16};
-                float part = 0.0f;
-                for (int c = threadIdx.x; c < p.k / 8; c += kWorkers) {
-                    float v[8];
-                    load_row8(row + c * 8, v);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) part = fmaf(v[j], v[j], part);
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (lane == 0) norm[warp * 16 + m] = part;
-            }
-            named_barrier_sync(1, kWorkers);
-            if (threadIdx.x < 16) {
-                float total = 0.0f;
-#pragma unroll
-                for (int w = 0; w < kWorkerWarps; ++w) total += norm[w * 16 + threadIdx.x];
-                norm[kWorkerWarps * 16 + threadIdx.x] = 1.0f / sqrtf(total / static_cast<float>(p.k) + p.eps);
-            }
-            named_barrier_sync(1, kWorkers);
-        }
-        {
-            const int slices = local_sb * p.members;
-#pragma unroll 1
-            for (int first = warp; first < slices; first += 2 * kWorkerWarps) {
-                // two slices per trip so that their loads are in flight together
-                const int second = first + kWorkerWarps;
-                float v0[8], v1[8];
-                const int m0 = first % p.members, s0 = first / p.members;
-                load_activation_slice(p, m0, sb_begin + s0, lane, p.mode == 1 ? norm[kWorkerWarps * 16 + m0] : 1.0f, v0);
-                const int m1 = second < slices ? second % p.members : m0, s1 = second < slices ? second / p.members : s0;
-                load_activation_slice(p, m1, sb_begin + s1, lane, p.mode == 1 ? norm[kWorkerWarps * 16 + m1] : 1.0f, v1);
-                convert_to_tiles(p, v0, m0, s0, lane, b);
-                if (second < slices) convert_to_tiles(p, v1, m1, s1, lane, b);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_ready);
-        }
-        // every worker reads the scale factors the others wrote
-        named_barrier_sync(1, kWorkers);
-
-        float acc[kNT / 2];
-#pragma unroll
-        for (int c = 0; c < kNT / 2; ++c) acc[c] = 0.0f;
-        float d_prev = 0.0f, dmin_prev = 0.0f;
-        const uint32_t raw_addr = smem_addr(raw) + static_cast<uint32_t>(row_in_tile) * P::kSbBytes;
-        const uint32_t column0 = static_cast<uint32_t>(half * (kNT / 2));
-
-        auto read_back = [&](int i, float d, float dmin) {
-            // acc[c] += scale[c] * (d * D[c] - dmin * Dmin[c]) for this thread's row and this half's columns
-            const int buf = i % kDBuffers;
-            if (ok && !mbar_wait_bounded(&d_full[buf], (i / kDBuffers) & 1)) {
-                atomicExch(p.status, kDeviceWaitTimeout);
-                ok = false;
-            }
-            tcgen05_fence_after_sync();
-            uint32_t dm[8], dn[8];
-            const uint32_t taddr = lane_base + kColD + buf * 2 * kNT + column0;
-            tmem_ld8(taddr, dm);
-            tmem_ld8(taddr + kNT, dn);
-            tmem_ld_wait();
-            const float4 s0 = *reinterpret_cast<const float4*>(b.scale + i * kNT + column0);
-            const float4 s1 = *reinterpret_cast<const float4*>(b.scale + i * kNT + column0 + 4);
-            const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float t = fmaf(d, __uint_as_float(dm[c]), -(dmin * __uint_as_float(dn[c])));
-                acc[c] = fmaf(sc[c], t, acc[c]);
-            }
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&d_empty[buf]);
-        };
 
 #pragma unroll 1
         for (int i = 0; i < local_sb; ++i) {
@@ -482,80 +547,158 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
                 atomicExch(p.status, kDeviceWaitTimeout);
                 ok = false;
             }
-            stamp(p, warp, i, 0);
+            if (i < 4 && quadrant == 0) stamp(p, 2 + half, 2 + i * 4);
+            const int abuf = i % AB;
+            if constexpr (FMT == kQ6_K) {
+                const uint32_t blk = raw_addr + static_cast<uint32_t>(s) * P::kRawStageBytes + ((static_cast<uint32_t>(sb_begin + i) * 210u) & 15u);
+                const float d = f16_bits_to_f32(lds_u16(blk + 208));
+                const bool wide = !(fabsf(d) <= 1.0f);   // kept symmetrical with the other formats: beyond it d multiplies afterwards
+                if (!(fabsf(d) < 32.0f)) atomicExch(p.status, kDeviceScaleRange);
+                const uint32_t d2 = half2_bits(d, d);
+                const float fd = wide ? 1.0f : d;
+                // this half's chunk of 128 weights: 64 low-nibble bytes, 32 two-bit bytes, eight int8 scales
+                const uint32_t la = blk + 64 * half, lb = la + 32, qh = blk + 128 + 32 * half, sc = blk + 192 + 8 * half;
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = half * 2 + jj;
+                    const int slot = abuf * kPairs + j;
+                    // groups 2 jj and 2 jj + 1 of the chunk; factor[0..1]: the two runs of 16 of the first, [2..3]: of the second
+                    float factor[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) factor[r] = fd * static_cast<float>(lds_s8(sc + 4 * jj + r));
+                    uint32_t out_lo[16], out_hi[16];
+                    if (jj == 0) unpack_pair_q6<0>(la, lb, qh, factor, out_lo, out_hi);
+                    else unpack_pair_q6<2>(la, lb, qh, factor, out_lo, out_hi);
+                    if (wide) {
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) {
+                            out_lo[r] = hmul2(out_lo[r], d2);
+                            out_hi[r] = hmul2(out_hi[r], d2);
+                        }
+                    }
+                    if (i >= AB && ok && !mbar_wait_bounded(&a_empty[slot], ((i / AB) - 1) & 1)) {
+                        atomicExch(p.status, kDeviceWaitTimeout);
+                        ok = false;
+                    }
+                    tcgen05_fence_after_sync();
+                    tmem_st16(lane_base + slot * kPairColumns, out_lo);
+                    tmem_st16(lane_base + slot * kPairColumns + 16, out_hi);
+                    tmem_st_wait();
+                    tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[slot]);
+                }
+            } else {
             const uint32_t blk = raw_addr + static_cast<uint32_t>(s) * P::kRawStageBytes;
             const uint4 header = lds128(blk);   // d | dmin, 12 scale bytes
             uint32_t sc_lo, sc_hi, m_lo, m_hi;
             unpack_k_scales(header.y, header.z, header.w, sc_lo, sc_hi, m_lo, m_hi);
             const uint32_t sc_word = half ? sc_hi : sc_lo;   // scales of sub-blocks 4 half .. 4 half + 3
+            const float d = f16_bits_to_f32(header.x & 0xffffu);
+            const float dmin = f16_bits_to_f32(header.x >> 16);
+            // 1024 * f16(d * sc) must stay finite: beyond |d| = 1 the pair is expanded without d and multiplied afterwards
+            const bool wide = !(fabsf(d) <= 1.0f);
+            if (!(fabsf(d) < 32.0f)) atomicExch(p.status, kDeviceScaleRange);
+            const uint32_t d2 = half2_bits(d, d);
             if (half == 0) {
-                // the eight minima as f16, twice: K slots 0..7 meet the block sums' hi parts, 8..15 their lo parts
+                const float nd = -dmin;
                 uint32_t mins[8];
-                mins[0] = byte_pair_half2(m_lo, false);
-                mins[1] = byte_pair_half2(m_lo, true);
-                mins[2] = byte_pair_half2(m_hi, false);
-                mins[3] = byte_pair_half2(m_hi, true);
+                mins[0] = half2_bits(nd * byte_of(m_lo, 0), nd * byte_of(m_lo, 1));
+                mins[1] = half2_bits(nd * byte_of(m_lo, 2), nd * byte_of(m_lo, 3));
+                mins[2] = half2_bits(nd * byte_of(m_hi, 0), nd * byte_of(m_hi, 1));
+                mins[3] = half2_bits(nd * byte_of(m_hi, 2), nd * byte_of(m_hi, 3));
                 mins[4] = mins[0]; mins[5] = mins[1]; mins[6] = mins[2]; mins[7] = mins[3];
-                // the buffer was last read by the minimum MMA of super-block i - 2, whose accumulator this thread has read back
-                tmem_st8(lane_base + kColAMin + (i % kDBuffers) * 8, mins);
-            }
-#pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-                const int j = half * 2 + jj;
-                if (i > 0 && ok && !mbar_wait_bounded(&a_empty[j], (i - 1) & 1)) {
+                if (i >= 2 && ok && !mbar_wait_bounded(&min_empty[i & 1], ((i >> 1) - 1) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
                 }
                 tcgen05_fence_after_sync();
-                stamp(p, warp, i, 1 + 4 * jj);
-                uint32_t out_lo[16], out_hi[16];
-                unpack_pair<FMT>(blk + kQuantOffset + 32 * j, blk + 16, j, byte_pair_half2(sc_word, jj != 0), out_lo, out_hi);
-                stamp(p, warp, i, 2 + 4 * jj);
-                tmem_st16(lane_base + j * kPairColumns, out_lo);
-                tmem_st16(lane_base + j * kPairColumns + 16, out_hi);
-                stamp(p, warp, i, 3 + 4 * jj);
+                tmem_st8(lane_base + P::kColAMin + (i & 1) * 8, mins);
                 tmem_st_wait();
-                stamp(p, warp, i, 4 + 4 * jj);
                 tcgen05_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[j]);
+                if (lane == 0) mbar_arrive(&min_full[i & 1]);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = half * 2 + jj;
+                const int slot = abuf * kPairs + j;
+                const float scale_a = byte_of(sc_word, 2 * jj), scale_b = byte_of(sc_word, 2 * jj + 1);
+                const float fa = wide ? scale_a : scale_a * d, fb = wide ? scale_b : scale_b * d;
+                uint32_t out_lo[16], out_hi[16];
+                unpack_pair<FMT>(blk + kQuantOffset + 32 * j, blk + 16, j, half2_bits(fa, fa), half2_bits(fb, fb), out_lo, out_hi);
+                if (wide) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        out_lo[r] = hmul2(out_lo[r], d2);
+                        out_hi[r] = hmul2(out_hi[r], d2);
+                    }
+                }
+                if (i >= AB && ok && !mbar_wait_bounded(&a_empty[slot], ((i / AB) - 1) & 1)) {
+                    atomicExch(p.status, kDeviceWaitTimeout);
+                    ok = false;
+                }
+                tcgen05_fence_after_sync();
+                tmem_st16(lane_base + slot * kPairColumns, out_lo);
+                tmem_st16(lane_base + slot * kPairColumns + 16, out_hi);
+                tmem_st_wait();
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[slot]);
+            }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[s]);
-            stamp(p, warp, i, 9);
-            if (i > 0) read_back(i - 1, d_prev, dmin_prev);
-            stamp(p, warp, i, 10);
-            d_prev = f16_bits_to_f32(header.x & 0xffffu);
-            dmin_prev = f16_bits_to_f32(header.x >> 16);
+            if (i < 4 && quadrant == 0) stamp(p, 2 + half, 3 + i * 4);
         }
-        if (local_sb > 0) read_back(local_sb - 1, d_prev, dmin_prev);
+        if (quadrant == 0) stamp(p, 2 + half, 20);
 
-        // ---------------- output: columns -> members (plane 1 of member m is column 8 + m) through shared memory ----------------
-        named_barrier_sync(1, kWorkers);   // every raw stage has been read: the ring is free
-        float* tile = reinterpret_cast<float*>(raw);   // [kNT][kRows]
-#pragma unroll
-        for (int c = 0; c < kNT / 2; ++c) tile[(column0 + c) * kRows + row_in_tile] = ok ? acc[c] : 0.0f;
-        named_barrier_sync(1, kWorkers);
+        // ---------------- the accumulators, once: a thread holds its row's columns of this half ----------------
+        pdl_wait_prior();   // the scale factors (and y, when it is accumulated into) come from earlier kernels
+        if (threadIdx.x < NT) up[threadIdx.x] = reinterpret_cast<const float*>(p.image + I::scales_offset(p.nsb))[threadIdx.x];
+        if (ok && !mbar_wait_bounded(d_full, 0)) {
+            atomicExch(p.status, kDeviceWaitTimeout);
+            ok = false;
+        }
+        tcgen05_fence_after_sync();
+        if (quadrant == 0) stamp(p, 2 + half, 21);
+        named_barrier_sync(1, kWorkers);   // the scale factors are in place
         const bool split = p.ksplit > 1;
         float* part = split ? p.partial + static_cast<size_t>(blockIdx.y) * p.members * p.n : nullptr;
-        for (int idx = threadIdx.x; idx < p.members * kRows; idx += kWorkers) {
-            const int m = idx >> 7;
-            const long long row = static_cast<long long>(n0) + (idx & (kRows - 1));
-            if (row < p.n) {
-                float value = tile[m * kRows + (idx & (kRows - 1))];
-                if (p.planes == 2) value += tile[(8 + m) * kRows + (idx & (kRows - 1))];
-                const size_t o = static_cast<size_t>(m) * p.n + row;
-                if (split) {
-                    part[o] = value;
-                } else if (p.y_bf16) {
-                    const float old = p.accumulate ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]) : 0.0f;
-                    static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value + old);
-                } else {
-                    const float old = p.accumulate ? static_cast<const float*>(p.y)[o] : 0.0f;
-                    static_cast<float*>(p.y)[o] = value + old;
+        const long long row = static_cast<long long>(n0) + row_in_tile;
+        const int column0 = half * (NT / 2);
+#pragma unroll
+        for (int c8 = 0; c8 < NT / 16; ++c8) {
+            uint32_t d0[8], d1[8];
+            tmem_ld8(lane_base + P::kColD + column0 + c8 * 8, d0);
+            tmem_ld8(lane_base + P::kColD + NT + column0 + c8 * 8, d1);
+            tmem_ld_wait();
+            float v[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) v[c] = ok ? __uint_as_float(d0[c]) + __uint_as_float(d1[c]) : 0.0f;
+            const int per_member = p.planes;   // columns per member
+#pragma unroll
+            for (int c = 0; c < 8; c += 1) {
+                if (per_member == 2 && (c & 1)) continue;
+                const int column = column0 + c8 * 8 + c;
+                const int m = per_member == 2 ? column >> 1 : column;
+                if (m < p.members && row < p.n) {
+                    const float value = (per_member == 2 ? v[c] + v[c + 1 < 8 ? c + 1 : c] : v[c]) * up[m];
+                    const size_t o = static_cast<size_t>(m) * p.n + row;
+                    if (split) {
+                        part[o] = value;
+                    } else if (p.y_bf16) {
+                        const float old = p.accumulate ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]) : 0.0f;
+                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value + old);
+                    } else {
+                        const float old = p.accumulate ? static_cast<const float*>(p.y)[o] : 0.0f;
+                        static_cast<float*>(p.y)[o] = value + old;
+                    }
                 }
             }
         }
+        tcgen05_fence_before_sync();
+        if (quadrant == 0) stamp(p, 2 + half, 23);
         // ---------------- split-K: the CTA that draws the last ticket of its row tile adds the partial tiles ----------------
         if (split) {
             __threadfence();
@@ -571,19 +714,42 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
             if (*last_flag != 0) {
                 __threadfence();
                 const size_t plane = static_cast<size_t>(p.members) * p.n;
-                for (int idx = threadIdx.x; idx < p.members * kRows; idx += kWorkers) {
-                    const int m = idx >> 7;
-                    const long long row = static_cast<long long>(n0) + (idx & (kRows - 1));
-                    if (row < p.n) {
-                        const size_t o = static_cast<size_t>(m) * p.n + row;
-                        float sum = 0.0f;
-                        for (int z = 0; z < p.ksplit; ++z) sum += __ldcg(p.partial + z * plane + o);
+                const bool vector = (p.n & 3) == 0;
+                for (int idx = threadIdx.x; idx < p.members * (kRows / 4); idx += kWorkers) {
+                    const int m = idx / (kRows / 4);
+                    const long long row = static_cast<long long>(n0) + (idx % (kRows / 4)) * 4;
+                    if (row >= p.n) continue;
+                    const size_t o = static_cast<size_t>(m) * p.n + row;
+                    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (vector) {
+                        int z = 0;
+                        for (; z + 4 <= p.ksplit; z += 4) {   // four loads in flight, added in split order
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.partial + (z + 0) * plane + o));
+                            const float4 b = __ldcg(reinterpret_cast<const float4*>(p.partial + (z + 1) * plane + o));
+                            const float4 c = __ldcg(reinterpret_cast<const float4*>(p.partial + (z + 2) * plane + o));
+                            const float4 e = __ldcg(reinterpret_cast<const float4*>(p.partial + (z + 3) * plane + o));
+                            sum[0] = (((sum[0] + a.x) + b.x) + c.x) + e.x;
+                            sum[1] = (((sum[1] + a.y) + b.y) + c.y) + e.y;
+                            sum[2] = (((sum[2] + a.z) + b.z) + c.z) + e.z;
+                            sum[3] = (((sum[3] + a.w) + b.w) + c.w) + e.w;
+                        }
+                        for (; z < p.ksplit; ++z) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.partial + z * plane + o));
+                            sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
+                        }
+                    } else {
+                        for (int z = 0; z < p.ksplit; ++z)
+                            for (int r = 0; r < 4; ++r)
+                                if (row + r < p.n) sum[r] += __ldcg(p.partial + z * plane + o + r);
+                    }
+                    for (int r = 0; r < 4; ++r) {
+                        if (row + r >= p.n) break;
                         if (p.y_bf16) {
-                            if (p.accumulate) sum += __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]);
-                            static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(sum);
+                            if (p.accumulate) sum[r] += __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o + r]);
+                            static_cast<__nv_bfloat16*>(p.y)[o + r] = __float2bfloat16_rn(sum[r]);
                         } else {
-                            if (p.accumulate) sum += static_cast<const float*>(p.y)[o];
-                            static_cast<float*>(p.y)[o] = sum;
+                            if (p.accumulate) sum[r] += static_cast<const float*>(p.y)[o + r];
+                            static_cast<float*>(p.y)[o + r] = sum[r];
                         }
                     }
                 }
@@ -592,42 +758,62 @@ __global__ void __launch_bounds__(kTmemThreads, 2) qgemv_tmem_kernel(const __gri
     }
 
     // ---------------- teardown: every warp arrives here, then TMEM is released ----------------
+    if (warp == 0) stamp(p, 2, 24);
     tcgen05_fence_before_sync();
     __syncthreads();
-    if (warp == kIssuerWarp) tmem_dealloc(tmem_base, kTmemColumns);
+    if (warp == kIssuerWarp) tmem_dealloc(tmem_base, P::kTmemColumns);
+    if (warp == 0) stamp(p, 2, 25);
 }
 
 constexpr size_t kSmemLimit = 227 * 1024;
 
-// K splits: enough CTAs to fill two per SM, no CTA with more super-blocks than its resident B tiles hold.
-int choose_splits(int tiles, int nsb, int sm_count, int members, size_t scratch_bytes, int n, int max_tickets) {
-    // the largest split count whose CTAs still fit one wave of two per SM; more splits only where a CTA's K range
-    // would not fit its resident B tiles otherwise
-    int ks = (2 * sm_count) / tiles;
-    const int needed = (nsb + kMaxLocalSb - 1) / kMaxLocalSb;
-    if (ks < needed) ks = needed;
-    if (ks > nsb) ks = nsb;
-    if (ks < 1) ks = 1;
-    if (ks > 1 && (static_cast<size_t>(ks) * members * n * sizeof(float) > scratch_bytes || tiles > max_tickets)) return 0;
-    return ks;
+// K splits by a cost model in units of super-blocks: waves of CTAs x (super-blocks per CTA + a fixed cost per CTA).
+int choose_splits(int tiles, int nsb, int ctas_per_wave, int members, size_t scratch_bytes, int n, int max_tickets) {
+    constexpr double kFixedCost = 5.0;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int ks = 1; ks <= nsb && ks <= 32; ++ks) {
+        if (ks > 1 && (static_cast<size_t>(ks) * members * n * sizeof(float) > scratch_bytes || tiles > max_tickets)) break;
+        const int waves = (tiles * ks + ctas_per_wave - 1) / ctas_per_wave;
+        // the last CTA of a row tile reads ks partial tiles of members x 128 floats: about one super-block time per 32 KB
+        const double reduce = ks > 1 ? 1.0 + ks * members * 512.0 / 32768.0 : 0.0;
+        const double cost = waves * ((nsb + ks - 1) / ks + kFixedCost + reduce);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = ks;
+        }
+    }
+    return best;
 }
 
-template <uint32_t FMT>
+template <uint32_t FMT, int NT>
 cudaError_t launch_format(const TmemGemvArgs& a) {
-    using P = TmemPlan<FMT>;
-    auto kernel = qgemv_tmem_kernel<FMT>;
+    using P = TmemPlan<FMT, NT>;
+    using I = typename P::I;
+    auto kernel = qgemv_tmem_kernel<FMT, NT>;
     const int nsb = a.k / kSuperBlock;
     const int tiles = (a.n + kRows - 1) / kRows;
-    int ksplit = choose_splits(tiles, nsb, a.sm_count, a.members, a.scratch_bytes, a.n, a.ticket_count);
-    if (a.force_ksplit > 0 && a.force_ksplit <= nsb && (nsb + a.force_ksplit - 1) / a.force_ksplit <= kMaxLocalSb) ksplit = a.force_ksplit;
-    if (ksplit == 0) return cudaErrorInvalidConfiguration;
-    const int b_sb = (nsb + ksplit - 1) / ksplit;
-    // raw ring: as deep as two CTAs per SM allow (one CTA per SM when the resident B tiles leave less than two stages)
-    int raw_stages = kMaxRawStages;
-    while (raw_stages > 2 && P::smem_bytes(raw_stages, b_sb) > (kSmemLimit - 2048) / 2) --raw_stages;
+    // scratch: [activation image][split-K partial tiles]
+    const size_t image_bytes = (I::bytes(nsb) + 1023) / 1024 * 1024;
+    if (image_bytes > a.scratch_bytes) return cudaErrorInvalidConfiguration;
+    uint8_t* image = static_cast<uint8_t*>(a.scratch);
+    float* partial = reinterpret_cast<float*>(image + image_bytes);
+    const size_t partial_bytes = a.scratch_bytes - image_bytes;
+    // rings: two CTAs per SM for the narrow accumulators, one for 64 columns
+    const int resident = NT >= 64 ? 1 : 2;
+    const size_t budget = (kSmemLimit - 1024 * resident) / resident;
+    int raw_stages = kMaxStages, b_stages = 3;
+    while (P::smem_bytes(raw_stages, b_stages) > budget && (raw_stages > 2 || b_stages > 2)) {
+        if (raw_stages > b_stages || b_stages == 2) --raw_stages;
+        else --b_stages;
+    }
     if (a.stages > 0 && a.stages < raw_stages) raw_stages = a.stages < 2 ? 2 : a.stages;
-    const size_t smem = P::smem_bytes(raw_stages, b_sb);
+    const size_t smem = P::smem_bytes(raw_stages, b_stages);
     if (smem > kSmemLimit) return cudaErrorInvalidConfiguration;
+    int ksplit = choose_splits(tiles, nsb, resident * a.sm_count, a.members, partial_bytes, a.n, a.ticket_count);
+    if (a.force_ksplit > 0 && a.force_ksplit <= nsb && static_cast<size_t>(a.force_ksplit) * a.members * a.n * sizeof(float) <= partial_bytes &&
+        tiles <= a.ticket_count)
+        ksplit = a.force_ksplit;
     static int configured_device = -1;
     int device = 0;
     cudaGetDevice(&device);
@@ -642,7 +828,7 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     CUtensorMap wmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes / 2), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(P::kSbBytes / 2), static_cast<cuuint32_t>(kRows)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(P::kRowPitch / 2), static_cast<cuuint32_t>(kRows)};
     const cuuint32_t elem[2] = {1, 1};
     if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t*>(a.weights), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -653,10 +839,11 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.mode = a.mode;
     p.norm_weight = a.norm_weight;
     p.eps = a.eps;
+    p.image = image;
     p.y = a.y;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
     p.accumulate = a.accumulate ? 1 : 0;
-    p.partial = static_cast<float*>(a.scratch);
+    p.partial = partial;
     p.tickets = a.tickets;
     p.k = a.k;
     p.n = a.n;
@@ -665,24 +852,38 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.planes = a.x_bf16 ? 1 : 2;
     p.ksplit = ksplit;
     p.raw_stages = raw_stages;
-    p.b_sb = b_sb;
-    p.trace = a.trace;
+    p.b_stages = b_stages;
     p.status = a.device_status;
+    p.trace = a.trace;
+    if (!a.image_ready) {
+        const cudaError_t e = launch_kernel(tmem_image_kernel<NT>, dim3(a.members), dim3(256), 0, a.stream, p);
+        if (e != cudaSuccess) return e;
+    }
     return launch_kernel(kernel, dim3(tiles, ksplit), dim3(kTmemThreads), smem, a.stream, wmap, p);
+}
+
+template <uint32_t FMT>
+cudaError_t launch_columns(const TmemGemvArgs& a) {
+    const int columns = a.members * (a.x_bf16 ? 1 : 2);
+    if (columns <= 16) return launch_format<FMT, 16>(a);
+    if (columns <= 32) return launch_format<FMT, 32>(a);
+    return launch_format<FMT, 64>(a);
 }
 
 }  // namespace
 
 bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_bf16, const void* weights) {
-    if (value_type != kQ4_K && value_type != kQ5_K) return false;
-    if (members < 1 || members > (x_bf16 ? 16 : 8) || k <= 0 || k % kSuperBlock != 0 || n < 1) return false;
+    if (value_type != kQ4_K && value_type != kQ5_K && value_type != kQ6_K) return false;
+    if (members < 1 || members > (x_bf16 ? 64 : 32) || k <= 0 || k % kSuperBlock != 0 || n < 1) return false;
+    if (value_type == kQ6_K && (k / kSuperBlock) % 8 != 0) return false;   // rows of 210-byte super-blocks must start on 16-byte boundaries
     return reinterpret_cast<uintptr_t>(weights) % 16 == 0;
 }
 
 cudaError_t launch_qgemv_tmem(const TmemGemvArgs& a) {
     switch (a.value_type) {
-        case kQ4_K: return launch_format<kQ4_K>(a);
-        case kQ5_K: return launch_format<kQ5_K>(a);
+        case kQ4_K: return launch_columns<kQ4_K>(a);
+        case kQ5_K: return launch_columns<kQ5_K>(a);
+        case kQ6_K: return launch_columns<kQ6_K>(a);
         default: return cudaErrorInvalidValue;
     }
 }

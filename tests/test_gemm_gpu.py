@@ -125,8 +125,10 @@ def test_config3_prefill(ctx, vt, n, k, m):
     weight = upload(ctx, vt, w, k, n)
     x = synth.random_activations(m, k, seed=m)
     y, x_seen = run(ctx, weight, x, n, y_dtype=torch.bfloat16)
-    # the f64 host reference over a sample of tokens (every 37th) and all output rows
-    sample = np.arange(0, m, 37)
+    # the f64 host reference over all output rows of a sample of tokens: every 37th, the rows either side of each
+    # 256-token tile boundary, the last token, and one whole token tile (the last 128 tokens)
+    edges = np.array([t for b in range(256, m, 256) for t in (b - 1, b)] + [m - 1])
+    sample = np.unique(np.concatenate([np.arange(0, m, 37), edges, np.arange(m - 128, m)]))
     check(vt, w, k, n, y[sample], x_seen[sample], y_bf16=True)
 
 
