@@ -154,11 +154,11 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
-# DRAM bytes moved per algorithmic byte by the tensor-core decode kernel, from an ncu capture of one launch
-# (dram__bytes_read.sum + dram__bytes_write.sum = 28.53 MB over 28.44 MB of encoded weights, activations and
-# outputs for Q4_K 12288x4096 with 16 member rows; profiles/qgemv_tc_q4k_12288x4096_m16.md).  The kernel reads
+# DRAM bytes moved per algorithmic byte by the batch kernel (weights unpacked into tensor memory), from an ncu capture
+# of one launch (dram__bytes_read.sum + dram__bytes_write.sum = 28.56 MB over 28.44 MB of encoded weights, activations
+# and outputs for Q4_K 12288x4096 with 16 member rows; profiles/qgemv_tmem_q4k_12288x4096_m16.md).  The kernel reads
 # every weight byte once whatever the shape, so the ratio is applied to the sweep's mean call.
-TC_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.003
+TC_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.004
 
 
 def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
@@ -170,7 +170,7 @@ def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
     achieved, us_per_call, bytes_per_call = dominant
     traffic = None if TC_TRAFFIC_PER_ALGORITHMIC_BYTE is None else TC_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_call
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-            "peak_source": source, "kernel": "qgemv_tc_kernel + its activation pre-pass (calls of 16 and 64 member rows)",
+            "peak_source": source, "kernel": "qgemv_tmem_kernel + its activation pre-pass (calls of 16 and 64 member rows)",
             "us_per_call": us_per_call, "algorithmic_bytes_per_call": bytes_per_call,
             "whole_step": {"achieved": step_gbps, "frac": step_gbps / peak, "bytes_per_step": step_bytes}}
 
@@ -216,33 +216,118 @@ def prefill_leg(ctx, device, stream):
     return results
 
 
-def decode_leg(args, ctx, device, rank, world, peak):
-    """Decode tok/s.  One GPU: Qwen3-8B shape, Q4_K_M mix, 2048 tokens of context, 256 generated, batch 1 and 32.
-    Several GPUs: Qwen3-32B shape, tensor parallel over all ranks, 4096 tokens of context, batch 64, all-reduce
-    after o_proj and ffn_down.  Weights are random-init on the device and the context is random KV entries
-    (what a random-token prompt leaves in the cache)."""
+def time_decode(decoder, generated, world, device, stream):
+    """Replays the captured step `generated - 3` times after three warm-up replays; device time, max over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    for _ in range(3):
+        decoder.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(generated - 3):
+        decoder.replay()
+    b.record(stream)
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def decode_entry(decoder, geometry, weights, members, context_tokens, generated, ms, peak, world, data):
+    steps = generated - 3
+    step_ms = ms / steps
+    weight_bytes = weights.bytes_per_step()   # this rank's shard
+    kv_bytes = geometry.layers * members * decoder.shapes["kv_heads"] * geometry.head_dim * 2 * 2 * (context_tokens + generated // 2)
+    return {
+        "tokens_per_s": members * steps / (ms * 1e-3), "ms_per_token_step": step_ms, "members": members,
+        "context": context_tokens, "generated": generated, "layers": geometry.layers, "launches_per_step": decoder.launches_per_step,
+        "weight_bytes_per_step_per_gpu": weight_bytes, "kv_bytes_per_step_per_gpu": kv_bytes,
+        "hbm_GBps_per_gpu": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9,
+        "hbm_frac_of_peak": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / peak,
+        "data": data, "n_gpus": world,
+    }
+
+
+def tp_parity_leg(ctx, rank, world, link_factory):
+    """Two layers of a reduced geometry, weights generated on the host and cut with engine_b200/sharding.py: the
+    tensor-parallel decoder (exchanges over peer memory) against the unsharded decoder on rank 0, five steps."""
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     from engine_b200 import decode
 
+    geometry = decode.DenseGeometry(hidden=1024, layers=2, q_heads=8, kv_heads=8, head_dim=128, intermediate=2048, vocabulary=4096)
+    members = 4
+    tensors, vectors = decode.host_model(geometry, seed=3)
+    out = {}
+    for label, partial_dtype in (("f32_partials", torch.float32), ("bf16_partials", torch.bfloat16)):
+        link = link_factory(members * geometry.hidden * 4)
+        sharded = decode.CudaDenseDecode(ctx, geometry, decode.shard_host_model(ctx, geometry, tensors, vectors, world, rank), members, 32,
+                                         process_group=dist.group.WORLD, world=world, rank=rank, peer_link=link, partial_dtype=partial_dtype)
+        single = decode.CudaDenseDecode(ctx, geometry, decode.shard_host_model(ctx, geometry, tensors, vectors, 1, 0), members, 32) if rank == 0 else None
+        tokens = torch.tensor([(17 * m + 3) % geometry.vocabulary for m in range(members)], dtype=torch.int32)
+        worst, equal, compared = 0.0, 0, 0
+        for decoder in (sharded, single):
+            if decoder is not None:
+                decoder.tokens.copy_(tokens)
+        for _ in range(5):
+            sharded.run_step()
+            ctx.synchronize()
+            slices = [torch.empty(members, decode.local_shapes(geometry, world, r)["vocab_end"] - decode.local_shapes(geometry, world, r)["vocab_begin"],
+                                  device=ctx.device) for r in range(world)]
+            dist.all_gather(slices, sharded.logits)
+            following = torch.empty(members, dtype=torch.int32, device=ctx.device)
+            if rank == 0:
+                single.run_step()
+                ctx.synchronize()
+                full, got = single.logits.cpu().numpy(), torch.cat(slices, dim=1).cpu().numpy()
+                worst = max(worst, float(np.max(np.abs(got - full)) / np.abs(full).max()))
+                equal += int((sharded.next_tokens == single.next_tokens).sum().item())
+                compared += members
+                following.copy_(single.next_tokens)
+            dist.broadcast(following, src=0)
+            for decoder in (sharded, single):
+                if decoder is not None:
+                    decoder.tokens.copy_(following)
+                    decoder.positions.add_(1)
+            torch.cuda.synchronize()
+        out[label] = {"logits_max_rel_err": worst, "tokens_equal": equal, "tokens_compared": compared}
+        del sharded, single
+        torch.cuda.synchronize()
+        dist.barrier()
+        link.close()
+    out["geometry"] = "hidden 1024, 2 layers, 8 heads, intermediate 2048, vocabulary 4096; 4 sequences, 5 steps"
+    return out
+
+
+def decode_leg(args, ctx, device, rank, world, peak):
+    """Decode tok/s.  One GPU: Qwen3-8B shape, Q4_K_M mix, 2048 tokens of context, 256 generated, batch 1 and 32, and
+    the Qwen3-32B shape at batch 64 with 4096 tokens of context (the one-GPU point of the tensor-parallel curve).
+    Several GPUs: the Qwen3-32B shape tensor parallel over all ranks, once with the exchanges over peer memory
+    (ribn_tp_*: one kernel per exchange) and once with NCCL all-reduces, each also with the exchanges left out of the
+    captured step to show their share of it.  Weights are random-init on the device; the one-GPU 8B contexts are real
+    prompts run through the prefill path, the 32B contexts random KV entries (what a random prompt leaves behind)."""
+    import torch
+    import torch.distributed as dist
+
+    from engine_b200 import decode, tp
+
     results = {}
     generated = 256
-    if world == 1:
-        geometry = decode.DenseGeometry.qwen3_8b(args.decode_layers or 36)
-        plans = [("qwen3_8b_batch1", 1, 2048), ("qwen3_8b_batch32", 32, 2048)]
-        group = None
-    else:
-        geometry = decode.DenseGeometry.qwen3_32b(args.decode_layers or 64)
-        plans = [(f"qwen3_32b_tp{world}_batch64", 64, 4096)]
-        group = dist.group.WORLD
     try:
-        weights = decode.random_weights(ctx, geometry, seed=1, world=world, rank=rank)
-        for name, members, context_tokens in plans:
-            decoder = decode.CudaDenseDecode(ctx, geometry, weights, members, context_tokens + generated + 8, process_group=group,
-                                             world=world, rank=rank)
-            prefill = None
-            if world == 1:
+        if world == 1:
+            geometry = decode.DenseGeometry.qwen3_8b(args.decode_layers or 36)
+            weights = decode.random_weights(ctx, geometry, seed=1)
+            for name, members, context_tokens in [("qwen3_8b_batch1", 1, 2048), ("qwen3_8b_batch32", 32, 2048)]:
+                decoder = decode.CudaDenseDecode(ctx, geometry, weights, members, context_tokens + generated + 8)
                 # the context is a real prompt: random tokens through the prefill path (tensor-core GEMM, shared-cache
                 # attention), which leaves the KV entries and the first generated token of every sequence
                 prompt_generator = torch.Generator(device="cpu")
@@ -257,52 +342,89 @@ def decode_leg(args, ctx, device, rank, world, peak):
                 b.record(ctx.stream)
                 ctx.synchronize()
                 prefill_ms = a.elapsed_time(b)
-                prefill = {"tokens_per_s": members * context_tokens / (prefill_ms * 1e-3), "ms": prefill_ms, "chunk": 512,
-                           "prompt_tokens": members * context_tokens}
                 decoder.capture(advance=True)            # its eager step writes slot `context_tokens` again and advances nothing
-            else:
-                decoder.fill_context(context_tokens)
+                ms = time_decode(decoder, generated, 1, device, ctx.stream)
+                results[name] = decode_entry(decoder, geometry, weights, members, context_tokens, generated, ms, peak, 1,
+                                             "random-init weights (Q4_K_M mix), context prefilled from random prompt tokens, greedy decoding")
+                results[name]["prefill"] = {"tokens_per_s": members * context_tokens / (prefill_ms * 1e-3), "ms": prefill_ms, "chunk": 512,
+                                            "prompt_tokens": members * context_tokens}
+                del decoder
+                torch.cuda.empty_cache()
+            results["reference_cuda_decode"] = reference_decode_leg(ctx, geometry, weights, device)
+            del weights
+            torch.cuda.empty_cache()
+        # ---- the Qwen3-32B shape at batch 64 x 4096: every rank count runs it, so that the curve has its one-GPU point
+        geometry = decode.DenseGeometry.qwen3_32b(args.decode_layers or 64)
+        members, context_tokens, steps32 = 64, 4096, 67
+        data32 = "random-init weights (Q4_K_M mix), random KV context, greedy decoding"
+        group = dist.group.WORLD if world > 1 else None
+        weights = decode.random_weights(ctx, geometry, seed=1, world=world, rank=rank)
+        name = f"qwen3_32b_tp{world}_batch64"
+        paths = [("peer_memory", True)] + ([("nccl", False)] if world > 1 else [])
+        for label, fused in (paths if world > 1 else [("single", False)]):
+            link = None
+            if fused:
+                link = tp.PeerLink(ctx, rank, world, members * geometry.hidden * 4)
+                link.connect_group(group)
+            decoder = decode.CudaDenseDecode(ctx, geometry, weights, members, context_tokens + generated + 8, process_group=group, world=world, rank=rank,
+                                             peer_link=link, partial_dtype=torch.bfloat16)
+            decoder.fill_context(context_tokens)
+            decoder.capture(advance=True)
+            decoder.fill_context(context_tokens)   # the eager step inside capture() advanced nothing but wrote one cache slot
+            ms = time_decode(decoder, steps32, world, device, ctx.stream)
+            entry = decode_entry(decoder, geometry, weights, members, context_tokens, steps32, ms, peak, world, data32)
+            if world > 1:
+                # the same step captured without its exchanges: what is left is GEMVs, attention and elementwise launches
+                decoder.skip_exchange = True
                 decoder.capture(advance=True)
-                decoder.fill_context(context_tokens)   # the eager step inside capture() advanced nothing but wrote one cache slot
-            for _ in range(3):
-                decoder.replay()
+                decoder.fill_context(context_tokens)
+                bare = time_decode(decoder, steps32, world, device, ctx.stream)
+                decoder.skip_exchange = False
+                entry["ms_per_step_without_exchanges"] = bare / (steps32 - 3)
+                entry["exchange_share_of_step"] = 1.0 - bare / ms
+                entry["exchanges_per_step"] = 2 * geometry.layers
+                entry["exchange"] = ("one kernel per exchange over peer memory (bf16 partials, residual folded in), token choice in one kernel"
+                                     if fused else "ncclAllReduce of f32 partials + residual_add, token choice by all-gathers")
+            results[name if label in ("peer_memory", "single") else f"{name}_{label}"] = entry
+            del decoder
+            torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(ctx.stream)
-            for _ in range(generated - 3):
-                decoder.replay()
-            b.record(ctx.stream)
-            torch.cuda.synchronize()
-            ms = a.elapsed_time(b)
-            if world > 1:
-                t = torch.tensor([ms], device=device)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-            steps = generated - 3
-            step_ms = ms / steps
-            weight_bytes = weights.bytes_per_step()   # this rank's shard
-            shapes = decoder.shapes
-            kv_bytes = geometry.layers * members * shapes["kv_heads"] * geometry.head_dim * 2 * 2 * (context_tokens + generated // 2)
-            results[name] = {
-                "tokens_per_s": members * steps / (ms * 1e-3), "ms_per_token_step": step_ms, "members": members,
-                "context": context_tokens, "generated": generated, "layers": geometry.layers, "launches_per_step": decoder.launches_per_step,
-                "weight_bytes_per_step_per_gpu": weight_bytes, "kv_bytes_per_step_per_gpu": kv_bytes,
-                "hbm_GBps_per_gpu": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9,
-                "hbm_frac_of_peak": (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / peak,
-                "data": "random-init weights (Q4_K_M mix), " + ("context prefilled from random prompt tokens" if prefill else "random KV context")
-                        + ", greedy decoding", "n_gpus": world,
-            }
-            if prefill:
-                results[name]["prefill"] = prefill
-            del decoder
+            if link is not None:
+                link.close()
             torch.cuda.empty_cache()
-        if world == 1:
-            results["reference_cuda_decode"] = reference_decode_leg(ctx, geometry, weights, device)
+        if world > 1:
+            results["tp_parity"] = tp_parity_leg(ctx, rank, world, lambda slot: _connected_link(ctx, rank, world, slot, group))
+            # the one-GPU point, measured in this very run on every rank's own GPU (no communication): rank 0's figure
+            del weights
+            torch.cuda.empty_cache()
+            solo_weights = decode.random_weights(ctx, geometry, seed=1)
+            solo = decode.CudaDenseDecode(ctx, geometry, solo_weights, members, context_tokens + generated + 8)
+            solo.fill_context(context_tokens)
+            solo.capture(advance=True)
+            solo.fill_context(context_tokens)
+            ms = time_decode(solo, 35, 1, device, ctx.stream)
+            one = decode_entry(solo, geometry, solo_weights, members, context_tokens, 35, ms, peak, 1, data32)
+            results["qwen3_32b_tp1_batch64"] = one
+            results["tp_efficiency"] = {"tokens_per_s": results[name]["tokens_per_s"], "tp1_tokens_per_s": one["tokens_per_s"],
+                                        "speedup": results[name]["tokens_per_s"] / one["tokens_per_s"],
+                                        "efficiency": results[name]["tokens_per_s"] / one["tokens_per_s"] / world, "n_gpus": world}
+            del solo, solo_weights
+            torch.cuda.empty_cache()
     except Exception as exc:   # the sweep line must still be printed
+        import traceback
+
         results["error"] = f"{type(exc).__name__}: {exc}"
+        results["traceback"] = traceback.format_exc()[-1500:]
     return results
+
+
+def _connected_link(ctx, rank, world, slot_bytes, group):
+    from engine_b200 import tp
+
+    link = tp.PeerLink(ctx, rank, world, slot_bytes)
+    link.connect_group(group)
+    return link
 
 
 def reference_decode_leg(ctx, geometry, weights, device):
@@ -841,6 +963,17 @@ def main() -> None:
             line["reference_cuda"] = reference_cuda
         if decode_results is not None:
             line["decode"] = decode_results
+            # the tensor-parallel curve, at the top level: tok/s of the Qwen3-32B shape on this many GPUs (strong scaling:
+            # one model, one batch) and, from two GPUs on, its ratio to the one-GPU point measured in the same run
+            key = f"qwen3_32b_tp{world}_batch64"
+            if key in decode_results:
+                line["tp"] = {"metric": "decode_tokens_per_s", "model": "Qwen3-32B shape, Q4_K_M mix, batch 64, 4096 context", "n_gpus": world,
+                              "scaling": "strong", "tokens_per_s": decode_results[key]["tokens_per_s"],
+                              "exchange_share_of_step": decode_results[key].get("exchange_share_of_step"),
+                              "nccl_tokens_per_s": decode_results.get(key + "_nccl", {}).get("tokens_per_s"),
+                              "tp1_tokens_per_s": decode_results.get("tp_efficiency", {}).get("tp1_tokens_per_s"),
+                              "efficiency": decode_results.get("tp_efficiency", {}).get("efficiency"),
+                              "parity": decode_results.get("tp_parity")}
         if prefill_results is not None:
             line["prefill"] = prefill_results
         if cpu_baseline is not None:

@@ -134,6 +134,17 @@ SIGNATURES = {
     "ribn_silu_mul_typed": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64]),
     "ribn_residual_add": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_uint64]),
     "ribn_argmax": (ctypes.c_int, [_vp, _vp, ctypes.c_uint32, ctypes.c_uint64, _vp]),
+    "ribn_tp_create": (ctypes.c_int, [_vp, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint64, _vp, ctypes.POINTER(_vp)]),
+    "ribn_tp_destroy": (None, [_vp]),
+    "ribn_tp_last_error": (ctypes.c_char_p, [_vp]),
+    "ribn_tp_block_bytes": (ctypes.c_uint64, [ctypes.c_uint64]),
+    "ribn_tp_export": (ctypes.c_int, [_vp, _vp]),
+    "ribn_tp_connect": (ctypes.c_int, [_vp, _vp]),
+    "ribn_tp_connect_pointers": (ctypes.c_int, [_vp, ctypes.POINTER(_vp)]),
+    "ribn_tp_set_wait": (ctypes.c_int, [_vp, ctypes.c_uint64]),
+    "ribn_tp_partial": (ctypes.c_int, [_vp, ctypes.c_uint32, ctypes.POINTER(_vp)]),
+    "ribn_tp_allreduce_residual": (ctypes.c_int, [_vp, _vp, ctypes.c_uint32, _vp, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int]),
+    "ribn_tp_select_tokens": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint32, _vp]),
     "ribn_context_stream": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(_vp)]),
     "ribn_gguf_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "ribn_gguf_close": (None, [_vp]),

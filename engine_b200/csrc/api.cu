@@ -48,6 +48,15 @@ struct ribn_ctx {
     uint64_t expected = 0, actual = 0;
 };
 
+namespace ribn {
+void context_internals(const ribn_ctx* ctx, int* device, void** stream, int* sm_count, int** status) {
+    *device = ctx->device;
+    *stream = ctx->stream;
+    *sm_count = ctx->sm_count;
+    *status = ctx->device_status;
+}
+}  // namespace ribn
+
 namespace {
 
 using ribn::GemvArgs;

@@ -189,6 +189,12 @@ cudaError_t launch_qgemv_tc(const TcArgs& args);
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);
 
+// What the tensor-parallel exchange (tp.cu) needs of a context: its device, stream, SM count and status word.
+}  // namespace ribn
+struct ribn_ctx;
+namespace ribn {
+void context_internals(const ribn_ctx* ctx, int* device, void** stream, int* sm_count, int** status);
+
 // The reference's Q8_1 activation format and the integer-dot GEMV over it (q8_1.cu).
 cudaError_t launch_quantize_q8_1(const float* input, uint32_t* output, uint64_t blocks, int sm_count, cudaStream_t stream);
 cudaError_t launch_gemv_q8_1(uint32_t value_type, const uint8_t* weights, const uint32_t* packed, float* output, int k, int n, int members,

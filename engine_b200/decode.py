@@ -174,6 +174,62 @@ def random_weights(context: RibnContext, geometry: DenseGeometry, seed: int = 0,
     return weights
 
 
+def host_model(geometry: DenseGeometry, seed: int = 0):
+    """Full (unsharded) encoded tensors and norm vectors generated on the host with numpy, so that every rank of a
+    tensor-parallel run -- and the single-GPU run it is compared with -- starts from the same bytes.
+    Returns ({name: (value_type, K, N, bytes)}, {name: float32 vector}); gate and up are separate tensors here."""
+    import numpy as np
+
+    shapes = local_shapes(geometry, 1, 0)
+    rng = np.random.default_rng(seed)
+    tensors, vectors = {}, {}
+    kinds = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+    for name, kind, salt in [("token_embd", "token_embd", 1), ("output", "output", 2)] + [
+            (f"blk.{i}.{kind}", kind, 10 + 8 * i + j) for i in range(geometry.layers) for j, kind in enumerate(kinds)]:
+        k, n = shapes[kind]
+        tensors[name] = (VALUE_TYPES[kind], k, n, synth.random_weight(VALUE_TYPES[kind], k, n, seed=seed * 100 + salt))
+    for name, length in [("output_norm", geometry.hidden)] + [(f"blk.{i}.{v}", n) for i in range(geometry.layers)
+                                                              for v, n in (("attn_norm", geometry.hidden), ("ffn_norm", geometry.hidden),
+                                                                           ("attn_q_norm", geometry.head_dim), ("attn_k_norm", geometry.head_dim))]:
+        vectors[name] = (1 + 0.02 * rng.standard_normal(length)).astype(np.float32)
+    return tensors, vectors
+
+
+def shard_host_model(context: RibnContext, geometry: DenseGeometry, tensors: dict, vectors: dict, world: int, rank: int) -> DenseWeights:
+    """Rank `rank`'s shard of a host_model, uploaded: q/k/v by whole heads, the output head by rows, o_proj and ffn_down by
+    input super-blocks, gate and up by rows of whole super-blocks and stored as one [gate | up] matrix (sharding.py)."""
+    import numpy as np
+
+    from . import sharding
+
+    weights = DenseWeights()
+
+    def put(name, vt, k, n, data):
+        weights.matrices[name] = CudaQuantizedWeight(WeightTensorSpec.new(name, [k, n]), vt, torch.from_numpy(np.ascontiguousarray(data)).to(context.device))
+
+    for name, (vt, k, n, data) in tensors.items():
+        kind = name.split(".")[-1]
+        if kind == "token_embd":
+            put(name, vt, k, n, data)
+        elif kind in ("attn_q", "attn_k", "attn_v"):
+            part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank, multiple=geometry.head_dim)
+            put(name, vt, kk, nn, part)
+        elif kind == "output":
+            part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank)
+            put(name, vt, kk, nn, part)
+        elif kind in ("attn_output", "ffn_down"):
+            part, (kk, nn), _ = sharding.shard_k(data, vt, k, n, world, rank)
+            put(name, vt, kk, nn, part)
+        elif kind == "ffn_gate":
+            up_vt, _, _, up = tensors[name.replace("ffn_gate", "ffn_up")]
+            gate_part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank, multiple=256)
+            up_part, _ = sharding.shard_rows(up, up_vt, k, n, world, rank, multiple=256)
+            put(name.replace("ffn_gate", "ffn_gate_up"), vt, kk, 2 * nn, np.concatenate([gate_part, up_part]))
+    for name, v in vectors.items():
+        weights.vectors[name] = torch.from_numpy(v).to(context.device)
+    return weights
+
+
 class CudaDenseDecode:
     """One decode step for `members` sequences (one new token each), replayable as a CUDA graph.
 
@@ -181,9 +237,13 @@ class CudaDenseDecode:
     must then be that rank's shard (see local_shapes)."""
 
     def __init__(self, context: RibnContext, geometry: DenseGeometry, weights: DenseWeights, members: int, max_context: int,
-                 process_group=None, world: int = 1, rank: int = 0):
+                 process_group=None, world: int = 1, rank: int = 0, peer_link=None, partial_dtype: torch.dtype = torch.float32):
         self.context, self.geometry, self.weights, self.members, self.max_context = context, geometry, weights, members, max_context
         self.group, self.world, self.rank = process_group, world, rank
+        # peer_link (engine_b200.tp.PeerLink, connected): the sums after o_proj / ffn_down and the token choice run as
+        # one kernel each over peer memory instead of NCCL collectives plus elementwise launches
+        self.link, self.partial_dtype = peer_link, partial_dtype
+        self.skip_exchange = False   # timing aid: leave the exchanges out of a captured step (results are then wrong)
         self.shapes = local_shapes(geometry, world, rank)
         self.ops = CudaDenseOps(context)
         self.kernels = {vt: QwenGemvKernel.from_value_type(vt, context) for vt in (Q4_K, Q6_K)}
@@ -233,8 +293,14 @@ class CudaDenseDecode:
         self.launches_per_step += len(jobs) + (1 if prepass else 0)
 
     def _all_reduce(self, t: torch.Tensor) -> None:
-        torch.distributed.all_reduce(t, group=self.group)
-        self.launches_per_step += 1
+        if not self.skip_exchange:
+            torch.distributed.all_reduce(t, group=self.group)
+            self.launches_per_step += 1
+
+    def _exchange(self, slot: int) -> None:
+        if not self.skip_exchange:
+            self.link.allreduce_residual(slot, self.hidden, self.members, self.geometry.hidden, self.partial_dtype)
+            self.launches_per_step += 1
 
     def _layer(self, i: int) -> None:
         g, s, w = self.geometry, self.shapes, self.weights
@@ -252,7 +318,11 @@ class CudaDenseDecode:
         self.ops.qk_norm_rope_append(attention, self.q, self.k, self.v)
         self.ops.attention_decode(attention, self.q, self.attended)
         self.launches_per_step += 3   # head norm + rope + cache append; split-KV attention; merge of the splits
-        if parallel:
+        if parallel and self.link is not None:
+            # partial sums of the column-split projection go straight into the link's slot; one kernel pulls the peers'
+            self._fused([(f"blk.{i}.attn_output", self.link.partial(0, self.members, g.hidden, self.partial_dtype))], self.attended)
+            self._exchange(0)
+        elif parallel:
             # partial sums of the column-split projection: all-reduce, then the residual
             self._fused([(f"blk.{i}.attn_output", self.projected)], self.attended)
             self._all_reduce(self.projected)
@@ -261,7 +331,10 @@ class CudaDenseDecode:
         else:
             self._fused([(f"blk.{i}.attn_output", self.hidden)], self.attended, accumulate=True)      # hidden += W attended
         self._fused([(f"blk.{i}.ffn_gate_up", self.gate_up)], self.hidden, norm=w.vectors[f"blk.{i}.ffn_norm"])
-        if parallel:
+        if parallel and self.link is not None:
+            self._fused([(f"blk.{i}.ffn_down", self.link.partial(1, self.members, g.hidden, self.partial_dtype))], self.gate_up, swiglu=True)
+            self._exchange(1)
+        elif parallel:
             self._fused([(f"blk.{i}.ffn_down", self.projected)], self.gate_up, swiglu=True)
             self._all_reduce(self.projected)
             self.ops.residual_add(self.hidden, self.projected)
@@ -285,6 +358,10 @@ class CudaDenseDecode:
         logits = self.logits if logits is None else logits
         out = self.next_tokens if out is None else out
         rows = logits.shape[0]
+        if self.link is not None and out.data_ptr() % 16 == 0 and logits.data_ptr() % 16 == 0:
+            self.link.select_tokens(logits, rows, self.shapes["vocab_begin"], out)
+            self.launches_per_step += 1
+            return
         local = torch.empty(rows, dtype=torch.int32, device=self.context.device)
         self.ops.argmax(logits, rows, local)
         values = logits.gather(1, local.long().unsqueeze(1)).squeeze(1)
@@ -293,7 +370,10 @@ class CudaDenseDecode:
         torch.distributed.all_gather(gathered_values, values, group=self.group)
         torch.distributed.all_gather(gathered_indices, local + self.shapes["vocab_begin"], group=self.group)
         all_values = torch.stack(gathered_values)            # [world][members]
-        best = all_values.argmax(dim=0)                        # first rank wins ties: the lowest index
+        # the rules of ribn_argmax across ranks: NaN never wins (a rank whose slice is all NaN reports its first index with
+        # a NaN value), and argmax returns the first of equal maxima, i.e. the lowest rank = the lowest token index
+        all_values = torch.where(torch.isnan(all_values), torch.full_like(all_values, float("-inf")), all_values)
+        best = all_values.argmax(dim=0)
         out.copy_(torch.stack(gathered_indices).gather(0, best.unsqueeze(0)).squeeze(0))
 
     # -- prefill ------------------------------------------------------------------------------------

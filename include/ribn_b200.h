@@ -347,6 +347,45 @@ int ribn_materialize_quantized(ribn_ctx* ctx, ribn_gguf* file, const char* name,
 /* The device and the stream a context was created on. */
 int ribn_context_stream(const ribn_ctx* ctx, int* device, void** cuda_stream);
 
+/* ---- tensor-parallel exchange over peer memory --------------------------------------------------
+ * The reference runs on one GPU.  With the weights sharded over `world` GPUs of one node (output rows of q/k/v, gate/up
+ * and the output head; input columns of o_proj and ffn_down), two steps of a decode layer need the other ranks:
+ * the sum of the column-split projections' partial outputs, and the choice of the next token from per-rank slices of
+ * the logits.  Both run as one kernel per rank over memory the peers map: no collective library is called.
+ *
+ * Every rank creates a link (a block of device memory: two partial slots of slot_bytes plus 4 KiB of flags), hands its
+ * 64-byte handle to the peers over any host channel, and connects.  ribn_tp_partial(slot) is where this rank's GEMV
+ * writes its partial [members][length] (f32 or bf16); consecutive exchanges must alternate slots 0 and 1.  Waits on
+ * peers are bounded (ribn_tp_set_wait, default 1 s): a peer that never arrives makes ribn_synchronize return
+ * RIBN_E_TIMEOUT; the GPU is not left waiting.
+ *
+ * Block layout (part of the contract between ranks; all words little-endian u32): [slot 0][slot 1] then, at byte
+ * 2 * slot_bytes: flags[16] (flags[p] = number of the last exchange rank p has published here), select_flags[16] (the
+ * same for token selection), pairs[2][64][2] (this rank's best (ordered key of the value, token) per member, generation
+ * = exchange number & 1), then words private to the rank. */
+typedef struct ribn_tp ribn_tp;
+#define RIBN_TP_HANDLE_BYTES 64
+/* local_block NULL: the link allocates its block (exportable).  Otherwise the caller's memory of
+ * ribn_tp_block_bytes(slot_bytes), 256-byte aligned, zeroed by this call; such links connect by pointers. */
+int ribn_tp_create(ribn_ctx* ctx, uint32_t rank, uint32_t world, uint64_t slot_bytes, void* local_block, ribn_tp** out);
+void ribn_tp_destroy(ribn_tp* tp);
+const char* ribn_tp_last_error(const ribn_tp* tp);
+uint64_t ribn_tp_block_bytes(uint64_t slot_bytes);
+int ribn_tp_export(ribn_tp* tp, void* handle_out /* RIBN_TP_HANDLE_BYTES */);
+int ribn_tp_connect(ribn_tp* tp, const void* handles /* [world][RIBN_TP_HANDLE_BYTES], own entry ignored */);
+/* Peers in the same process (peer access enabled by the caller): their blocks' device pointers, own entry ignored. */
+int ribn_tp_connect_pointers(ribn_tp* tp, void* const* blocks);
+int ribn_tp_set_wait(ribn_tp* tp, uint64_t microseconds);
+int ribn_tp_partial(ribn_tp* tp, uint32_t slot, void** device_pointer);
+/* hidden[m][i] += sum over ranks, in rank order, of their partials in `slot`; every rank ends with identical bits.
+ * Replaces the all-reduce and the residual_add (model_ops.rs:600-610) behind o_proj and ffn_down. */
+int ribn_tp_allreduce_residual(ribn_ctx* ctx, ribn_tp* tp, uint32_t slot, float* hidden_device, uint32_t members, uint64_t length,
+                               int partial_dtype);
+/* argmax / argmax_batch (model_ops.rs:201-314) over a vocabulary split by rows across the ranks: logits_device is this
+ * rank's [members][length] slice, whose first column is token index_base.  NaN never wins, ties go to the lowest token. */
+int ribn_tp_select_tokens(ribn_ctx* ctx, ribn_tp* tp, const float* logits_device, uint32_t members, uint64_t length,
+                          uint32_t index_base, uint32_t* tokens_device);
+
 /* ---- the reference's Q8_1 activation format (compatibility mode) ------------------------------
  * CudaQ8_1Quantizer::execute (crates/nvidia/src/activation.rs:15-88 over activation.cu:3-28): every block of 32
  * floats becomes nine words -- half(max|x|/127) | half(sum x) << 16, then 32 signed bytes round(x / scale).  The

@@ -18,54 +18,18 @@ GEOMETRY = dict(hidden=512, layers=2, q_heads=4, kv_heads=2, head_dim=128, inter
 
 
 def encoded_model(seed):
-    """Full encoded tensors (numpy bytes) and norm vectors, generated on the host so that every rank sees the same."""
-    from engine_b200 import decode, synth
+    from engine_b200 import decode
     g = decode.DenseGeometry(**GEOMETRY)
-    shapes = decode.local_shapes(g, 1, 0)
-    rng = np.random.default_rng(seed)
-    tensors, vectors = {}, {}
-    kinds = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
-    for name, kind, salt in [("token_embd", "token_embd", 1), ("output", "output", 2)] + [
-            (f"blk.{i}.{kind}", kind, 10 + 8 * i + j) for i in range(g.layers) for j, kind in enumerate(kinds)]:
-        k, n = shapes[kind]
-        tensors[name] = (decode.VALUE_TYPES[kind], k, n, synth.random_weight(decode.VALUE_TYPES[kind], k, n, seed=seed * 100 + salt))
-    for name, length in [("output_norm", g.hidden)] + [(f"blk.{i}.{v}", n) for i in range(g.layers)
-                                                      for v, n in (("attn_norm", g.hidden), ("ffn_norm", g.hidden),
-                                                                   ("attn_q_norm", g.head_dim), ("attn_k_norm", g.head_dim))]:
-        vectors[name] = (1 + 0.02 * rng.standard_normal(length)).astype(np.float32)
+    tensors, vectors = decode.host_model(g, seed)
     return g, tensors, vectors
 
 
 def shard_weights(context, g, tensors, vectors, world, rank):
-    import engine_b200
-    from engine_b200 import decode, sharding
-    weights = decode.DenseWeights()
-    put = lambda name, vt, k, n, data: weights.matrices.__setitem__(
-        name, engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new(name, [k, n]), vt, torch.from_numpy(np.ascontiguousarray(data)).to(context.device)))
-    for name, (vt, k, n, data) in tensors.items():
-        kind = name.split(".")[-1]
-        if kind == "token_embd":
-            put(name, vt, k, n, data)
-        elif kind in ("attn_q", "attn_k", "attn_v"):
-            part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank, multiple=g.head_dim)
-            put(name, vt, kk, nn, part)
-        elif kind == "output":
-            part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank)
-            put(name, vt, kk, nn, part)
-        elif kind in ("attn_output", "ffn_down"):
-            part, (kk, nn), _ = sharding.shard_k(data, vt, k, n, world, rank)
-            put(name, vt, kk, nn, part)
-        elif kind == "ffn_gate":
-            up_vt, _, _, up = tensors[name.replace("ffn_gate", "ffn_up")]
-            gate_part, (kk, nn) = sharding.shard_rows(data, vt, k, n, world, rank, multiple=256)
-            up_part, _ = sharding.shard_rows(up, up_vt, k, n, world, rank, multiple=256)
-            put(name.replace("ffn_gate", "ffn_gate_up"), vt, kk, 2 * nn, np.concatenate([gate_part, up_part]))
-    for name, v in vectors.items():
-        weights.vectors[name] = torch.from_numpy(v).to(context.device)
-    return weights
+    from engine_b200 import decode
+    return decode.shard_host_model(context, g, tensors, vectors, world, rank)
 
 
-def _rank_main(rank, world, port, members, queue):
+def _rank_main(rank, world, port, members, queue, path="nccl"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
 
@@ -76,8 +40,15 @@ def _rank_main(rank, world, port, members, queue):
     try:
         g, tensors, vectors = encoded_model(seed=members)
         context = engine_b200.RibnContext(rank, stream=torch.cuda.Stream(device=rank))
+        link, partial_dtype = None, torch.float32
+        if path != "nccl":
+            # the exchanges over peer memory: one kernel per rank instead of an NCCL all-reduce plus a residual_add
+            from engine_b200 import tp
+            partial_dtype = torch.bfloat16 if path == "link-bf16" else torch.float32
+            link = tp.PeerLink(context, rank, world, members * g.hidden * 4)
+            link.connect_group(dist.group.WORLD)
         sharded = decode.CudaDenseDecode(context, g, shard_weights(context, g, tensors, vectors, world, rank), members, 64,
-                                         process_group=dist.group.WORLD, world=world, rank=rank)
+                                         process_group=dist.group.WORLD, world=world, rank=rank, peer_link=link, partial_dtype=partial_dtype)
         single = None
         if rank == 0:
             single = decode.CudaDenseDecode(context, g, shard_weights(context, g, tensors, vectors, 1, 0), members, 64)
@@ -123,6 +94,9 @@ def _rank_main(rank, world, port, members, queue):
         # Release the captured graph (it holds NCCL kernels) before the communicator goes away.
         del sharded, single
         torch.cuda.synchronize()
+        dist.barrier()      # nobody unmaps a block a peer's kernel may still read
+        if link is not None:
+            link.close()
         context.close()
     finally:
         dist.destroy_process_group()
@@ -134,15 +108,16 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("path", ["nccl", "link-f32", "link-bf16"])
 @pytest.mark.parametrize("members", [2, 6])
-def test_two_gpus_decode_like_one(members):
+def test_two_gpus_decode_like_one(members, path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, members, queue)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, members, queue, path)) for r in range(2)]
     for p in procs:
         p.start()
     result = queue.get(timeout=240)      # rank 0 reports before teardown; a stuck rank must not hold the suite
