@@ -134,15 +134,47 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(float* __restr
 }
 
 // ---------------------------------------------------------------- attention, one new token per member
-// Split-KV ("flash decoding"): grid (kv_heads, members, splits); warp w of the CTA owns query head
-// kv_head * group + w.  The CTA walks its token range in tiles of 32: the K and V tiles go through shared
-// memory once for the whole group; lane = token for the scores, lane = 4 output dims for P.V.
-constexpr int kAttnTile = 32;
+// Split-KV ("flash decoding") on the warp-level tensor-core instruction: grid (kv_heads, members, splits), four warps.
+// The query heads that share a KV head (up to eight) are the rows of one m16n8k16 A operand, so a K / V tile is read from
+// shared memory once for the whole group (a kernel that lets every head read the tile with its own loads is bound by
+// shared-memory bandwidth at 1/8 of what HBM delivers).  The CTA walks its token range in tiles of 64: cp.async brings K
+// and V rows into padded shared-memory rows (272 bytes: ldmatrix of eight rows touches every bank once), warp w owns
+// tokens 16 w .. 16 w + 15 of every tile and keeps its own running maximum, sum and 16 x 128 output accumulator; the four
+// warps are merged through shared memory at the end.  The reference computes in f32 over the f16 cache
+// (model_ops.rs:439-562); to stay at that accuracy the f32 queries and the probabilities enter the MMAs as two f16 parts
+// each (hi + lo: about 22 bits), with f32 accumulation.
+constexpr int kAttnTile = 64;
 constexpr int kAttnHeadDim = 128;
-constexpr int kAttnKStride = kAttnHeadDim + 8;   // halves; rows 272 bytes apart: the 16-byte loads of eight lanes cover all banks once
+constexpr int kAttnKStride = kAttnHeadDim + 8;   // halves; rows 272 bytes apart
 constexpr int kAttnMaxGroup = 8;
+constexpr int kAttnWarps = 4;
+constexpr int kAttnTileBytes = kAttnTile * kAttnKStride * 2;
+constexpr int kAttnSmemBytes = 4 * kAttnTileBytes;   // two stages of K and V; reused for the merge of the warps
 
-__global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(const float* __restrict__ q, const __half* __restrict__ k_cache,
+__device__ __forceinline__ void ldmatrix_x4(uint32_t address, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t address, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// (lo, hi) as f16 pair, and the f16 pair of what that rounding lost
+__device__ __forceinline__ void split_half2(float lo, float hi, uint32_t& main, uint32_t& rest) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    const float2 back = __half22float2(h);
+    main = *reinterpret_cast<const uint32_t*>(&h);
+    rest = pack_half2(lo - back.x, hi - back.y);
+}
+
+__global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_split_kernel(const float* __restrict__ q, const __half* __restrict__ k_cache,
                                                                              const __half* __restrict__ v_cache,
                                                                              const int* __restrict__ positions, float* __restrict__ part_o,
                                                                              float* __restrict__ part_ml, int q_heads, int kv_heads,
@@ -150,10 +182,7 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
                                                                              int shared_cache, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
-    // Two tiles of each: the next one streams in (cp.async) while the warps work on the current one.
-    __shared__ __align__(16) __half k_tiles[2][kAttnTile * kAttnKStride];
-    __shared__ __align__(16) __half v_tiles[2][kAttnTile * kAttnHeadDim];
-    __shared__ __align__(16) float q_rows[kAttnMaxGroup * kAttnHeadDim];
+    extern __shared__ __align__(128) uint8_t attn_smem[];
     const int kv_head = blockIdx.x;
     const int member = blockIdx.y;
     const int split = blockIdx.z;
@@ -161,7 +190,7 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     const int group = q_heads / kv_heads;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q_head = kv_head * group + warp;
+    const int g = lane >> 2, t = lane & 3;   // fragment coordinates: row g (and g + 8), column pair t
     // positions[] is device memory: the walk is clamped to the context the splits were planned for (at most the
     // cache size), and a position outside it is reported through the status word
     int tokens = positions[member] + 1;
@@ -172,106 +201,162 @@ __global__ void __launch_bounds__(kAttnMaxGroup * 32) attention_split_kernel(con
     const int begin = split * chunk;
     const int end = min(tokens, begin + chunk);
 
-    for (int i = threadIdx.x; i < group * kAttnHeadDim; i += blockDim.x)
-        q_rows[i] = q[(static_cast<size_t>(member) * q_heads + kv_head * group) * kAttnHeadDim + i];
+    // The group's queries as A fragments, times scale * log2(e) (the softmax runs on exp2), hi and lo parts: rows = heads
+    // (rows from `group` on are zero), eight K steps of 16 dims.
+    uint32_t q_hi[8][4], q_lo[8][4];
+    {
+        const float factor = scale * 1.4426950408889634f;
+        const float* q_group = q + (static_cast<size_t>(member) * q_heads + static_cast<size_t>(kv_head) * group) * kAttnHeadDim;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                const int row = g + 8 * (part & 1), column = 16 * ks + 2 * t + 8 * (part >> 1);
+                float2 v = make_float2(0.0f, 0.0f);
+                if (row < group) v = *reinterpret_cast<const float2*>(q_group + row * kAttnHeadDim + column);
+                split_half2(v.x * factor, v.y * factor, q_hi[ks][part], q_lo[ks][part]);
+            }
+        }
+    }
 
     const long long sequence = shared_cache ? 0 : member;
     const __half* k_base = k_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
     const __half* v_base = v_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
-    float running_max = -INFINITY, running_sum = 0.0f;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(attn_smem));
 
-    // Tile loads: 32 tokens x 128 halves each, 16 bytes per request; rows past the range are zero-filled.
+    // Tile loads: 64 tokens x 128 halves of K and of V, 16 bytes per request; rows past the range are zero-filled.
     auto request_tile = [&](int buffer, int t0) {
         const int valid = min(kAttnTile, end - t0);
         for (int i = threadIdx.x; i < kAttnTile * (kAttnHeadDim / 8); i += blockDim.x) {
             const int row = i / (kAttnHeadDim / 8);
-            const int chunk = i % (kAttnHeadDim / 8);
-            __half* kd = k_tiles[buffer] + row * kAttnKStride + 8 * chunk;
-            __half* vd = v_tiles[buffer] + row * kAttnHeadDim + 8 * chunk;
+            const int piece = i % (kAttnHeadDim / 8);
+            const uint32_t kd = smem_base + (2 * buffer) * kAttnTileBytes + (row * kAttnKStride + 8 * piece) * 2;
+            const uint32_t vd = kd + kAttnTileBytes;
             if (row < valid) {
-                const __half* ks = k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk;
-                const __half* vs = v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * chunk;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(kd))), "l"(ks) : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(vd))), "l"(vs) : "memory");
+                const __half* ks = k_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * piece;
+                const __half* vs = v_base + static_cast<long long>(t0 + row) * kAttnHeadDim + 8 * piece;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(ks) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vd), "l"(vs) : "memory");
             } else {
-                *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(kd), "r"(0) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vd), "r"(0) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     if (begin < end) request_tile(0, begin);
 
+    float out[16][4];   // rows g, g + 8; dims 8 n + 2 t, + 1
+#pragma unroll
+    for (int n = 0; n < 16; ++n) out[n][0] = out[n][1] = out[n][2] = out[n][3] = 0.0f;
+    float running_max[2] = {-INFINITY, -INFINITY}, running_sum[2] = {0.0f, 0.0f};
+    // ldmatrix row addresses of this lane inside a tile: K as B operand (not transposed), V as B operand (transposed)
+    const uint32_t k_lane = ((16 * warp + (lane & 7) + 8 * (lane >> 4)) * kAttnKStride + 8 * ((lane >> 3) & 1)) * 2;
+    const uint32_t v_lane = ((16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1)) * kAttnKStride + 8 * (lane >> 4)) * 2;
+
     int buffer = 0;
     for (int t0 = begin; t0 < end; t0 += kAttnTile, buffer ^= 1) {
-        const int valid = min(kAttnTile, end - t0);
         if (t0 + kAttnTile < end) {
             request_tile(buffer ^ 1, t0 + kAttnTile);   // its previous contents were consumed before the barrier that ended the last round
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        __syncthreads();   // this tile has landed for every thread (and q_rows is written, first time round)
-        const __half* k_tile = k_tiles[buffer];
-        const __half* v_tile = v_tiles[buffer];
-        if (warp < group) {
-            // scores: lane = token of the tile
-            const float* qv = q_rows + warp * kAttnHeadDim;
-            const __half* kr = k_tile + lane * kAttnKStride;
-            float dot = 0.0f;
-#pragma unroll 4
-            for (int d = 0; d < kAttnHeadDim; d += 8) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
-                const float4 q0 = *reinterpret_cast<const float4*>(qv + d);
-                const float4 q1 = *reinterpret_cast<const float4*>(qv + d + 4);
-                const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                const float2 k45 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
-                const float2 k67 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
-                dot = fmaf(q0.x, k01.x, dot);
-                dot = fmaf(q0.y, k01.y, dot);
-                dot = fmaf(q0.z, k23.x, dot);
-                dot = fmaf(q0.w, k23.y, dot);
-                dot = fmaf(q1.x, k45.x, dot);
-                dot = fmaf(q1.y, k45.y, dot);
-                dot = fmaf(q1.z, k67.x, dot);
-                dot = fmaf(q1.w, k67.y, dot);
+        __syncthreads();   // this tile has landed for every thread
+        const int first = t0 + 16 * warp;    // this warp's sixteen tokens
+        if (first < end) {
+            const uint32_t k_tile = smem_base + (2 * buffer) * kAttnTileBytes, v_tile = k_tile + kAttnTileBytes;
+            // scores: S[16 heads][16 tokens] = Q K^T, two n-tiles of eight tokens
+            float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t b[4];   // (tokens 0-7: dims lo, hi), (tokens 8-15: dims lo, hi) of this K step
+                ldmatrix_x4(k_tile + k_lane + 32 * ks, b);
+                mma_f16(s[0], q_hi[ks], b[0], b[1]);
+                mma_f16(s[1], q_hi[ks], b[2], b[3]);
+                mma_f16(s[0], q_lo[ks], b[0], b[1]);
+                mma_f16(s[1], q_lo[ks], b[2], b[3]);
             }
-            const float score = lane < valid ? dot * scale : -INFINITY;
-            float tile_max = score;
+            // mask the tokens past the range, then the online softmax of rows g and g + 8
+            const int valid = end - first;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
-            const float new_max = fmaxf(running_max, tile_max);
-            const float p = lane < valid ? expf(score - new_max) : 0.0f;
-            float tile_sum = p;
+            for (int n = 0; n < 2; ++n) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, o);
-            const float rescale = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
-            running_sum = running_sum * rescale + tile_sum;
-            running_max = new_max;
+                for (int c = 0; c < 4; ++c)
+                    if (8 * n + 2 * t + (c & 1) >= valid) s[n][c] = -INFINITY;
+            }
+            uint32_t p_hi[4], p_lo[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] *= rescale;
-            // P.V: lane = output dims 4*lane .. 4*lane+3
-            for (int tk = 0; tk < valid; ++tk) {
-                const float pt = __shfl_sync(0xffffffffu, p, tk);
-                const uint2 raw = *reinterpret_cast<const uint2*>(v_tile + tk * kAttnHeadDim + 4 * lane);
-                const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                acc[0] = fmaf(pt, v01.x, acc[0]);
-                acc[1] = fmaf(pt, v01.y, acc[1]);
-                acc[2] = fmaf(pt, v23.x, acc[2]);
-                acc[3] = fmaf(pt, v23.y, acc[3]);
+            for (int r = 0; r < 2; ++r) {
+                float tile_max = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+                const float new_max = fmaxf(running_max[r], tile_max);   // finite: the warp has at least one valid token
+                const float rescale = exp2f(running_max[r] - new_max);   // 0 the first time round
+                running_max[r] = new_max;
+                const float p0 = exp2f(s[0][2 * r] - new_max), p1 = exp2f(s[0][2 * r + 1] - new_max);
+                const float p2 = exp2f(s[1][2 * r] - new_max), p3 = exp2f(s[1][2 * r + 1] - new_max);
+                running_sum[r] = running_sum[r] * rescale + ((p0 + p1) + (p2 + p3));   // this lane's share; lanes are added at the end
+#pragma unroll
+                for (int n = 0; n < 16; ++n) {
+                    out[n][2 * r] *= rescale;
+                    out[n][2 * r + 1] *= rescale;
+                }
+                // A fragment of P: a[r] = tokens 2t, 2t+1 of row g + 8 r; a[2 + r] = tokens 8 + 2t, + 1
+                split_half2(p0, p1, p_hi[r], p_lo[r]);
+                split_half2(p2, p3, p_hi[2 + r], p_lo[2 + r]);
+            }
+            // O += P V: one K step of sixteen tokens, sixteen n-tiles of eight dims
+#pragma unroll
+            for (int pair = 0; pair < 8; ++pair) {
+                uint32_t b[4];   // dims 16 pair .. + 7: (tokens 0-7, 8-15), dims 16 pair + 8 .. + 15: (tokens 0-7, 8-15)
+                ldmatrix_x4_trans(v_tile + v_lane + 32 * pair, b);
+                mma_f16(out[2 * pair], p_hi, b[0], b[1]);
+                mma_f16(out[2 * pair + 1], p_hi, b[2], b[3]);
+                mma_f16(out[2 * pair], p_lo, b[0], b[1]);
+                mma_f16(out[2 * pair + 1], p_lo, b[2], b[3]);
             }
         }
         __syncthreads();   // every warp is done with this buffer before the next round refills it
     }
-    if (warp < group) {
-        const size_t slot = (static_cast<size_t>(member) * q_heads + q_head) * splits + split;
-        *reinterpret_cast<float4*>(part_o + slot * kAttnHeadDim + 4 * lane) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        if (lane == 0) {
-            part_ml[slot * 2] = running_max;
-            part_ml[slot * 2 + 1] = running_sum;
+
+    // merge the four warps: [warp][row] maximum and sum, [warp][row][dim] output, in the tile buffers
+    float* merge_o = reinterpret_cast<float*>(attn_smem);                        // [4][8][128]
+    float* merge_m = merge_o + kAttnWarps * kAttnMaxGroup * kAttnHeadDim;         // [4][8]
+    float* merge_l = merge_m + kAttnWarps * kAttnMaxGroup;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        running_sum[r] += __shfl_xor_sync(0xffffffffu, running_sum[r], 1);
+        running_sum[r] += __shfl_xor_sync(0xffffffffu, running_sum[r], 2);
+    }
+    if (g < kAttnMaxGroup) {   // rows g + 8 are padding: at most eight heads share a KV head
+        if (t == 0) {
+            merge_m[warp * kAttnMaxGroup + g] = running_max[0];
+            merge_l[warp * kAttnMaxGroup + g] = running_sum[0];
+        }
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+            *reinterpret_cast<float2*>(merge_o + (warp * kAttnMaxGroup + g) * kAttnHeadDim + 8 * n + 2 * t) = make_float2(out[n][0], out[n][1]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * kAttnHeadDim; i += blockDim.x) {
+        const int row = i / kAttnHeadDim, dim = i % kAttnHeadDim;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, merge_m[w * kAttnMaxGroup + row]);
+        float total = 0.0f, value = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float m = merge_m[w * kAttnMaxGroup + row];
+            const float weight = m == -INFINITY ? 0.0f : exp2f(m - top);
+            total = fmaf(merge_l[w * kAttnMaxGroup + row], weight, total);
+            value = fmaf(merge_o[(w * kAttnMaxGroup + row) * kAttnHeadDim + dim], weight, value);
+        }
+        const size_t slot = (static_cast<size_t>(member) * q_heads + static_cast<size_t>(kv_head) * group + row) * splits + split;
+        part_o[slot * kAttnHeadDim + dim] = value;
+        if (dim == 0) {
+            part_ml[slot * 2] = top * 0.6931471805599453f;   // back to natural-log units for the merge of the splits
+            part_ml[slot * 2 + 1] = total;
         }
     }
 }
@@ -424,7 +509,15 @@ cudaError_t launch_attention_decode(const LayerAttentionArgs& a, void* out, bool
     float* part_o = static_cast<float*>(scratch);
     float* part_ml = part_o + static_cast<size_t>(a.members) * a.q_heads * splits * kAttnHeadDim;
     const float scale = 1.0f / sqrtf(static_cast<float>(a.head_dim));
-    cudaError_t e = launch_kernel_if(pdl_switch() == 1, attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(group * 32), 0, a.stream,
+    static int configured_device = -1;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (configured_device != device) {
+        const cudaError_t attribute = cudaFuncSetAttribute(attention_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
+        if (attribute != cudaSuccess) return attribute;
+        configured_device = device;
+    }
+    cudaError_t e = launch_kernel_if(pdl_switch() == 1, attention_split_kernel, dim3(a.kv_heads, a.members, splits), dim3(kAttnWarps * 32), kAttnSmemBytes, a.stream,
                                   static_cast<const float*>(a.q), static_cast<const __half*>(a.k_cache), static_cast<const __half*>(a.v_cache),
                                   a.positions, part_o, part_ml, a.q_heads, a.kv_heads, a.max_context, static_cast<int>(chunk), scale,
                                   static_cast<int>(a.active_context), a.shared_cache ? 1 : 0, a.device_status);

@@ -1,7 +1,7 @@
 // Quantized skinny GEMM (9..64 member rows) on the 5th-generation tensor cores with the weight operand unpacked
 // straight into tensor memory.
 //
-//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]          Q4_K / Q5_K / Q6_K, up to 64 bf16 or 32 f32 member rows per launch
+//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]          Q4_K / Q5_K / Q6_K, up to 64 member rows per launch
 //
 // The path is bound by HBM: a 4.5-bit weight arrives every ~0.025 SM clocks, which leaves about three thread
 // instructions per weight, and the integer pipe -- where the bit manipulation of the unpacking runs -- issues
@@ -18,9 +18,9 @@
 //     the A operand of tcgen05.mma (M = 128 rows, K = 16 per instruction, N = 16 / 32 / 64 columns); they never
 //     pass through shared memory.  The minimum term -dmin * m[g] * sum_g(x) is one more MMA per super-block with
 //     the eight products -dmin * m[g] as A and the activations' block sums as B;
-//   * the B operand -- the activations as f16, scaled by one power of two per member row, two planes (hi + lo)
-//     for f32 inputs -- is made once per call by a pre-pass in exactly the swizzled K-major tiles the MMA
-//     reads, and streamed from L2 into a shared-memory ring with bulk copies next to the weights;
+//   * the B operand -- the activations as f16, scaled by one power of two per member row -- is made once per
+//     call by a pre-pass in exactly the swizzled K-major tiles the MMA reads, and streamed from L2 into a
+//     shared-memory ring with bulk copies next to the weights;
 //   * the accumulator is read back once, at the end of the CTA's K range.
 // About 1.5 thread instructions per weight whatever the number of member rows.
 //
@@ -849,7 +849,9 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.n = a.n;
     p.nsb = nsb;
     p.members = a.members;
-    p.planes = a.x_bf16 ? 1 : 2;
+    // f32 activations reach this kernel only on request (option tc_f32_activations), as values rounded to f16 under the
+    // member row's power-of-two factor: one plane, like bf16.  (The image and the read-back also serve two planes, hi + lo.)
+    p.planes = 1;
     p.ksplit = ksplit;
     p.raw_stages = raw_stages;
     p.b_stages = b_stages;
@@ -864,7 +866,7 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
 
 template <uint32_t FMT>
 cudaError_t launch_columns(const TmemGemvArgs& a) {
-    const int columns = a.members * (a.x_bf16 ? 1 : 2);
+    const int columns = a.members;
     if (columns <= 16) return launch_format<FMT, 16>(a);
     if (columns <= 32) return launch_format<FMT, 32>(a);
     return launch_format<FMT, 64>(a);
@@ -874,7 +876,8 @@ cudaError_t launch_columns(const TmemGemvArgs& a) {
 
 bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_bf16, const void* weights) {
     if (value_type != kQ4_K && value_type != kQ5_K && value_type != kQ6_K) return false;
-    if (members < 1 || members > (x_bf16 ? 64 : 32) || k <= 0 || k % kSuperBlock != 0 || n < 1) return false;
+    (void)x_bf16;
+    if (members < 1 || members > 64 || k <= 0 || k % kSuperBlock != 0 || n < 1) return false;
     if (value_type == kQ6_K && (k / kSuperBlock) % 8 != 0) return false;   // rows of 210-byte super-blocks must start on 16-byte boundaries
     return reinterpret_cast<uintptr_t>(weights) % 16 == 0;
 }

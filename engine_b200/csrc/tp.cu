@@ -24,7 +24,7 @@
 // can be at most one exchange ahead of a peer (it needs the peer's flag for e + 1, which the peer stores only after its
 // exchange e has completed), so a slot is never rewritten while somebody still reads it.
 //
-// No collective library, no multicast object and no bulk-copy engine is involved: ordinary loads and stores on mapped
+// No collective library, no switch-side reduction and no bulk-copy engine is involved: ordinary loads and stores on mapped
 // peer memory.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
