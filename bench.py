@@ -175,6 +175,43 @@ def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
             "whole_step": {"achieved": step_gbps, "frac": step_gbps / peak, "bytes_per_step": step_bytes}}
 
 
+def attention_profile(spec: str) -> None:
+    """One layer's decode attention (ribn_attention_decode: split-KV kernel + merge) on random f16 KV entries, five calls;
+    prints the mean device time and the KV bytes per second.  For profiler captures of attention_split_kernel."""
+    import torch
+
+    import engine_b200
+    from engine_b200 import _lib, decode
+
+    fields = [int(v) for v in spec.split(":")]
+    members, context = fields[0], fields[1]
+    q_heads, kv_heads = (fields[2], fields[3]) if len(fields) >= 4 else (32, 8)
+    stream = torch.cuda.Stream()
+    ctx = engine_b200.RibnContext(0, stream=stream)
+    ops = decode.CudaDenseOps(ctx)
+    with torch.cuda.stream(stream):
+        k_cache = torch.randn(members, kv_heads, context, 128, device=ctx.device).to(torch.float16)
+        v_cache = torch.randn(members, kv_heads, context, 128, device=ctx.device).to(torch.float16)
+        q = torch.randn(members, q_heads * 128, device=ctx.device)
+        out = torch.empty(members, q_heads * 128, device=ctx.device)
+        positions = torch.full((members,), context - 1, dtype=torch.int32, device=ctx.device)
+        attention = _lib.Attention(members, q_heads, kv_heads, 128, 128, 1e6, 1e-6, None, None, positions.data_ptr(), k_cache.data_ptr(),
+                                   v_cache.data_ptr(), context, context)
+        ops.attention_decode(attention, q, out)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(5):
+            ops.attention_decode(attention, q, out)
+        b.record(stream)
+    ctx.synchronize()
+    us = a.elapsed_time(b) / 5 * 1e3
+    kv_bytes = 2 * k_cache.numel() * 2
+    print(json.dumps({"attention_profile": {"members": members, "context": context, "q_heads": q_heads, "kv_heads": kv_heads, "us_per_call": us,
+                                            "kv_bytes": kv_bytes, "GBps": kv_bytes / us / 1e3, "frac_of_peak": kv_bytes / us / 1e3 / measured_peak()[0],
+                                            "note": "back-to-back calls over the same cache: a cache of more than 126 MB is re-read from HBM"}}))
+
+
 def prefill_leg(ctx, device, stream):
     """ribn_gemm on the two configuration-3 matrices, 512 and 2048 tokens, bf16 in and out: TFLOP/s and the fraction of
     the measured dense bf16 throughput (the kernel issues two MMAs per weight -- high and low bf16 part -- so half of
@@ -647,6 +684,8 @@ def main() -> None:
     parser.add_argument("--no-cases", action="store_true", help="skip the per-case table and the Q8_0 leg")
     parser.add_argument("--members", default="", help="comma-separated member counts replacing 1,4,16,64 (measurement runs, not the benchmark line)")
     parser.add_argument("--formats", default="", help="comma-separated formats (Q8_0,Q4_K,Q5_K,Q6_K) replacing the sweep's three")
+    parser.add_argument("--attention", default="", metavar="MEMBERS:CONTEXT[:Q_HEADS:KV_HEADS]",
+                        help="profiling run, not the benchmark: five calls of the decode attention of one layer (random KV), then exit")
     parser.add_argument("--only", default="", help="restrict the sweep to one case FORMAT:NxK:M (e.g. Q4_K:4096x4096:1); "
                         "a small run for profiler captures, not a benchmark line")
     args = parser.parse_args()
@@ -680,6 +719,9 @@ def main() -> None:
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    if args.attention:
+        attention_profile(args.attention)
+        return
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
