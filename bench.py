@@ -301,7 +301,7 @@ def tp_parity_leg(ctx, rank, world, link_factory):
 
     from engine_b200 import decode
 
-    geometry = decode.DenseGeometry(hidden=1024, layers=2, q_heads=8, kv_heads=8, head_dim=128, intermediate=2048, vocabulary=4096)
+    geometry = decode.DenseGeometry(hidden=1024, layers=2, q_heads=16, kv_heads=8, head_dim=128, intermediate=2048, vocabulary=4096)
     members = 4
     tensors, vectors = decode.host_model(geometry, seed=3)
     out = {}
@@ -341,7 +341,7 @@ def tp_parity_leg(ctx, rank, world, link_factory):
         torch.cuda.synchronize()
         dist.barrier()
         link.close()
-    out["geometry"] = "hidden 1024, 2 layers, 8 heads, intermediate 2048, vocabulary 4096; 4 sequences, 5 steps"
+    out["geometry"] = "hidden 1024, 2 layers, 16 query / 8 key-value heads, intermediate 2048, vocabulary 4096; 4 sequences, 5 steps"
     return out
 
 

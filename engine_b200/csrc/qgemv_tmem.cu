@@ -82,7 +82,9 @@ struct TmemParams {
     int y_bf16;
     int accumulate;
     float* partial;             // split-K scratch [ksplit][members][n]
-    unsigned int* tickets;      // one zero-initialised counter per row tile
+    unsigned int* tickets;      // zero-initialised counters: [row tile] arrivals, [ticket_stride + row tile] departures
+    int ticket_stride;
+    int cooperative;            // every CTA of the grid is resident at once: the CTAs of a row tile share the sum of its partial tiles
     int k, n, nsb, members, planes, ksplit, raw_stages, b_stages;
     int* status;
     long long* trace;           // diagnostics (builds with -DRIBN_TRACE): wall-clock stamps of CTA (0, 0), or null
@@ -699,23 +701,53 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
         }
         tcgen05_fence_before_sync();
         if (quadrant == 0) stamp(p, 2 + half, 23);
-        // ---------------- split-K: the CTA that draws the last ticket of its row tile adds the partial tiles ----------------
+        // ---------------- split-K: the partial tiles of a row tile are added in split order ----------------
+        // When the whole grid is resident at once (the launcher knows), every CTA of the row tile waits for the others'
+        // partial tiles (bounded) and adds its own share of the tile: the sum is spread over `ksplit` SMs.  Otherwise the
+        // CTA that draws the last ticket adds the whole tile (a CTA must not wait for one that may not have started).
         if (split) {
             __threadfence();
             named_barrier_sync(1, kWorkers);
+            unsigned int* ticket = p.tickets + blockIdx.x;
+            unsigned int* departed = p.tickets + p.ticket_stride + blockIdx.x;
+            int first_item = 0, last_item = p.members * (kRows / 4);
             if (threadIdx.x == 0) {
-                unsigned int* ticket = p.tickets + blockIdx.x;
-                const unsigned int drawn = atomicAdd(ticket, 1u);
-                const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
-                if (last) *ticket = 0;   // ready for the next launch
-                *last_flag = last ? 1u : 0u;
+                if (p.cooperative) {
+                    atomicAdd(ticket, 1u);
+                    unsigned long long start;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(start));
+                    bool all = true;
+                    unsigned int spins = 0;
+                    while (*reinterpret_cast<volatile unsigned int*>(ticket) < static_cast<unsigned int>(p.ksplit)) {
+                        if ((++spins & 255u) == 0u) {
+                            unsigned long long now;
+                            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                            if (now - start > 1000000000ull) {
+                                all = false;
+                                break;
+                            }
+                        }
+                    }
+                    if (!all) atomicExch(p.status, kDeviceWaitTimeout);
+                    *last_flag = all ? 1u : 0u;
+                } else {
+                    const unsigned int drawn = atomicAdd(ticket, 1u);
+                    const bool last = drawn == static_cast<unsigned int>(p.ksplit - 1);
+                    if (last) *ticket = 0;   // ready for the next launch
+                    *last_flag = last ? 1u : 0u;
+                }
             }
             named_barrier_sync(1, kWorkers);
+            if (p.cooperative) {
+                const int items = p.members * (kRows / 4);
+                first_item = static_cast<int>(static_cast<long long>(items) * blockIdx.y / p.ksplit);
+                last_item = static_cast<int>(static_cast<long long>(items) * (blockIdx.y + 1) / p.ksplit);
+            }
             if (*last_flag != 0) {
                 __threadfence();
                 const size_t plane = static_cast<size_t>(p.members) * p.n;
                 const bool vector = (p.n & 3) == 0;
-                for (int idx = threadIdx.x; idx < p.members * (kRows / 4); idx += kWorkers) {
+                for (int idx = first_item + static_cast<int>(threadIdx.x); idx < last_item; idx += kWorkers) {
                     const int m = idx / (kRows / 4);
                     const long long row = static_cast<long long>(n0) + (idx % (kRows / 4)) * 4;
                     if (row >= p.n) continue;
@@ -754,6 +786,14 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
                     }
                 }
             }
+            if (p.cooperative) {
+                // the last CTA to leave resets both counters: by then every CTA of the row tile has passed its wait
+                named_barrier_sync(1, kWorkers);
+                if (threadIdx.x == 0 && atomicAdd(departed, 1u) == static_cast<unsigned int>(p.ksplit - 1)) {
+                    *departed = 0;
+                    *ticket = 0;
+                }
+            }
         }
     }
 
@@ -769,6 +809,7 @@ constexpr size_t kSmemLimit = 227 * 1024;
 
 // K splits by a cost model in units of super-blocks: waves of CTAs x (super-blocks per CTA + a fixed cost per CTA).
 int choose_splits(int tiles, int nsb, int ctas_per_wave, int members, size_t scratch_bytes, int n, int max_tickets) {
+    max_tickets /= 2;   // arrivals and departures
     constexpr double kFixedCost = 5.0;
     int best = 1;
     double best_cost = 1e30;
@@ -776,7 +817,8 @@ int choose_splits(int tiles, int nsb, int ctas_per_wave, int members, size_t scr
         if (ks > 1 && (static_cast<size_t>(ks) * members * n * sizeof(float) > scratch_bytes || tiles > max_tickets)) break;
         const int waves = (tiles * ks + ctas_per_wave - 1) / ctas_per_wave;
         // the last CTA of a row tile reads ks partial tiles of members x 128 floats: about one super-block time per 32 KB
-        const double reduce = ks > 1 ? 1.0 + ks * members * 512.0 / 32768.0 : 0.0;
+        // one wave: the CTAs of a row tile share the sum (each reads members x 128 floats in all); more: the last one reads all
+        const double reduce = ks <= 1 ? 0.0 : (waves == 1 ? 1.0 + members * 512.0 / 32768.0 : 1.0 + ks * members * 512.0 / 32768.0);
         const double cost = waves * ((nsb + ks - 1) / ks + kFixedCost + reduce);
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
@@ -814,6 +856,7 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     if (a.force_ksplit > 0 && a.force_ksplit <= nsb && static_cast<size_t>(a.force_ksplit) * a.members * a.n * sizeof(float) <= partial_bytes &&
         tiles <= a.ticket_count)
         ksplit = a.force_ksplit;
+    const bool cooperative = ksplit > 1 && tiles * ksplit <= resident * a.sm_count && 2 * tiles <= a.ticket_count;
     static int configured_device = -1;
     int device = 0;
     cudaGetDevice(&device);
@@ -845,6 +888,8 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.accumulate = a.accumulate ? 1 : 0;
     p.partial = partial;
     p.tickets = a.tickets;
+    p.ticket_stride = a.ticket_count / 2;
+    p.cooperative = cooperative ? 1 : 0;
     p.k = a.k;
     p.n = a.n;
     p.nsb = nsb;
