@@ -113,7 +113,9 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "mma_image_members": launches of at least this many rows convert their activations in a pre-pass launch,
  *                   narrower ones inside the GEMV kernel (1..9, default 3);
  *   "mma_stages":   ring depth of that kernel, 0 = as many stages as fit (default);
- *   "tc_min_members": smallest bf16 batch ribn_gemv sends to the tcgen05 decode kernel (default 9);
+ *   "tc_min_members": smallest bf16 batch ribn_gemv sends to a tcgen05 batch kernel (default 9);
+ *   "tmem_gemv":    1 = those batches (Q4_K / Q5_K / Q6_K, up to 64 rows) run on the kernel that unpacks the weights into
+ *                   tensor memory (default); 0 = on the f16-tile kernel, which also serves Q8_0;
  *   "tc_four_row_bytes": where the mma kernel does not serve a shape, bf16 batches of exactly four rows use the
  *                   tcgen05 kernel when the encoded weights are at least this many bytes (default 8 MiB);
  *   "tc_f32_activations": 1 = f32 batches may use the tcgen05 kernel too (they are rounded to f16; default 0);
