@@ -63,13 +63,29 @@ namespace {
 constexpr int kRows = 128;                 // weight rows per CTA = UMMA M = TMEM lanes
 constexpr int kWorkerWarps = 8;
 constexpr int kWorkers = kWorkerWarps * 32;
-constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;             // issues pairs 0 and 1 of every super-block and the minimum term into accumulator 0; owns TMEM
-constexpr int kIssuerWarp2 = 10;           // issues pairs 2 and 3 into accumulator 1
-constexpr int kTmemThreads = 352;
+// Worker sets: with 64 accumulator columns one CTA owns the SM (shared memory), and eight worker warps leave the issue slots
+// two thirds idle while they wait on shared memory, tensor memory and barriers; a second set of eight takes the odd
+// super-blocks (its own A slots and minimum buffer: the A operand is double-buffered there anyway).
+template <int NT>
+struct Roles {
+    static constexpr int kSets = NT >= 64 ? 2 : 1;
+    static constexpr int kProducerWarp = kSets * kWorkerWarps;
+    static constexpr int kIssuerWarp = kProducerWarp + 1;    // pairs 0 and 1 of every super-block and the minimum term, accumulator 0; owns TMEM
+    static constexpr int kIssuerWarp2 = kProducerWarp + 2;   // pairs 2 and 3, accumulator 1
+    static constexpr int kThreads = (kProducerWarp + 3) * 32;
+};
 constexpr int kPairs = 4;                  // 64-weight pairs of sub-blocks per super-block = A slots in TMEM
 constexpr int kPairColumns = 32;           // TMEM columns of one pair: 64 halves per row
 constexpr int kMaxStages = 4;
+
+// Tiled TMA wants a 16-byte aligned base and row pitch.  A Q6_K matrix whose rows are 210 * nsb bytes with nsb not a
+// multiple of eight has neither for most rows, but rows n, n + P, n + 2 P, ... (P = 16 / gcd(row bytes, 16)) are P * row
+// bytes apart -- a multiple of 16 -- so the matrix is P interleaved matrices, one tensor map each, whose bases are rounded
+// down to 16 bytes; a row tile is then P boxes of 128 / P rows, and tile row r = c * (128 / P) + j is matrix row
+// n0 + j * P + c.
+struct WeightMaps {
+    CUtensorMap map[8];
+};
 
 struct TmemParams {
     const void* x;              // [members][k] (swiglu: [members][2k]) f32 or bf16
@@ -86,6 +102,8 @@ struct TmemParams {
     int ticket_stride;
     int cooperative;            // every CTA of the grid is resident at once: the CTAs of a row tile share the sum of its partial tiles
     int k, n, nsb, members, planes, ksplit, raw_stages, b_stages;
+    int row_classes;            // 1, or for Q6_K rows that do not start on 16-byte boundaries 2 / 4 / 8: rows n0 + j * classes + c share class c
+    unsigned int row_bytes;
     int* status;
     long long* trace;           // diagnostics (builds with -DRIBN_TRACE): wall-clock stamps of CTA (0, 0), or null
 };
@@ -213,48 +231,72 @@ __device__ __forceinline__ void umma_f16_tmem_a_elected(uint32_t tmem_d, uint32_
 }
 
 // ---------------------------------------------------------------- pre-pass: activations -> MMA tiles in global memory
-__device__ __forceinline__ void load_activation_slice(const TmemParams& p, int m, int sb, int lane, float inv_rms, float (&v)[8]) {
-    const int k0 = sb * kSuperBlock + lane * 8;
-    const size_t row_elements = static_cast<size_t>(p.k) * (p.mode == 2 ? 2 : 1);
-    const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * row_elements * (p.x_bf16 ? 2 : 4), p.x_bf16};
-    load_row8(row + k0, v);
-    if (p.mode == 2) {
-        float u[8];
-        load_row8(row + (p.k + k0), u);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u[j];
-    } else if (p.mode == 1) {
-        float g[8];
-        load_x8<float>(p.norm_weight + k0, g);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * g[j];
-    }
-}
+// grid (members), 256 threads.  One sweep over the member's row in global memory: the values (x, or silu(gate) * up) go
+// to a shared-memory copy of the row while their sum of squares (fused RMSNorm) and largest magnitude are gathered; the
+// normalisation, the largest magnitude of what enters the product and the conversion then work on the copy.  Every value
+// is multiplied by the power of two that brings that magnitude into [512, 1024) and stored as f16 (plane 0; for two
+// planes also the f16 of what plane 0 lost).  Within a group of four K elements the tiles hold [e0, e2, e1, e3], the order
+// the weight unpacking produces.  Rows longer than the copy can hold (`cached` = 0) are re-read from global memory.
+constexpr int kImageCacheFloats = 50 * 1024;   // 200 KB
 
-// grid (members), 256 threads.  Three sweeps over the member's row (it stays in L1/L2): sum of squares when an RMSNorm
-// is fused, the largest magnitude of the values that enter the product, then the conversion: every value times the
-// power of two that brings that magnitude into [512, 1024), as f16 (plane 0) and, for f32 inputs, the f16 of what
-// plane 0 lost (plane 1).  Within a group of four K elements the tiles hold [e0, e2, e1, e3], the order the weight
-// unpacking produces.
 template <int NT>
-__global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p) {
+__global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int cached) {
     using I = ImagePlan<NT, 5>;
+    extern __shared__ __align__(16) float row_copy[];
     __shared__ float red[8];
     __shared__ uint32_t red_bits[8];
     pdl_launch_dependents();
     pdl_wait_prior();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x;
+    const size_t row_elements = static_cast<size_t>(p.k) * (p.mode == 2 ? 2 : 1);
+    const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * row_elements * (p.x_bf16 ? 2 : 4), p.x_bf16};
+    // what the first sweep reads of super-block sb: x (modes 0, 1) or silu(gate) * up (mode 2)
+    auto read_slice = [&](int sb, float (&v)[8]) {
+        const int k0 = sb * kSuperBlock + lane * 8;
+        load_row8(row + k0, v);
+        if (p.mode == 2) {
+            float u[8];
+            load_row8(row + (p.k + k0), u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (v[j] / (1.0f + expf(-v[j]))) * u[j];
+        }
+    };
+    auto keep = [&](int sb, const float (&v)[8]) {
+        float4* dst = reinterpret_cast<float4*>(row_copy + sb * kSuperBlock + lane * 8);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    };
+    auto kept = [&](int sb, float (&v)[8]) {
+        const float4* src = reinterpret_cast<const float4*>(row_copy + sb * kSuperBlock + lane * 8);
+        const float4 a = src[0], b = src[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    };
+    // non-negative floats order like their bit patterns; infinities and NaNs (0x7f800000 and above) come out on top
+    uint32_t biggest = 0u;
+    float part = 0.0f;
+    for (int sb = warp; sb < p.nsb; sb += 16) {   // two slices per trip: their loads are in flight together
+        float v0[8], v1[8];
+        const bool second = sb + 8 < p.nsb;
+        read_slice(sb, v0);
+        if (second) read_slice(sb + 8, v1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            part = fmaf(v0[j], v0[j], part);
+            biggest = max(biggest, __float_as_uint(fabsf(v0[j])));
+        }
+        if (cached) keep(sb, v0);
+        if (second) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                part = fmaf(v1[j], v1[j], part);
+                biggest = max(biggest, __float_as_uint(fabsf(v1[j])));
+            }
+            if (cached) keep(sb + 8, v1);
+        }
+    }
     float inv_rms = 1.0f;
     if (p.mode == 1) {
-        const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * p.k * (p.x_bf16 ? 2 : 4), p.x_bf16};
-        float part = 0.0f;
-        for (int c = threadIdx.x; c < p.k / 8; c += 256) {
-            float v[8];
-            load_row8(row + c * 8, v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) part = fmaf(v[j], v[j], part);
-        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
         if (lane == 0) red[warp] = part;
@@ -263,14 +305,20 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) total += red[w];
         inv_rms = 1.0f / sqrtf(total / static_cast<float>(p.k) + p.eps);
-    }
-    // non-negative floats order like their bit patterns; infinities and NaNs (0x7f800000 and above) come out on top
-    uint32_t biggest = 0u;
-    for (int sb = warp; sb < p.nsb; sb += 8) {
-        float v[8];
-        load_activation_slice(p, m, sb, lane, inv_rms, v);
+        // the normalised values, in the order of operations of rms_norm (x * inv_rms * weight), and their largest magnitude
+        biggest = 0u;
+        for (int sb = warp; sb < p.nsb; sb += 8) {
+            float v[8], g[8];
+            if (cached) kept(sb, v);
+            else read_slice(sb, v);
+            load_x8<float>(p.norm_weight + sb * kSuperBlock + lane * 8, g);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) biggest = max(biggest, __float_as_uint(fabsf(v[j])));
+            for (int j = 0; j < 8; ++j) {
+                v[j] = v[j] * inv_rms * g[j];
+                biggest = max(biggest, __float_as_uint(fabsf(v[j])));
+            }
+            if (cached) keep(sb, v);
+        }
     }
     biggest = __reduce_max_sync(0xffffffffu, biggest);
     if (lane == 0) red_bits[warp] = biggest;
@@ -291,7 +339,17 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p) {
     float* scales = reinterpret_cast<float*>(p.image + I::scales_offset(p.nsb));
     for (int sb = warp; sb < p.nsb; sb += 8) {
         float v[8];
-        load_activation_slice(p, m, sb, lane, inv_rms, v);
+        if (cached) {
+            kept(sb, v);   // a warp reads back what it wrote itself
+        } else {
+            read_slice(sb, v);
+            if (p.mode == 1) {
+                float g[8];
+                load_x8<float>(p.norm_weight + sb * kSuperBlock + lane * 8, g);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = v[j] * inv_rms * g[j];
+            }
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = bad ? 0.0f : v[j] * down;
         uint8_t* stage = p.image + static_cast<size_t>(sb) * I::kStageBytes;
@@ -392,11 +450,14 @@ __device__ __forceinline__ void unpack_pair_q6(uint32_t la, uint32_t lb, uint32_
 
 // ---------------------------------------------------------------- the kernel
 template <uint32_t FMT, int NT>
-__global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const TmemParams p) {
+__global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_tmem_kernel(const __grid_constant__ WeightMaps wmaps, const TmemParams p) {
     using P = TmemPlan<FMT, NT>;
     using I = typename P::I;
+    using R = Roles<NT>;
+    constexpr int kProducerWarp = R::kProducerWarp, kIssuerWarp = R::kIssuerWarp, kIssuerWarp2 = R::kIssuerWarp2, kSets = R::kSets;
     constexpr uint32_t kQuantOffset = FMT == kQ5_K ? 48 : 16;
     constexpr int AB = P::kABuffers;
+    static_assert(kSets == 1 || AB == kSets, "a worker set owns one buffer of the A operand");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const int sb_begin = static_cast<int>(static_cast<long long>(p.nsb) * blockIdx.y / p.ksplit);
@@ -441,7 +502,7 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
         }
         mbar_init(d_full, 2);
         mbar_fence_init();
-        tma_prefetch_descriptor(&wmap);
+        for (int c = 0; c < p.row_classes; ++c) tma_prefetch_descriptor(&wmaps.map[c]);
     }
     if (warp == kIssuerWarp) tmem_alloc(tmem_holder, P::kTmemColumns);
     tcgen05_fence_before_sync();
@@ -458,9 +519,18 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
                 const int s = i % p.raw_stages;
                 if (i >= p.raw_stages && !mbar_wait_bounded(&raw_empty[s], ((i / p.raw_stages) - 1) & 1)) return false;
                 mbar_arrive_expect_tx(&raw_full[s], P::kRawStageBytes);
-                // x in 16-bit elements: the super-block's first byte, rounded down to a 16-byte boundary for Q6_K
-                const int x = FMT == kQ6_K ? (((sb_begin + i) * P::kSbBytes) & ~15) / 2 : (sb_begin + i) * (P::kSbBytes / 2);
-                tma_load_2d(raw + static_cast<size_t>(s) * P::kRawStageBytes, &wmap, x, n0, &raw_full[s]);
+                if constexpr (FMT == kQ6_K) {
+                    // x in 16-bit elements: the super-block's first byte within the class's rows, rounded down to 16 bytes
+                    const int rows = kRows / p.row_classes;
+                    for (int c = 0; c < p.row_classes; ++c) {
+                        const unsigned int delta = (static_cast<unsigned int>(c) * p.row_bytes) & 15u;
+                        const int x = static_cast<int>((delta + static_cast<unsigned int>(sb_begin + i) * 210u) & ~15u) / 2;
+                        tma_load_2d(raw + static_cast<size_t>(s) * P::kRawStageBytes + static_cast<size_t>(c) * rows * P::kRowPitch, &wmaps.map[c], x,
+                                    n0 / p.row_classes, &raw_full[s]);
+                    }
+                } else {
+                    tma_load_2d(raw + static_cast<size_t>(s) * P::kRawStageBytes, &wmaps.map[0], (sb_begin + i) * (P::kSbBytes / 2), n0, &raw_full[s]);
+                }
                 return true;
             };
             auto issue_b = [&](int i) {
@@ -535,7 +605,8 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
         __syncwarp();
     } else {
         // ---------------- workers ----------------
-        const int half = warp >> 2;                      // which 128 weights of every super-block this thread expands
+        const int set = warp / kWorkerWarps;             // set s expands super-blocks s, s + kSets, ...
+        const int half = (warp % kWorkerWarps) >> 2;     // which 128 weights of every super-block this thread expands
         const int quadrant = warp & 3;                   // a warp reaches TMEM lanes 32 * (warp % 4) .. + 31
         const int row_in_tile = quadrant * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16);
@@ -543,16 +614,18 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
         bool ok = true;
 
 #pragma unroll 1
-        for (int i = 0; i < local_sb; ++i) {
+        for (int i = set; i < local_sb; i += kSets) {
             const int s = i % p.raw_stages;
             if (ok && !mbar_wait_bounded(&raw_full[s], (i / p.raw_stages) & 1)) {
                 atomicExch(p.status, kDeviceWaitTimeout);
                 ok = false;
             }
-            if (i < 4 && quadrant == 0) stamp(p, 2 + half, 2 + i * 4);
+            if (i < 4 && quadrant == 0 && set == 0) stamp(p, 2 + half, 2 + i * 4);
             const int abuf = i % AB;
             if constexpr (FMT == kQ6_K) {
-                const uint32_t blk = raw_addr + static_cast<uint32_t>(s) * P::kRawStageBytes + ((static_cast<uint32_t>(sb_begin + i) * 210u) & 15u);
+                const uint32_t row_class = static_cast<uint32_t>(row_in_tile) / static_cast<uint32_t>(kRows / p.row_classes);
+                const uint32_t blk = raw_addr + static_cast<uint32_t>(s) * P::kRawStageBytes +
+                                     ((((row_class * p.row_bytes) & 15u) + static_cast<uint32_t>(sb_begin + i) * 210u) & 15u);
                 const float d = f16_bits_to_f32(lds_u16(blk + 208));
                 const bool wide = !(fabsf(d) <= 1.0f);   // kept symmetrical with the other formats: beyond it d multiplies afterwards
                 if (!(fabsf(d) < 32.0f)) atomicExch(p.status, kDeviceScaleRange);
@@ -651,11 +724,12 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[s]);
-            if (i < 4 && quadrant == 0) stamp(p, 2 + half, 3 + i * 4);
+            if (i < 4 && quadrant == 0 && set == 0) stamp(p, 2 + half, 3 + i * 4);
         }
-        if (quadrant == 0) stamp(p, 2 + half, 20);
+        if (quadrant == 0 && set == 0) stamp(p, 2 + half, 20);
 
-        // ---------------- the accumulators, once: a thread holds its row's columns of this half ----------------
+        // ---------------- the accumulators, once (first worker set): a thread holds its row's columns of this half ----------------
+        if (set == 0) {
         pdl_wait_prior();   // the scale factors (and y, when it is accumulated into) come from earlier kernels
         if (threadIdx.x < NT) up[threadIdx.x] = reinterpret_cast<const float*>(p.image + I::scales_offset(p.nsb))[threadIdx.x];
         if (ok && !mbar_wait_bounded(d_full, 0)) {
@@ -667,7 +741,9 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
         named_barrier_sync(1, kWorkers);   // the scale factors are in place
         const bool split = p.ksplit > 1;
         float* part = split ? p.partial + static_cast<size_t>(blockIdx.y) * p.members * p.n : nullptr;
-        const long long row = static_cast<long long>(n0) + row_in_tile;
+        // tile row -> matrix row (interleaved classes for unaligned Q6_K rows, the identity otherwise)
+        const int rows_per_class = kRows / p.row_classes;
+        const long long row = static_cast<long long>(n0) + (row_in_tile % rows_per_class) * p.row_classes + row_in_tile / rows_per_class;
         const int column0 = half * (NT / 2);
 #pragma unroll
         for (int c8 = 0; c8 < NT / 16; ++c8) {
@@ -795,6 +871,7 @@ __global__ void __launch_bounds__(kTmemThreads, NT >= 64 ? 1 : 2) qgemv_tmem_ker
                 }
             }
         }
+        }   // first worker set
     }
 
     // ---------------- teardown: every warp arrives here, then TMEM is released ----------------
@@ -868,14 +945,25 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return cudaErrorNotSupported;
     const unsigned long long row_bytes = static_cast<unsigned long long>(nsb) * P::kSbBytes;
-    CUtensorMap wmap;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes / 2), static_cast<cuuint64_t>(a.n)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(P::kRowPitch / 2), static_cast<cuuint32_t>(kRows)};
-    const cuuint32_t elem[2] = {1, 1};
-    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t*>(a.weights), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
+    int classes = 1;
+    while ((row_bytes * classes) % 16 != 0) classes *= 2;   // 1 for Q4_K / Q5_K; up to 8 for Q6_K
+    WeightMaps wmaps{};
+    for (int c = 0; c < classes; ++c) {
+        const unsigned long long first = static_cast<unsigned long long>(c) * row_bytes, delta = first & 15ull;
+        const unsigned long long class_rows = (static_cast<unsigned long long>(a.n) - c + classes - 1) / classes;
+        if (static_cast<unsigned long long>(a.n) <= static_cast<unsigned long long>(c)) {
+            wmaps.map[c] = wmaps.map[0];   // fewer rows than classes: never addressed with a valid row
+            continue;
+        }
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>((delta + row_bytes) / 2), static_cast<cuuint64_t>(class_rows)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes * classes)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(P::kRowPitch / 2), static_cast<cuuint32_t>(kRows / classes)};
+        const cuuint32_t elem[2] = {1, 1};
+        if (encode(&wmaps.map[c], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint8_t*>(a.weights) + (first - delta), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     TmemParams p{};
     p.x = a.x;
     p.x_bf16 = a.x_bf16 ? 1 : 0;
@@ -900,13 +988,24 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.ksplit = ksplit;
     p.raw_stages = raw_stages;
     p.b_stages = b_stages;
+    p.row_classes = classes;
+    p.row_bytes = static_cast<unsigned int>(row_bytes);
     p.status = a.device_status;
     p.trace = a.trace;
     if (!a.image_ready) {
-        const cudaError_t e = launch_kernel(tmem_image_kernel<NT>, dim3(a.members), dim3(256), 0, a.stream, p);
+        const int cached = a.k <= kImageCacheFloats ? 1 : 0;
+        static int image_device = -1;
+        if (image_device != device) {
+            const cudaError_t attribute = cudaFuncSetAttribute(tmem_image_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                               static_cast<int>(kImageCacheFloats * sizeof(float)));
+            if (attribute != cudaSuccess) return attribute;
+            image_device = device;
+        }
+        const cudaError_t e = launch_kernel(tmem_image_kernel<NT>, dim3(a.members), dim3(256), cached ? static_cast<size_t>(a.k) * sizeof(float) : 0,
+                                            a.stream, p, cached);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(kernel, dim3(tiles, ksplit), dim3(kTmemThreads), smem, a.stream, wmap, p);
+    return launch_kernel(kernel, dim3(tiles, ksplit), dim3(Roles<NT>::kThreads), smem, a.stream, wmaps, p);
 }
 
 template <uint32_t FMT>
@@ -923,7 +1022,7 @@ bool qgemv_tmem_supports(uint32_t value_type, int k, int n, int members, bool x_
     if (value_type != kQ4_K && value_type != kQ5_K && value_type != kQ6_K) return false;
     (void)x_bf16;
     if (members < 1 || members > 64 || k <= 0 || k % kSuperBlock != 0 || n < 1) return false;
-    if (value_type == kQ6_K && (k / kSuperBlock) % 8 != 0) return false;   // rows of 210-byte super-blocks must start on 16-byte boundaries
+    if (value_type == kQ6_K && static_cast<unsigned long long>(k / kSuperBlock) * 210ull > 0xffffffffull) return false;
     return reinterpret_cast<uintptr_t>(weights) % 16 == 0;
 }
 

@@ -56,13 +56,21 @@ def run_gemv(ctx, vt, weight, x_host, n, x_dtype=torch.float32, y_dtype=torch.fl
     return y.float().cpu().numpy().astype(np.float64), x.float().cpu().numpy()
 
 
-def check(vt, w, k, n, y, x_seen, y_bf16=False):
+def check(vt, w, k, n, y, x_seen, y_bf16=False, strict=False):
+    """Task metric |y - ref| / max(|ref|, sqrt(sum (w x)^2)) <= 2e-3 against the f64 product.  `strict` also asks for the
+    stricter denominator max(|ref|, 1e-3 * ||w_row|| * ||x||) (oracle.max_rel_error_strict): it holds on every path that
+    keeps f32-class arithmetic; the two tcgen05 batch kernels round weights to f16 and exceed it on cancelling outputs,
+    which is why their tests do not pass strict=True."""
     ref = oracle.gemv_f64(vt, w, k, n, x_seen)
     scale = oracle.gemv_scale(vt, w, k, n, x_seen)
     err = oracle.max_rel_error(y, ref, scale)
     bound = TOL + (BF16_ROUNDOFF if y_bf16 else 0.0)
     assert np.all(np.isfinite(y)), "kernel left outputs unwritten"
     assert err <= bound, f"max rel err {err:.3e} > {bound:.3e}"
+    if strict:
+        tight = oracle.max_rel_error_strict(y, ref, oracle.row_norms(vt, w, k, n), x_seen)
+        print(f"observed max rel err {err:.2e} (task metric), {tight:.2e} (strict metric)")
+        assert tight <= bound, f"strict max rel err {tight:.3e} > {bound:.3e}"
     return err
 
 
@@ -173,7 +181,7 @@ def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype):
             ctx.set_option("mma_image_members", image_members)
             for members in range(1, 9):
                 y, x_seen = run_gemv(ctx, vt, weight, x[:members], n, x_dtype=x_dtype)
-                check(vt, w, k, n, y, x_seen)
+                check(vt, w, k, n, y, x_seen, strict=True)
                 results[(image_members, members)] = y
     finally:
         ctx.set_option("mma_image_members", 3)
@@ -205,6 +213,22 @@ def test_batch_size_contract_beyond_the_reference_cap(ctx, gemv_path, vt):
     drift = oracle.max_rel_error(nine[:8], eight, scale)
     print(f"bf16 rows 0..7, batch of 9 against batch of 8: max rel difference {drift:.2e}")
     assert 0 < drift <= 2e-3
+
+
+@pytest.mark.parametrize("nsb", [1, 2, 3, 4, 5, 13, 25, 50, 100])
+def test_q6_k_batches_when_rows_do_not_start_on_16_byte_boundaries(ctx, gemv_path, nsb):
+    """Q6_K rows are 210 * K/256 bytes: unless K/256 is a multiple of eight most rows start off the 16-byte boundary
+    tiled TMA needs (the Qwen3-32B shape's ffn_down, K = 25600, and every input-column shard of it).  The batch kernel
+    then reads the matrix as 2, 4 or 8 interleaved matrices; 300 rows leave a ragged last tile."""
+    if gemv_path != 0:
+        pytest.skip("the batch kernel is on the default path only")
+    k, n = 256 * nsb, 300
+    w = synth.random_weight(14, k, n, seed=nsb)
+    weight = upload(ctx, 14, w, k, n)
+    for members in (9, 64):
+        x = synth.random_activations(members, k, seed=members + nsb)
+        y, x_seen = run_gemv(ctx, 14, weight, x, n, x_dtype=torch.bfloat16)
+        check(14, w, k, n, y, x_seen)
 
 
 def test_q6_k_full_range_scales(ctx):
