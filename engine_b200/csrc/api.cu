@@ -23,8 +23,14 @@ struct ribn_ctx {
     cudaStream_t stream = nullptr;
     int sm_count = 0;
     int* device_status = nullptr;   // one word, written by kernels whose bounded waits ran out
-    void* staging = nullptr;        // device scratch for the host-buffer entry points
+    void* staging = nullptr;        // device scratch for the host-buffer entry points: kStagingSlots slots of staging_bytes
     uint64_t staging_bytes = 0;
+    // Host-buffer calls overlap: uploads run on `in_stream`, downloads on `out_stream`, the GEMVs on the context's stream,
+    // tied together per staging slot by events, so that the copies of one call hide behind the compute of its neighbours.
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    cudaEvent_t in_done[4] = {}, compute_done[4] = {}, out_done[4] = {};
+    bool slot_used[4] = {};
+    uint64_t host_calls = 0;
     int variant = 0;                // GEMV tuning variant (ribn_set_option)
     int gemv_path = 0;              // 0 = choose per shape, 1 = f32 CUDA-core kernel only, 2 = integer-dot kernel only
     void* workspace = nullptr;      // device scratch owned by the context (packed activations, split-K partial tiles)
@@ -62,6 +68,7 @@ namespace {
 using ribn::GemvArgs;
 
 constexpr int kTicketCount = 16384;
+constexpr int kStagingSlots = 4;
 constexpr uint64_t kTraceBytes = 64 << 10;
 
 struct Layout {
@@ -687,6 +694,13 @@ void ribn_destroy(ribn_ctx* ctx) {
     if (ctx == nullptr) return;
     DeviceGuard guard(ctx->device);
     if (ctx->staging != nullptr) cudaFree(ctx->staging);
+    for (int i = 0; i < kStagingSlots; ++i) {
+        if (ctx->in_done[i] != nullptr) cudaEventDestroy(ctx->in_done[i]);
+        if (ctx->compute_done[i] != nullptr) cudaEventDestroy(ctx->compute_done[i]);
+        if (ctx->out_done[i] != nullptr) cudaEventDestroy(ctx->out_done[i]);
+    }
+    if (ctx->in_stream != nullptr) cudaStreamDestroy(ctx->in_stream);
+    if (ctx->out_stream != nullptr) cudaStreamDestroy(ctx->out_stream);
     if (ctx->workspace != nullptr) cudaFree(ctx->workspace);
     if (ctx->tickets != nullptr) cudaFree(ctx->tickets);
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
@@ -704,6 +718,7 @@ int ribn_synchronize(ribn_ctx* ctx) {
     if (ctx == nullptr) return RIBN_E_INVALID_ARGUMENT;
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && ctx->out_stream != nullptr) e = cudaStreamSynchronize(ctx->out_stream);   // downloads of host-buffer calls
     if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
     int status = 0;
     e = cudaMemcpy(&status, ctx->device_status, sizeof status, cudaMemcpyDeviceToHost);
@@ -948,13 +963,26 @@ int ribn_reserve_staging(ribn_ctx* ctx, uint64_t bytes) {
     if (bytes <= ctx->staging_bytes) return RIBN_OK;
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && ctx->out_stream != nullptr) e = cudaStreamSynchronize(ctx->out_stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "stream synchronize");
     if (ctx->staging != nullptr) cudaFree(ctx->staging);
     ctx->staging = nullptr;
     ctx->staging_bytes = 0;
-    e = cudaMalloc(&ctx->staging, bytes);
+    bytes = (bytes + 255) & ~255ull;
+    e = cudaMalloc(&ctx->staging, bytes * kStagingSlots);
     if (e != cudaSuccess) return record_cuda(ctx, e, "staging allocation");
     ctx->staging_bytes = bytes;
+    if (ctx->in_stream == nullptr) {
+        e = cudaStreamCreateWithFlags(&ctx->in_stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking);
+        for (int i = 0; i < kStagingSlots && e == cudaSuccess; ++i) {
+            e = cudaEventCreateWithFlags(&ctx->in_done[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->compute_done[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->out_done[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) return record_cuda(ctx, e, "copy streams");
+    }
+    for (bool& used : ctx->slot_used) used = false;
     return RIBN_OK;
 }
 
@@ -983,13 +1011,24 @@ int ribn_gemv_host_async(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweig
                                 fmt("staging buffer holds %" PRIu64 " bytes, this call needs %" PRIu64
                                     " (ribn_reserve_staging)",
                                     ctx->staging_bytes, y_offset + y_bytes)));
-    uint8_t* x_dev = static_cast<uint8_t*>(ctx->staging);
+    // slot of this call; its previous user's download must have left it before the upload overwrites it
+    const int slot = static_cast<int>(ctx->host_calls++ % kStagingSlots);
+    uint8_t* x_dev = static_cast<uint8_t*>(ctx->staging) + static_cast<uint64_t>(slot) * ctx->staging_bytes;
     uint8_t* y_dev = x_dev + y_offset;
-    cudaError_t e = cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, ctx->stream);
+    cudaError_t e = cudaSuccess;
+    if (ctx->slot_used[slot]) e = cudaStreamWaitEvent(ctx->in_stream, ctx->out_done[slot], 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, ctx->in_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(ctx->in_done[slot], ctx->in_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->in_done[slot], 0);
     if (e != cudaSuccess) return record_cuda(ctx, e, "activation upload");
     const int status = enqueue_gemv(ctx, weight, k, n, x_dev, x_dtype, y_dev, y_dtype, members);
+    // whatever happened, the slot's chain of events stays complete: the next user of the slot waits on out_done
+    e = cudaEventRecord(ctx->compute_done[slot], ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ctx->compute_done[slot], 0);
+    if (e == cudaSuccess && status == RIBN_OK) e = cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, ctx->out_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(ctx->out_done[slot], ctx->out_stream);
+    ctx->slot_used[slot] = true;
     if (status != RIBN_OK) return status;
-    e = cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, ctx->stream);
     if (e != cudaSuccess) return record_cuda(ctx, e, "output download");
     return RIBN_OK;
 }

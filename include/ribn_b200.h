@@ -187,10 +187,11 @@ int ribn_gemv_host(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *we
                    const void *x_host, int x_dtype, uint64_t x_len,
                    void *y_host, int y_dtype, uint64_t y_len, uint32_t members);
 
-/* The same without the final synchronisation: upload, GEMV and download are enqueued on the context's stream and
- * the call returns (the reference's own convention: "a call validates, then enqueues on the owner's stream and
- * returns", quantized.rs:357-362).  y_host is valid after ribn_synchronize; x_host must stay untouched until then.
- * Calls may follow one another without waiting: they share the staging buffer in stream order. */
+/* The same without the final synchronisation: the upload runs on a copy stream of the context, the GEMV on the context's
+ * stream, the download on a second copy stream, chained by events over four staging slots -- the copies of one call
+ * overlap the GEMVs of its neighbours -- and the call returns (the reference's own convention: "a call validates, then
+ * enqueues on the owner's stream and returns", quantized.rs:357-362).  y_host is valid after ribn_synchronize; x_host
+ * must stay untouched until then.  Calls may follow one another without waiting. */
 int ribn_gemv_host_async(ribn_ctx *ctx, uint32_t expected_type, const ribn_qweight *weight,
                    const void *x_host, int x_dtype, uint64_t x_len,
                    void *y_host, int y_dtype, uint64_t y_len, uint32_t members);

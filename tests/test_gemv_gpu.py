@@ -307,9 +307,9 @@ def test_host_buffers(ctx):
         own.reserve_staging(1 << 20)
         kernel.execute_host(weight, x, y, members)
         check(13, w, k, n, y.astype(np.float64), x)
-        # enqueue-only variant: three calls back to back through the one staging buffer, one synchronisation
-        xs = [torch.from_numpy(synth.random_activations(members, k, seed=10 + i)).pin_memory() for i in range(3)]
-        ys = [torch.full((members, n), float("nan")).pin_memory() for _ in range(3)]
+        # enqueue-only variant: eleven calls back to back (the four staging slots are reused), one synchronisation
+        xs = [torch.from_numpy(synth.random_activations(members, k, seed=10 + i)).pin_memory() for i in range(11)]
+        ys = [torch.full((members, n), float("nan")).pin_memory() for _ in range(11)]
         for xi, yi in zip(xs, ys):
             kernel.execute_host(weight, xi, yi, members, wait=False)
         own.synchronize()
