@@ -46,6 +46,8 @@ struct ribn_ctx {
     int tc_min_members = 9;         // batches of at least this many rows go to the tcgen05 decode kernel
     int tmem_gemv = 1;              // 1 = Q4_K / Q5_K batches of nine or more rows use the kernel that unpacks the weights into tensor memory
     int mma_gemv = 1;               // 1 = batches of up to eight rows use the half2-unpack + mma.sync kernel where it serves the shape
+    int imma_gemv = 1;              // 1 = up to imma_max_members rows of Q4_K / Q5_K use the integer tensor-core kernel (gemv_imma.cu)
+    int imma_max_members = 8;
     int mma_image_members = 3;      // launches of at least this many rows convert their activations in a pre-pass, fewer inside the kernel
     int mma_stages = 0;             // ring depth of that kernel, 0 = as many stages as fit
     int mma_resident = 0;           // CTAs per SM its shared-memory plan allows for, 0 = up to three
@@ -364,10 +366,60 @@ bool mma_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t
     return ribn::gemv_mma_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), per_launch, w->data);
 }
 
+// `images_made` (fused calls: shared by the projections of one input): bit 0 = the f16 image of this x is in the
+// workspace, bit 1 = the int8 image is (the two narrow kernels keep different images, side by side).
 int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
-                float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready, bool shared_image = false) {
+                float eps, void* y, int y_dtype, uint32_t members, bool accumulate, unsigned* images_made, bool shared_image = false) {
     const bool x_bf16 = x_dtype == RIBN_BF16;
     const uint64_t x_row_bytes = k * (mode == 2 ? 2 : 1) * dtype_bytes(x_dtype);
+    unsigned none_made = 0;
+    if (images_made == nullptr) images_made = &none_made;
+    // Q4_K / Q5_K: the integer tensor-core kernel, eight rows per launch (quants go to the instruction as they are).
+    const uint32_t per_launch = members < 8 ? members : 8;
+    if (ctx->imma_gemv != 0 && (members <= static_cast<uint32_t>(ctx->imma_max_members) || members > 8) &&
+        ribn::gemv_imma_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), static_cast<int>(per_launch), w->data)) {
+        // its images follow the ones the f16 kernel would keep for the same call
+        uint64_t offset = static_cast<uint64_t>((members + 7) / 8) * ribn::gemv_mma_image_bytes(static_cast<int>(per_launch), static_cast<int>(k), 2);
+        for (uint32_t m0 = 0; m0 < members; m0 += 8) {
+            ribn::MmaGemvArgs a{};
+            a.weights = static_cast<const uint8_t*>(w->data);
+            a.value_type = w->value_type;
+            a.k = static_cast<int>(k);
+            a.n = static_cast<int>(n);
+            a.members = static_cast<int>(members - m0 < 8 ? members - m0 : 8);
+            a.x = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(m0) * x_row_bytes;
+            a.x_bf16 = x_bf16;
+            a.mode = mode;
+            a.norm_weight = norm_weight;
+            a.eps = eps;
+            a.y = static_cast<uint8_t*>(y) + static_cast<uint64_t>(m0) * n * dtype_bytes(y_dtype);
+            a.y_bf16 = y_dtype == RIBN_BF16;
+            a.accumulate = accumulate;
+            a.stages = ctx->mma_stages;
+            a.resident = ctx->mma_resident;
+            a.grid_ctas = ctx->mma_ctas;
+            a.device_status = ctx->device_status;
+            a.sm_count = ctx->sm_count;
+            a.stream = ctx->stream;
+            const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
+                              (shared_image && ctx->mma_image_members <= 8) || (mode == 2 && ctx->mma_image_members <= 8);
+            const uint64_t image_bytes = ribn::gemv_imma_image_bytes(a.members, a.k);
+            if (wide && offset + image_bytes <= ctx->workspace_bytes) {
+                void* image = static_cast<uint8_t*>(ctx->workspace) + offset;
+                offset += image_bytes;
+                if ((*images_made & 2u) == 0) {
+                    const cudaError_t e = ribn::launch_gemv_imma_image(a, image);
+                    if (e != cudaSuccess) return record_cuda(ctx, e, "activation image launch");
+                }
+                a.image = image;
+            }
+            const cudaError_t e = ribn::launch_gemv_imma(a);
+            if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
+        }
+        *images_made |= 2u;
+        return RIBN_OK;
+    }
+    const bool image_ready = (*images_made & 1u) != 0;
     uint64_t image_offset = 0;
     for (uint32_t m0 = 0; m0 < members; m0 += 8) {
         ribn::MmaGemvArgs a{};
@@ -397,7 +449,8 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
         // about four slices per warp on, the conversion is worth a launch of its own (measured: two rows over K = 12288).
         // Several projections of one normalised or gated input share the image: the norm / activation runs once.
         const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
-                          (shared_image && ctx->mma_image_members <= 8);
+                          (shared_image && ctx->mma_image_members <= 8) ||
+                          (mode == 2 && ctx->mma_image_members <= 8);   // silu(gate) * up once, not once per CTA (measured: K = 12288, one row)
         if (wide && image_offset + image_bytes <= ctx->workspace_bytes) {
             void* image = static_cast<uint8_t*>(ctx->workspace) + image_offset;
             image_offset += image_bytes;
@@ -410,6 +463,7 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
         const cudaError_t e = ribn::launch_gemv_mma(a);
         if (e != cudaSuccess) return record_cuda(ctx, e, "GEMV launch");
     }
+    if (image_offset != 0) *images_made |= 1u;
     return RIBN_OK;
 }
 
@@ -443,7 +497,7 @@ int enqueue_gemv(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
         return enqueue_tc(ctx, w, k, n, x, x_dtype, y, y_dtype, members, norm_weight, eps);
     // Up to eight rows per launch (and wider f32 batches, in groups of eight): half2 unpack + mma.sync.
     if (mma)
-        return enqueue_mma(ctx, w, k, n, x, x_dtype, norm_weight != nullptr ? 1 : 0, norm_weight, eps, y, y_dtype, members, false, false);
+        return enqueue_mma(ctx, w, k, n, x, x_dtype, norm_weight != nullptr ? 1 : 0, norm_weight, eps, y, y_dtype, members, false, nullptr);
     // Path 1: integer-dot kernel.  The activations (normalised first when norm_weight is given) are
     // packed once into the context workspace, then consumed four member rows per launch (the
     // weights stay in L2 between the launches of one call).
@@ -552,9 +606,10 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
     }
     if (all_mma) {
         const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
+        unsigned images_made = 0;
         for (uint32_t j = 0; j < job_count; ++j) {
             const int rc = enqueue_mma(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
-                                       jobs[j].accumulate != 0, j > 0, job_count > 1 && mode != 0);
+                                       jobs[j].accumulate != 0, &images_made, job_count > 1 && mode != 0);
             if (rc != RIBN_OK) return rc;
         }
         return RIBN_OK;
@@ -816,6 +871,14 @@ int ribn_set_option(ribn_ctx* ctx, const char* name, int64_t value) {
     }
     if (std::strcmp(name, "tmem_gemv") == 0 && (value == 0 || value == 1)) {
         ctx->tmem_gemv = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "imma_gemv") == 0 && (value == 0 || value == 1)) {
+        ctx->imma_gemv = static_cast<int>(value);
+        return RIBN_OK;
+    }
+    if (std::strcmp(name, "imma_max_members") == 0 && value >= 1 && value <= 8) {
+        ctx->imma_max_members = static_cast<int>(value);
         return RIBN_OK;
     }
     if (std::strcmp(name, "mma_gemv") == 0 && (value == 0 || value == 1)) {

@@ -124,6 +124,12 @@ size_t gemv_mma_image_bytes(int members, int k, int planes);
 cudaError_t launch_gemv_mma_image(const MmaGemvArgs& args, void* image);
 cudaError_t launch_gemv_mma(const MmaGemvArgs& args);
 
+// The same call on the integer tensor-core instruction (gemv_imma.cu): Q4_K / Q5_K, 1..8 member rows; `planes` is unused.
+bool gemv_imma_supports(uint32_t value_type, int k, int n, int members, const void* weights);
+size_t gemv_imma_image_bytes(int members, int k);
+cudaError_t launch_gemv_imma_image(const MmaGemvArgs& args, void* image);
+cudaError_t launch_gemv_imma(const MmaGemvArgs& args);
+
 // tcgen05 GEMV with the weight operand unpacked into tensor memory (qgemv_tmem.cu): Q4_K / Q5_K, up to 8 f32 or
 // 16 bf16 member rows per launch.
 struct TmemGemvArgs {

@@ -287,9 +287,9 @@ class CudaDenseDecode:
         jobs = [(self.weights.matrices[name], y, accumulate) for name, y in names_outputs]
         gemv_fused(self.context, jobs, x, self.members, norm, self.geometry.eps, swiglu)
         # one launch per projection, plus the activation pre-pass where one runs (from three members on, for wide
-        # two-member inputs, and whenever several projections share a normalised or gated input)
-        shared = len(jobs) > 1 and (norm is not None or swiglu)
-        prepass = self.members >= 3 or shared or (self.members == 2 and x.shape[-1] // (2 if swiglu else 1) // 256 > 24)
+        # two-member inputs, for gated inputs, and whenever several projections share a normalised input)
+        shared = len(jobs) > 1 and norm is not None
+        prepass = self.members >= 3 or shared or swiglu or (self.members == 2 and x.shape[-1] // 256 > 24)
         self.launches_per_step += len(jobs) + (1 if prepass else 0)
 
     def _all_reduce(self, t: torch.Tensor) -> None:

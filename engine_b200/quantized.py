@@ -131,6 +131,7 @@ class CudaQuantizedWeight:
         self._spec = spec
         self._value_type = int(value_type)
         self._encoded = encoded
+        self._descriptor = None
 
     def spec(self) -> WeightTensorSpec:
         return self._spec
@@ -145,8 +146,11 @@ class CudaQuantizedWeight:
         return self._encoded
 
     def descriptor(self) -> QWeight:
-        dims = (ctypes.c_uint64 * 4)(*(list(self._spec.dimensions)[:4] + [0] * (4 - min(4, len(self._spec.dimensions)))))
-        return QWeight(self._encoded.data_ptr(), self._encoded.numel(), self._value_type, len(self._spec.dimensions), dims)
+        if self._descriptor is None:   # the bytes never move or change once resident, so neither does their description
+            dims = (ctypes.c_uint64 * 4)(*(list(self._spec.dimensions)[:4] + [0] * (4 - min(4, len(self._spec.dimensions)))))
+            self._descriptor = QWeight(self._encoded.data_ptr(), self._encoded.numel(), self._value_type,
+                                       len(self._spec.dimensions), dims)
+        return self._descriptor
 
 
 class CudaWeightStore:
