@@ -288,7 +288,7 @@ class CudaDenseDecode:
         gemv_fused(self.context, jobs, x, self.members, norm, self.geometry.eps, swiglu)
         # one launch per projection, plus the activation pre-pass where one runs (from three members on, for wide
         # two-member inputs, for gated inputs, and whenever several projections share a normalised input)
-        shared = len(jobs) > 1 and norm is not None
+        shared = len(jobs) > 1 and norm is not None and self.members >= 2
         prepass = self.members >= 3 or shared or swiglu or (self.members == 2 and x.shape[-1] // 256 > 24)
         self.launches_per_step += len(jobs) + (1 if prepass else 0)
 
@@ -308,7 +308,7 @@ class CudaDenseDecode:
         if i in self.qk_weights:
             jobs = [(self.qk_weights[i], self.qk, False), (w.matrices[f"blk.{i}.attn_v"], self.v, False)]
             gemv_fused(self.context, jobs, self.hidden, self.members, w.vectors[f"blk.{i}.attn_norm"], g.eps, False)
-            self.launches_per_step += 3
+            self.launches_per_step += 2   # one row: every CTA normalises and converts it itself, no pre-pass
         else:
             self._fused([(f"blk.{i}.attn_q", self.q), (f"blk.{i}.attn_k", self.k), (f"blk.{i}.attn_v", self.v)], self.hidden,
                         norm=w.vectors[f"blk.{i}.attn_norm"])
