@@ -84,6 +84,8 @@ class GemvJob(ctypes.Structure):
         ("y_dtype", ctypes.c_int),
         ("y_len", ctypes.c_uint64),
         ("accumulate", ctypes.c_int),
+        ("split_rows", ctypes.c_uint64),
+        ("y2_device", ctypes.c_void_p),
     ]
 
 

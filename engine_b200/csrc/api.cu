@@ -325,7 +325,8 @@ bool tmem_serves(const ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_
 }
 
 int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, const void* x, int x_dtype, int mode, const float* norm_weight,
-                 float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready = false) {
+                 float eps, void* y, int y_dtype, uint32_t members, bool accumulate, bool image_ready = false, void* y2 = nullptr,
+                 uint64_t n_first = 0) {
     ribn::TmemGemvArgs a{};
     a.weights = static_cast<const uint8_t*>(w->data);
     a.value_type = w->value_type;
@@ -337,6 +338,8 @@ int enqueue_tmem(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, c
     a.norm_weight = norm_weight;
     a.eps = eps;
     a.y = y;
+    a.y2 = y2;
+    a.n_first = static_cast<int>(n_first);
     a.y_bf16 = y_dtype == RIBN_BF16;
     a.accumulate = accumulate;
     a.members = static_cast<int>(members);
@@ -573,13 +576,48 @@ int enqueue_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count, 
         all_tc = all_tc && ribn::qgemm_tc_supports(jobs[j].weight->value_type, static_cast<int>(k));
         all_dp4a = all_dp4a && ribn::gemv_dp4a_fits(jobs[j].weight->value_type, static_cast<int>(k), members_per_launch);
     }
-    bool all_tmem = true;
-    for (uint32_t j = 0; j < job_count; ++j) all_tmem = all_tmem && tmem_serves(ctx, jobs[j].weight, k, ns[j], members, x_dtype);
+    bool all_tmem = true, any_split = false;
+    for (uint32_t j = 0; j < job_count; ++j) {
+        all_tmem = all_tmem && tmem_serves(ctx, jobs[j].weight, k, ns[j], members, x_dtype);
+        any_split = any_split || jobs[j].split_rows != 0;
+    }
+    if (any_split && !all_tmem) {
+        // Only the batch kernel writes two outputs from one launch; elsewhere the two projections of such a weight run as
+        // two jobs over its two row ranges (contiguous byte ranges of the encoded tensor).
+        ribn_gemv_job parts[2 * RIBN_MAX_FUSED_JOBS];
+        ribn_qweight views[2 * RIBN_MAX_FUSED_JOBS];
+        uint64_t part_ns[2 * RIBN_MAX_FUSED_JOBS];
+        uint32_t count = 0;
+        for (uint32_t j = 0; j < job_count; ++j) {
+            if (jobs[j].split_rows == 0) {
+                parts[count] = jobs[j];
+                part_ns[count++] = ns[j];
+                continue;
+            }
+            const uint64_t row_bytes = jobs[j].weight->encoded_bytes / ns[j];
+            for (int half = 0; half < 2; ++half) {
+                const uint64_t first = half == 0 ? 0 : jobs[j].split_rows, rows = half == 0 ? jobs[j].split_rows : ns[j] - jobs[j].split_rows;
+                views[count] = *jobs[j].weight;
+                views[count].data = static_cast<const uint8_t*>(jobs[j].weight->data) + first * row_bytes;
+                views[count].encoded_bytes = rows * row_bytes;
+                views[count].dimensions[1] = rows;
+                parts[count] = jobs[j];
+                parts[count].weight = &views[count];
+                parts[count].y_device = half == 0 ? jobs[j].y_device : jobs[j].y2_device;
+                parts[count].y_len = rows * members;
+                parts[count].split_rows = 0;
+                parts[count].y2_device = nullptr;
+                part_ns[count++] = rows;
+            }
+        }
+        return enqueue_fused(ctx, parts, count, part_ns, k, x, x_dtype, norm_weight, eps, members, swiglu);
+    }
     if (all_tmem) {
         const int mode = swiglu ? 2 : (norm_weight != nullptr ? 1 : 0);
         for (uint32_t j = 0; j < job_count; ++j) {
             const int rc = enqueue_tmem(ctx, jobs[j].weight, k, ns[j], x, x_dtype, mode, norm_weight, eps, jobs[j].y_device, jobs[j].y_dtype, members,
-                                        jobs[j].accumulate != 0, /*image_ready=*/j > 0);
+                                        jobs[j].accumulate != 0, /*image_ready=*/j > 0, jobs[j].split_rows != 0 ? jobs[j].y2_device : nullptr,
+                                        jobs[j].split_rows);
             if (rc != RIBN_OK) return rc;
         }
         return RIBN_OK;
@@ -1328,6 +1366,9 @@ int ribn_gemv_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count
         Failure f = validate_gemv(jobs[j].weight, jobs[j].expected_type, x_dtype, x_expected, jobs[j].y_dtype, jobs[j].y_len, members, &kj,
                                   &ns[j]);
         if (f.status != RIBN_OK) return record(ctx, f);
+        if (jobs[j].split_rows != 0 && (jobs[j].split_rows % 128 != 0 || jobs[j].split_rows >= ns[j] || jobs[j].y2_device == nullptr))
+            return record(ctx, fail(RIBN_E_INVALID_ARGUMENT,
+                                    fmt("projection %u: split_rows must be a multiple of 128 below N = %" PRIu64 " with a second output", j, ns[j])));
         if (j == 0) k = kj;
         if (kj != k)
             return record(ctx, fail(RIBN_E_INPUT_LENGTH, fmt("projection %u has input size %" PRIu64 ", the first has %" PRIu64, j, kj, k), k, kj));
@@ -1341,6 +1382,7 @@ int ribn_gemv_fused(ribn_ctx* ctx, const ribn_gemv_job* jobs, uint32_t job_count
     for (uint32_t j = 0; j < job_count && f.status == RIBN_OK; ++j) {
         f = check_device_pointer(ctx, jobs[j].weight->data, "weight");
         if (f.status == RIBN_OK) f = check_device_pointer(ctx, jobs[j].y_device, "output");
+        if (f.status == RIBN_OK && jobs[j].split_rows != 0) f = check_device_pointer(ctx, jobs[j].y2_device, "second output");
     }
     if (f.status != RIBN_OK) return record(ctx, f);
     return enqueue_fused(ctx, jobs, job_count, ns, k, x_device, x_dtype, norm_weight_device, eps, members, swiglu);

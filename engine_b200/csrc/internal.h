@@ -141,7 +141,9 @@ struct TmemGemvArgs {
     int mode;                 // 0 plain, 1 RMSNorm with norm_weight / eps first, 2 silu(gate) * up of [gate | up] rows
     const float* norm_weight;
     float eps;
-    void* y;                  // [members][n]
+    void* y;                  // [members][n], or with y2: rows below n_first as [members][n_first]
+    void* y2;                 // null, or where rows n_first.. go, as [members][n - n_first] (n_first a multiple of 128)
+    int n_first;
     bool y_bf16;
     bool accumulate;          // y += W x
     int members;

@@ -94,7 +94,9 @@ struct TmemParams {
     const float* norm_weight;
     float eps;
     uint8_t* image;             // the activations as MMA tiles (layout below), written by the pre-pass
-    void* y;
+    void* y;                    // rows below n_first: [members][n_first]
+    void* y2;                   // rows from n_first on: [members][n - n_first] (n_first = n: unused)
+    int n_first;
     int y_bf16;
     int accumulate;
     float* partial;             // split-K scratch [ksplit][members][n]
@@ -107,6 +109,17 @@ struct TmemParams {
     int* status;
     long long* trace;           // diagnostics (builds with -DRIBN_TRACE): wall-clock stamps of CTA (0, 0), or null
 };
+
+// Where output (member m, matrix row `row`) lives: a call may deliver its first n_first rows and the rest to two
+// buffers (two projections stored as one matrix).  n_first is a multiple of four, so groups of four rows stay together.
+__device__ __forceinline__ void* output_slot(const TmemParams& p, int m, long long row, size_t& index) {
+    if (row < p.n_first) {
+        index = static_cast<size_t>(m) * p.n_first + row;
+        return p.y;
+    }
+    index = static_cast<size_t>(m) * (p.n - p.n_first) + (row - p.n_first);
+    return p.y2;
+}
 
 // trace[role * 32 + event] = globaltimer (ns) of CTA (0, 0); roles: 0 producer, 1 issuer, 2 worker warp 0, 3 worker warp 4.
 __device__ __forceinline__ void stamp(const TmemParams& p, int role, int event) {
@@ -762,15 +775,18 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
                 const int m = per_member == 2 ? column >> 1 : column;
                 if (m < p.members && row < p.n) {
                     const float value = (per_member == 2 ? v[c] + v[c + 1 < 8 ? c + 1 : c] : v[c]) * up[m];
-                    const size_t o = static_cast<size_t>(m) * p.n + row;
                     if (split) {
-                        part[o] = value;
-                    } else if (p.y_bf16) {
-                        const float old = p.accumulate ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o]) : 0.0f;
-                        static_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(value + old);
+                        part[static_cast<size_t>(m) * p.n + row] = value;
                     } else {
-                        const float old = p.accumulate ? static_cast<const float*>(p.y)[o] : 0.0f;
-                        static_cast<float*>(p.y)[o] = value + old;
+                        size_t o;
+                        void* y = output_slot(p, m, row, o);
+                        if (p.y_bf16) {
+                            const float old = p.accumulate ? __bfloat162float(static_cast<const __nv_bfloat16*>(y)[o]) : 0.0f;
+                            static_cast<__nv_bfloat16*>(y)[o] = __float2bfloat16_rn(value + old);
+                        } else {
+                            const float old = p.accumulate ? static_cast<const float*>(y)[o] : 0.0f;
+                            static_cast<float*>(y)[o] = value + old;
+                        }
                     }
                 }
             }
@@ -850,14 +866,16 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
                             for (int r = 0; r < 4; ++r)
                                 if (row + r < p.n) sum[r] += __ldcg(p.partial + z * plane + o + r);
                     }
+                    size_t out;
+                    void* y = output_slot(p, m, row, out);
                     for (int r = 0; r < 4; ++r) {
                         if (row + r >= p.n) break;
                         if (p.y_bf16) {
-                            if (p.accumulate) sum[r] += __bfloat162float(static_cast<const __nv_bfloat16*>(p.y)[o + r]);
-                            static_cast<__nv_bfloat16*>(p.y)[o + r] = __float2bfloat16_rn(sum[r]);
+                            if (p.accumulate) sum[r] += __bfloat162float(static_cast<const __nv_bfloat16*>(y)[out + r]);
+                            static_cast<__nv_bfloat16*>(y)[out + r] = __float2bfloat16_rn(sum[r]);
                         } else {
-                            if (p.accumulate) sum[r] += static_cast<const float*>(p.y)[o + r];
-                            static_cast<float*>(p.y)[o + r] = sum[r];
+                            if (p.accumulate) sum[r] += static_cast<const float*>(y)[out + r];
+                            static_cast<float*>(y)[out + r] = sum[r];
                         }
                     }
                 }
@@ -972,6 +990,8 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
     p.eps = a.eps;
     p.image = image;
     p.y = a.y;
+    p.y2 = a.y2;
+    p.n_first = a.y2 != nullptr ? a.n_first : a.n;
     p.y_bf16 = a.y_bf16 ? 1 : 0;
     p.accumulate = a.accumulate ? 1 : 0;
     p.partial = partial;

@@ -87,16 +87,21 @@ class CudaDenseOps:
 
 def gemv_fused(context: RibnContext, jobs, x: torch.Tensor, members: int, norm: torch.Tensor | None = None, eps: float = 0.0,
                swiglu: bool = False) -> None:
-    """ribn_gemv_fused: `jobs` is a list of (weight, output, accumulate); one activation pre-pass serves them all."""
+    """ribn_gemv_fused: `jobs` is a list of (weight, output, accumulate[, second output]); one activation pre-pass serves
+    them all.  With a second output the weight holds two projections one after the other (split_rows of the C struct)."""
     array = (_lib.GemvJob * len(jobs))()
-    descriptors = [weight.descriptor() for weight, _, _ in jobs]   # kept alive until the call returns
-    for slot, descriptor, (weight, y, accumulate) in zip(array, descriptors, jobs):
+    descriptors = [job[0].descriptor() for job in jobs]   # kept alive until the call returns
+    for slot, descriptor, job in zip(array, descriptors, jobs):
+        weight, y, accumulate = job[:3]
+        second = job[3] if len(job) > 3 else None   # a weight that holds two projections: the second one's output
         slot.expected_type = 0
         slot.weight = ctypes.pointer(descriptor)
         slot.y_device = y.data_ptr()
         slot.y_dtype = _lib.RIBN_F32 if y.dtype == torch.float32 else _lib.RIBN_BF16
-        slot.y_len = y.numel()
+        slot.y_len = y.numel() + (second.numel() if second is not None else 0)
         slot.accumulate = 1 if accumulate else 0
+        slot.split_rows = y.numel() // members if second is not None else 0
+        slot.y2_device = second.data_ptr() if second is not None else None
     context.check(context._lib.ribn_gemv_fused(context.handle, array, len(jobs), x.data_ptr(),
                                                _lib.RIBN_F32 if x.dtype == torch.float32 else _lib.RIBN_BF16, x.numel(),
                                                norm.data_ptr() if norm is not None else None, norm.numel() if norm is not None else 0, eps,
@@ -119,7 +124,8 @@ class DenseWeights:
 
     def bytes_per_step(self) -> int:
         """Encoded weight bytes one decode step streams: every matrix once, except the embedding (one row per member)."""
-        return sum(w.encoded_bytes() for name, w in self.matrices.items() if name != "token_embd")
+        # attn_qk holds the bytes attn_q and attn_k are views of
+        return sum(w.encoded_bytes() for name, w in self.matrices.items() if name != "token_embd" and not name.endswith(".attn_qk"))
 
 
 def local_shapes(geometry: DenseGeometry, world: int, rank: int) -> dict:
@@ -252,16 +258,23 @@ class CudaDenseDecode:
         self.tokens = torch.zeros(m, dtype=torch.int32, device=dev)       # u32 on the device side
         self.positions = torch.zeros(m, dtype=torch.int32, device=dev)
         self.hidden = torch.zeros(m, g.hidden, **f32)
-        # One sequence: q and k projections of the same format run as one GEMV over their concatenated rows
-        # ([q | k] is then contiguous in the output, which the one-member layout of q and k allows).
+        # q and k projections of the same format are stored as one matrix (q rows, then k rows) and run as one GEMV:
+        # for one sequence [q | k] is contiguous in the output; batches name the second output (split_rows).
+        # attn_q and attn_k stay available as views of the joined bytes (the prefill GEMM uses them).
         q_dim, k_dim = s["q_heads"] * g.head_dim, s["kv_heads"] * g.head_dim
         self.qk_weights = {}
-        if m == 1:
-            for i in range(g.layers):
-                wq, wk = weights.matrices.get(f"blk.{i}.attn_q"), weights.matrices.get(f"blk.{i}.attn_k")
-                if wq is not None and wk is not None and wq.value_type() == wk.value_type():
-                    joined = torch.cat([wq.encoded_data(), wk.encoded_data()])
-                    self.qk_weights[i] = CudaQuantizedWeight(WeightTensorSpec.new(f"blk.{i}.attn_qk", [g.hidden, q_dim + k_dim]), wq.value_type(), joined)
+        for i in range(g.layers):
+            wq, wk = weights.matrices.get(f"blk.{i}.attn_q"), weights.matrices.get(f"blk.{i}.attn_k")
+            joined = weights.matrices.get(f"blk.{i}.attn_qk")
+            if joined is None and wq is not None and wk is not None and wq.value_type() == wk.value_type() and q_dim % 128 == 0:
+                data = torch.cat([wq.encoded_data(), wk.encoded_data()])
+                joined = CudaQuantizedWeight(WeightTensorSpec.new(f"blk.{i}.attn_qk", [g.hidden, q_dim + k_dim]), wq.value_type(), data)
+                weights.matrices[f"blk.{i}.attn_qk"] = joined
+                q_bytes = wq.encoded_bytes()
+                weights.matrices[f"blk.{i}.attn_q"] = CudaQuantizedWeight(wq.spec(), wq.value_type(), data[:q_bytes])
+                weights.matrices[f"blk.{i}.attn_k"] = CudaQuantizedWeight(wk.spec(), wk.value_type(), data[q_bytes:])
+            if joined is not None:
+                self.qk_weights[i] = joined
         self.qk = torch.zeros(m, q_dim + k_dim, **f32)
         self.q = self.qk[:, :q_dim] if m == 1 else torch.zeros(m, q_dim, **f32)
         self.k = self.qk[:, q_dim:] if m == 1 else torch.zeros(m, k_dim, **f32)
@@ -306,9 +319,12 @@ class CudaDenseDecode:
         g, s, w = self.geometry, self.shapes, self.weights
         parallel = self.group is not None and self.world > 1
         if i in self.qk_weights:
-            jobs = [(self.qk_weights[i], self.qk, False), (w.matrices[f"blk.{i}.attn_v"], self.v, False)]
-            gemv_fused(self.context, jobs, self.hidden, self.members, w.vectors[f"blk.{i}.attn_norm"], g.eps, False)
-            self.launches_per_step += 2   # one row: every CTA normalises and converts it itself, no pre-pass
+            qk_job = (self.qk_weights[i], self.qk, False) if self.members == 1 else (self.qk_weights[i], self.q, False, self.k)
+            gemv_fused(self.context, [qk_job, (w.matrices[f"blk.{i}.attn_v"], self.v, False)], self.hidden, self.members,
+                       w.vectors[f"blk.{i}.attn_norm"], g.eps, False)
+            # one row: every CTA normalises and converts it itself; from two rows on one pre-pass serves the launches,
+            # and only the batch kernel (nine rows and more) writes q and k from one launch
+            self.launches_per_step += 2 if self.members == 1 else (3 if self.members >= 9 else 4)
         else:
             self._fused([(f"blk.{i}.attn_q", self.q), (f"blk.{i}.attn_k", self.k), (f"blk.{i}.attn_v", self.v)], self.hidden,
                         norm=w.vectors[f"blk.{i}.attn_norm"])

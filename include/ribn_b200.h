@@ -245,6 +245,7 @@ int ribn_noalloc_status(int device, void *cuda_stream);
  *   GEMV -> residual_add               job.accumulate = 1: y += W x (model_ops.rs:600-610)
  *   silu_mul -> down GEMV              RIBN_FUSED_SWIGLU: x is [members][2K], rows [gate | up], the operand is
  *                                      silu(gate) * up (model_ops.rs:316-328)
+ *   q and k (any two projections of one format) stored as one matrix: one launch, two outputs (split_rows)
  * All jobs share K; each is validated like ribn_gemv before anything is launched.  Served by the integer-dot
  * kernel (1..4 member rows per launch) and the tensor-core decode kernel; shapes that only the f32 kernel
  * serves are refused with RIBN_E_INVALID_ARGUMENT (use the separate calls). */
@@ -255,6 +256,9 @@ typedef struct ribn_gemv_job {
     int y_dtype;
     uint64_t y_len;
     int accumulate;              /* 0: y = W x;  1: y += W x */
+    uint64_t split_rows;         /* 0, or a multiple of 128 below N: the weight holds two projections, one after the other */
+    void* y2_device;             /* split_rows != 0: rows [0, split_rows) go to y_device as [members][split_rows], rows
+                                  * [split_rows, N) to y2_device as [members][N - split_rows]; y_len stays members * N */
 } ribn_gemv_job;
 #define RIBN_MAX_FUSED_JOBS 8u
 #define RIBN_FUSED_SWIGLU 1u

@@ -298,6 +298,40 @@ def test_gemv_fused_equals_the_separate_calls(ctx, members, x_dtype):
     assert e.value.kind == "OutputLength"
 
 
+# ---- one stored matrix, two projections: the batch kernel writes both outputs from one launch, the narrow kernels run the
+# two row ranges as two jobs; either way the results are those of the two projections run separately
+@pytest.mark.parametrize("members,x_dtype", [(1, torch.float32), (4, torch.bfloat16), (16, torch.bfloat16), (64, torch.bfloat16)])
+@pytest.mark.parametrize("vt", [12, 14])
+def test_gemv_fused_two_outputs_from_one_matrix(ctx, members, x_dtype, vt):
+    k, n_first, n_second = 1024, 256, 136
+    rng = np.random.default_rng(100 + members)
+    w_first = synth.random_weight(vt, k, n_first, seed=11)
+    w_second = synth.random_weight(vt, k, n_second, seed=12)
+    upload = lambda w, n: engine_b200.CudaQuantizedWeight(engine_b200.WeightTensorSpec.new("w", [k, n]), vt, device(ctx, w))
+    joined = upload(np.concatenate([w_first, w_second]), n_first + n_second)
+    x = device(ctx, rng.standard_normal((members, k)).astype(np.float32) * 2, x_dtype)
+    gain = (1 + 0.02 * rng.standard_normal(k)).astype(np.float32)
+    y1 = torch.full((members, n_first), float("nan"), device=ctx.device)
+    y2 = torch.full((members, n_second), float("nan"), device=ctx.device)
+    decode.gemv_fused(ctx, [(joined, y1, False, y2)], x, members, norm=device(ctx, gain), eps=1e-6)
+    ctx.synchronize()
+    z1, z2 = torch.empty_like(y1), torch.empty_like(y2)
+    decode.gemv_fused(ctx, [(upload(w_first, n_first), z1, False), (upload(w_second, n_second), z2, False)], x, members, norm=device(ctx, gain), eps=1e-6)
+    ctx.synchronize()
+    assert torch.equal(y1, z1) and torch.equal(y2, z2)
+    x_seen = oracle.rms_norm(x.float().cpu().numpy(), gain, 1e-6)
+    for w, n, y in ((w_first, n_first, y1), (w_second, n_second, y2)):
+        err = oracle.max_rel_error(y.cpu().numpy().astype(np.float64), oracle.gemv_f64(vt, w, k, n, x_seen), oracle.gemv_scale(vt, w, k, n, x_seen))
+        assert err <= 2e-3
+    # accumulate applies to both outputs
+    decode.gemv_fused(ctx, [(joined, y1, True, y2)], x, members, norm=device(ctx, gain), eps=1e-6)
+    ctx.synchronize()
+    assert torch.allclose(y1, 2 * z1, rtol=1e-6, atol=0) and torch.allclose(y2, 2 * z2, rtol=1e-6, atol=0)
+    with pytest.raises(engine_b200.CudaQuantizedKernelError) as e:   # split_rows = 100: not a multiple of 128
+        decode.gemv_fused(ctx, [(joined, y1[:, :100].contiguous(), False, torch.empty(members, n_first + n_second - 100, device=ctx.device))], x, members)
+    assert e.value.kind == "InvalidArgument"
+
+
 # ---- the decode loop on a small random model
 def damp_block_scales(encoded: np.ndarray, vt: int, factor: float) -> np.ndarray:
     """Multiplies the f16 super-block scales of an encoded tensor (the generator's weights have a gain of hundreds
