@@ -60,6 +60,10 @@
 namespace ribn {
 namespace {
 
+// Upper bound of one suspended poll of an mbarrier wait: a waiting thread wakes when the phase completes, and until then
+// takes no issue slots from the threads that unpack.
+constexpr uint32_t kWaitHintNs = 1000u;
+
 constexpr int kRows = 128;                 // weight rows per CTA = UMMA M = TMEM lanes
 constexpr int kWorkerWarps = 8;
 constexpr int kWorkers = kWorkerWarps * 32;
@@ -530,7 +534,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
             bool ok = true;
             auto issue_raw = [&](int i) {
                 const int s = i % p.raw_stages;
-                if (i >= p.raw_stages && !mbar_wait_bounded(&raw_empty[s], ((i / p.raw_stages) - 1) & 1)) return false;
+                if (i >= p.raw_stages && !mbar_wait_bounded_hint(&raw_empty[s], ((i / p.raw_stages) - 1) & 1, kWaitHintNs)) return false;
                 mbar_arrive_expect_tx(&raw_full[s], P::kRawStageBytes);
                 if constexpr (FMT == kQ6_K) {
                     // x in 16-bit elements: the super-block's first byte within the class's rows, rounded down to 16 bytes
@@ -548,7 +552,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
             };
             auto issue_b = [&](int i) {
                 const int s = i % p.b_stages;
-                if (i >= p.b_stages && !mbar_wait_bounded(&b_empty[s], ((i / p.b_stages) - 1) & 1)) return false;
+                if (i >= p.b_stages && !mbar_wait_bounded_hint(&b_empty[s], ((i / p.b_stages) - 1) & 1, kWaitHintNs)) return false;
                 mbar_arrive_expect_tx(&b_full[s], I::kStageBytes);
                 const uint8_t* src = p.image + static_cast<size_t>(sb_begin + i) * I::kStageBytes;
                 uint8_t* dst = b_ring + static_cast<size_t>(s) * I::kStageBytes;
@@ -583,7 +587,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
         bool ok = true;
         for (int i = 0; i < local_sb && ok; ++i) {
             const int bs = i % p.b_stages;
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&b_full[bs], (i / p.b_stages) & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded_hint(&b_full[bs], (i / p.b_stages) & 1, kWaitHintNs));
             if (!ok) break;
             if (i < 4 && which == 0) stamp(p, 1, i * 4);
             const uint64_t desc_b0 = umma_smem_desc_sw128(smem_addr(b_ring + static_cast<size_t>(bs) * I::kStageBytes));
@@ -591,7 +595,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
                 const int j = which * 2 + jj;
-                ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(&a_full[abuf * kPairs + j], (i / AB) & 1));
+                ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded_hint(&a_full[abuf * kPairs + j], (i / AB) & 1, kWaitHintNs));
                 if (!ok) break;
                 if (i < 4 && which == 0) stamp(p, 1, i * 4 + 1 + jj);
                 tcgen05_fence_after_sync();
@@ -603,7 +607,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
             if (!ok) break;
             if (FMT != kQ6_K && which == 0) {
                 // minimum term: A = -dmin * m[g] twice (K slots 0..7 meet the block sums' hi parts, 8..15 their lo parts)
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&min_full[i & 1], (i >> 1) & 1));
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded_hint(&min_full[i & 1], (i >> 1) & 1, kWaitHintNs));
                 if (!ok) break;
                 tcgen05_fence_after_sync();
                 umma_f16_tmem_a_elected(d_tmem, tmem_base + P::kColAMin + (i & 1) * 8, desc_b0 + static_cast<uint64_t>(4 * (I::kTileBytes >> 4)), idesc, 1u);
@@ -629,7 +633,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
 #pragma unroll 1
         for (int i = set; i < local_sb; i += kSets) {
             const int s = i % p.raw_stages;
-            if (ok && !mbar_wait_bounded(&raw_full[s], (i / p.raw_stages) & 1)) {
+            if (ok && !mbar_wait_bounded_hint(&raw_full[s], (i / p.raw_stages) & 1, kWaitHintNs)) {
                 atomicExch(p.status, kDeviceWaitTimeout);
                 ok = false;
             }
@@ -664,7 +668,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
                             out_hi[r] = hmul2(out_hi[r], d2);
                         }
                     }
-                    if (i >= AB && ok && !mbar_wait_bounded(&a_empty[slot], ((i / AB) - 1) & 1)) {
+                    if (i >= AB && ok && !mbar_wait_bounded_hint(&a_empty[slot], ((i / AB) - 1) & 1, kWaitHintNs)) {
                         atomicExch(p.status, kDeviceWaitTimeout);
                         ok = false;
                     }
@@ -696,7 +700,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
                 mins[2] = half2_bits(nd * byte_of(m_hi, 0), nd * byte_of(m_hi, 1));
                 mins[3] = half2_bits(nd * byte_of(m_hi, 2), nd * byte_of(m_hi, 3));
                 mins[4] = mins[0]; mins[5] = mins[1]; mins[6] = mins[2]; mins[7] = mins[3];
-                if (i >= 2 && ok && !mbar_wait_bounded(&min_empty[i & 1], ((i >> 1) - 1) & 1)) {
+                if (i >= 2 && ok && !mbar_wait_bounded_hint(&min_empty[i & 1], ((i >> 1) - 1) & 1, kWaitHintNs)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
                 }
@@ -722,7 +726,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
                         out_hi[r] = hmul2(out_hi[r], d2);
                     }
                 }
-                if (i >= AB && ok && !mbar_wait_bounded(&a_empty[slot], ((i / AB) - 1) & 1)) {
+                if (i >= AB && ok && !mbar_wait_bounded_hint(&a_empty[slot], ((i / AB) - 1) & 1, kWaitHintNs)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
                 }
@@ -745,7 +749,7 @@ __global__ void __launch_bounds__(Roles<NT>::kThreads, NT >= 64 ? 1 : 2) qgemv_t
         if (set == 0) {
         pdl_wait_prior();   // the scale factors (and y, when it is accumulated into) come from earlier kernels
         if (threadIdx.x < NT) up[threadIdx.x] = reinterpret_cast<const float*>(p.image + I::scales_offset(p.nsb))[threadIdx.x];
-        if (ok && !mbar_wait_bounded(d_full, 0)) {
+        if (ok && !mbar_wait_bounded_hint(d_full, 0, kWaitHintNs)) {
             atomicExch(p.status, kDeviceWaitTimeout);
             ok = false;
         }
