@@ -165,7 +165,7 @@ def roofline(step_gbps, step_bytes, dominant, peak, peak_kind):
     source = f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s"
     if dominant is None:   # a run restricted to calls of up to eight member rows
         return {"bound": "hbm", "achieved": step_gbps, "peak": peak, "unit": "GB/s", "frac": step_gbps / peak, "traffic": None,
-                "peak_source": source, "kernel": "gemv_mma_kernel (+ activation pre-pass from three rows on), all calls of the step",
+                "peak_source": source, "kernel": "gemv_imma_kernel / gemv_mma_kernel (+ activation pre-pass from three rows on), all calls of the step",
                 "bytes_per_step": step_bytes}
     achieved, us_per_call, bytes_per_call = dominant
     traffic = None if TC_TRAFFIC_PER_ALGORITHMIC_BYTE is None else TC_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_call
@@ -370,7 +370,8 @@ def decode_leg(args, ctx, device, rank, world, peak):
                 prompt_generator = torch.Generator(device="cpu")
                 prompt_generator.manual_seed(members)
                 prompts = torch.randint(0, geometry.vocabulary, (members, context_tokens), generator=prompt_generator, dtype=torch.int32)
-                decoder.prefill(prompts[0][:64], sequence=0)                       # warm-up: first launches set kernel attributes
+                # warm-up with one full chunk: first launches load their kernels, set attributes and allocate the chunk's buffers
+                decoder.prefill(prompts[0][:512], sequence=0)
                 torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(ctx.stream)
@@ -628,7 +629,7 @@ def cpu_baseline_leg(ctx=None):
             return yd.cpu().numpy().astype(np.float64), xd.float().cpu().numpy()
         finally:
             for name, _ in options:
-                ctx.set_option(name, {"mma_gemv": 1, "gemv_path": 0, "tmem_gemv": 1}[name])
+                ctx.set_option(name, {"mma_gemv": 1, "gemv_path": 0, "tmem_gemv": 1, "imma_gemv": 1}[name])
 
     for vt in FORMATS:
         for n, k in SHAPES:
@@ -646,10 +647,12 @@ def cpu_baseline_leg(ctx=None):
 
                 norms = oracle.row_norms(vt, w, k, n)
                 y, seen = gpu_gemv(vt, w, k, n, x, torch.float32)
-                observe("mma_f16x2_planes (1 row, f32 in)", vt, n, k, w, seen, y, f32_reference=y32, norms=norms)
+                observe("narrow kernels: integer mma Q4_K/Q5_K, f16 mma Q6_K (1 row, f32 in)", vt, n, k, w, seen, y, f32_reference=y32, norms=norms)
                 x4 = synth.random_activations(4, k, seed=4)
                 y, seen = gpu_gemv(vt, w, k, n, x4, torch.bfloat16)
-                observe("mma_f16 (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                observe("narrow kernels: integer mma Q4_K/Q5_K, f16 mma Q6_K (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("imma_gemv", 0),))
+                observe("f16 mma, two planes (1 row, f32 in; imma_gemv = 0)", vt, n, k, w, seen, y, norms=norms)
                 x16 = synth.random_activations(16, k, seed=16)
                 y, seen = gpu_gemv(vt, w, k, n, x16, torch.bfloat16)
                 observe("tcgen05_weights_in_tmem (16 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
