@@ -37,7 +37,7 @@ struct ribn_ctx {
     uint64_t workspace_bytes = 0;
     unsigned int* tickets = nullptr;  // split-K tile counters of the tensor-core GEMM, zero between launches
     int tc_ksplit = 0;              // 0 = choose the split-K factor per shape
-    int tc_split_operands = 0;      // 1 = bf16 batches <= 64 use the split-operand GEMM (the prefill kernel) instead of the f16 decode kernel
+    int tc_split_operands = 0;      // 1 = bf16 batches <= 64 use the prefill GEMM kernel instead of the f16 decode kernel
     int tc_trace = 0;               // builds with -DRIBN_TRACE: 1 = kernels record pipeline clock stamps in the workspace tail
     int tc_row_copies = 0;          // 1 = force the per-row bulk-copy variant of the tensor-core kernel
     int dp4a_prepass = 1;           // 0 = calls of 1..4 rows pack their activations inside the GEMV kernel (measured slower: see the header)
@@ -769,7 +769,7 @@ int ribn_create(int device, void* cuda_stream, ribn_ctx** out) {
     e = cudaMalloc(&ctx->device_status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_status, 0, sizeof(int));
     // Scratch for fused-op intermediates, allocated once here so that no later call allocates.
-    ctx->workspace_bytes = 32ull << 20;
+    ctx->workspace_bytes = 96ull << 20;   // the f16 copy of 2048 token rows of 12288 values takes half of it
     if (e == cudaSuccess) e = cudaMalloc(&ctx->workspace, ctx->workspace_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->tickets, kTicketCount * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(ctx->tickets, 0, kTicketCount * sizeof(unsigned int));
@@ -1043,7 +1043,17 @@ int ribn_gemm(ribn_ctx* ctx, uint32_t expected_type, const ribn_qweight* weight,
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, x_device, "input");
     if (f.status == RIBN_OK) f = check_device_pointer(ctx, y_device, "output");
     if (f.status != RIBN_OK) return record(ctx, f);
-    return enqueue_tc(ctx, weight, k, n, x_device, RIBN_BF16, y_device, y_dtype, tokens);
+    // The kernel reads an f16 copy of the activations from the workspace: token rows go through in chunks whose copy takes at
+    // most half of it (a multiple of the 256-token tile; the weights of a later chunk come from L2 or HBM again).
+    uint64_t chunk = (ctx->workspace_bytes / 2) / (k * 2);
+    chunk = chunk >= 256 ? chunk / 256 * 256 : (chunk > 0 ? chunk : 1);
+    for (uint64_t first = 0; first < tokens; first += chunk) {
+        const uint64_t rows = tokens - first < chunk ? tokens - first : chunk;
+        const int rc = enqueue_tc(ctx, weight, k, n, static_cast<const uint8_t*>(x_device) + first * k * 2, RIBN_BF16,
+                                  static_cast<uint8_t*>(y_device) + first * n * dtype_bytes(y_dtype), y_dtype, rows);
+        if (rc != RIBN_OK) return rc;
+    }
+    return RIBN_OK;
 }
 
 #ifdef RIBN_TRACE

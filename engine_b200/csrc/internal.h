@@ -168,7 +168,7 @@ struct TcArgs {
     uint64_t weight_bytes;
     uint32_t value_type;
     int k, n, m;
-    const void* x;            // [m][k], 16-byte aligned; bf16 for launch_qgemm_tc, bf16 or f32 (x_bf16) for launch_qgemv_tc
+    const void* x;            // [m][k], 16-byte aligned; bf16 or f32 (x_bf16)
     bool x_bf16;
     const float* norm_weight; // launch_qgemv_tc only: RMSNorm weight applied to x first, or null
     float eps;
@@ -177,7 +177,7 @@ struct TcArgs {
     bool accumulate;          // launch_qgemv_tc only: y += W x
     void* y;                  // [m][n]
     bool y_bf16;
-    void* scratch;            // the activation tiles, then split-K partial tiles
+    void* scratch;            // the f16 activations and their factors, then split-K partial tiles
     size_t scratch_bytes;
     unsigned int* tickets;    // zero-initialised counters, one per output tile
     int ticket_count;
@@ -193,6 +193,11 @@ cudaError_t launch_qgemm_tc(const TcArgs& args);
 // Decode batches (1..64 members): one f16 operand tile per step, normalised per super-block; takes
 // f32 or bf16 activations and can apply RMSNorm to them in its conversion pre-pass.
 cudaError_t launch_qgemv_tc(const TcArgs& args);
+// The conversion pre-pass of both tensor-core kernels: row r of x (f32 or bf16, [gate | up] rows with swiglu, RMSNorm first
+// when norm_weight is given) times the power of two that brings its largest magnitude to at most 2^14, as f16 [m][k];
+// factor[r] = the inverse of that power.
+cudaError_t launch_convert_activations_f16(const void* x, bool x_bf16, bool swiglu, const float* norm_weight, float eps, void* x16, float* factor,
+                                           int m, int k, cudaStream_t stream);
 
 cudaError_t launch_dequantize(const uint8_t* weights, uint32_t value_type, uint64_t k, uint64_t n, float* out,
                               int sm_count, cudaStream_t stream);

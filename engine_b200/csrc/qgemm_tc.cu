@@ -1,7 +1,7 @@
 // Quantized GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) with the
 // dequantisation fused into the operand producer.
 //
-//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]      X bf16 [M][K], f32 accumulate
+//   Y[m][n] = sum_k dequant(W[n][k]) * X[m][k]      X bf16 (or f32) [M][K], f32 accumulate
 //
 // The reference has no such kernel: its prefill runs the batched GEMV eight
 // tokens at a time (crates/nvidia/src/decode.rs:1953-1977, :2149-2267 over
@@ -12,26 +12,30 @@
 // Shape of one CTA: 128 weight rows (the UMMA M dimension, one TMEM lane per
 // row) x NT tokens (the UMMA N dimension, NT in {16,32,64,128,256}) x a range
 // of K.  Per 64-wide K step:
-//   A = 128 x 64 dequantised weights as two bf16 tiles (high and low part, see
-//       below), K-major, 128-byte swizzle, written to shared memory by eight
-//       dequant warps from the raw GGUF bytes that a producer warp streams in
-//       with untiled bulk copies (one per row and super-block, completion on
-//       mbarriers);
-//   B = NT x 64 activations, bf16, brought by one tiled TMA load in the same
+//   A = 128 x 64 dequantised weights as one f16 tile, K-major, 128-byte
+//       swizzle, written to shared memory by sixteen dequant warps from the raw
+//       GGUF bytes that a producer warp streams in as tiled TMA boxes (bulk
+//       copies per row where rows are not 16-byte aligned), completion on
+//       mbarriers;
+//   B = NT x 64 activations as f16: a conversion pre-pass multiplies every token
+//       row by a power of two (largest magnitude at most 2^14) and the epilogue
+//       by its inverse; one tiled TMA load per step brings the tile in the same
 //       swizzled layout (rows past M read as zero);
-//   D (TMEM, f32) += A_high * B + A_low * B  with eight tcgen05.mma (K = 16
-//       each) issued by one thread; tcgen05.commit releases the stage.
+//   D (TMEM, f32) += A * B  with four tcgen05.mma (K = 16 each) issued by one
+//       thread; tcgen05.commit releases the stage.
 // The epilogue reads D with tcgen05.ld (thread = weight row, registers =
 // tokens) and stores Y.  With split-K the partial tiles go to a scratch buffer
 // and the last CTA of a tile (an atomic ticket, no spinning) adds them in a
 // fixed order, so results are deterministic.
 //
 // Precision: a single bf16 rounding of the weights (2^-9 relative) does not
-// meet the 2e-3 bound of the path over millions of outputs.  Each exact f32
-// weight is therefore split into w_high = bf16(w) and w_low = bf16(w - w_high)
-// (together 16 significant bits, 2^-17 relative); both operands of every MMA
-// are bf16, the activations are used as they are, and the extra MMA is free
-// where the kernel is bound by the weight stream.
+// meet the 2e-3 bound of the path over millions of outputs; an f16 rounding
+// (2^-12 relative, what the decode batch kernels apply) does, with one MMA per
+// K step where a split of every weight into two bf16 parts needed two.  Both
+// operands of kind::f16 must have the same format (an f16 A operand with a
+// bf16 B operand is an illegal instruction), hence the f16 copy of the
+// activations; bf16 activations convert exactly.  Weights beyond the f16 range
+// (|w| > 65504: super-block scales no checkpoint has) come out as infinities.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets the status
 // word, and every warp still reaches the common teardown that frees TMEM.
@@ -76,19 +80,22 @@ __device__ __forceinline__ void stamp(const TcParams& p, int role, int step, int
 #endif
 }
 
-template <uint32_t FMT, int NT, bool RAWTMA>
+// TT = token tiles per CTA: with two, a dequantised weight tile is multiplied with 2 x NT tokens (issuer t owns token tile
+// t and its accumulator), which halves the dequantisation per output.
+template <uint32_t FMT, int NT, bool RAWTMA, int TT>
 struct TcGeometry {
     using F = Format<FMT>;
     static constexpr int kBoxBytes = FMT == kQ6_K ? 240 : F::kBytes;
-    // Four stages keep all four slots busy; the widest tiles leave room for fewer (Q8_0 super-blocks are 272 bytes).
-    static constexpr int kAbStages = NT >= 256 ? 2 : (NT >= 128 || (NT >= 64 && FMT == kQ8_0)) ? 3 : 4;
+    // Four stages keep all four slots busy; the widest tiles leave room for three, two token tiles for two (the slots
+    // then share a stage: two halves of the K step each).
+    static constexpr int kAbStages = TT == 2 ? 2 : NT >= 256 ? 3 : 4;
     // bytes per row in a raw stage: the TMA box width, or a bulk copy from the 16-byte boundary below the block
     static constexpr int kSlot = RAWTMA ? kBoxBytes : ((F::kBytes + 15) / 16) * 16 + 16;
     static constexpr int kRawStageBytes = kBM * kSlot;
-    static constexpr int kAPartBytes = kBM * kBK * 2;        // one bf16 tile
-    static constexpr int kATileBytes = 2 * kAPartBytes;      // high part, then low part
-    static constexpr int kBTileBytes = NT * kBK * 2;
-    static constexpr int kTilesBytes = kAbStages * (kATileBytes + kBTileBytes);
+    static constexpr int kATileBytes = kBM * kBK * 2;        // one f16 tile
+    static constexpr int kBTileBytes = NT * kBK * 2;         // one token tile
+    static constexpr int kBStageBytes = TT * kBTileBytes;
+    static constexpr int kTilesBytes = kAbStages * (kATileBytes + kBStageBytes);
     static constexpr int kBarrierBytes = 256;
     // Raw stages fill what is left of shared memory, between two and six.
     static constexpr int kRawFit = (227 * 1024 - 1024 - kTilesBytes - kBarrierBytes) / kRawStageBytes;
@@ -97,25 +104,25 @@ struct TcGeometry {
     static_assert(kAbStages <= kSlots, "every tile of the ring needs a slot");
     static constexpr int kRawBytes = kRawStages * kRawStageBytes;
     static constexpr int kSmemBytes = 1024 + kTilesBytes + kRawBytes + kBarrierBytes;  // 1024: alignment slack
-    // Two accumulators: even K steps are issued by one thread into the first, odd steps by another
-    // into the second (an issue costs its thread far longer than the tensor pipe needs for so few
+    // Two accumulators.  One token tile: the K steps of the ring's even tiles are issued by one thread into the first,
+    // those of its odd tiles by another into the second (an issue costs its thread far longer than the tensor pipe needs for so few
     // tokens); the epilogue adds them.
     static constexpr int kTmemColumns = 2 * NT < 32 ? 32 : 2 * NT;
     static_assert(kSmemBytes <= 227 * 1024, "tile plan exceeds shared memory");
 };
 
-template <uint32_t FMT, int NT, bool RAWTMA>
+template <uint32_t FMT, int NT, bool RAWTMA, int TT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const TcParams p) {
-    using G = TcGeometry<FMT, NT, RAWTMA>;
+    using G = TcGeometry<FMT, NT, RAWTMA, TT>;
     using F = Format<FMT>;
-    using R = RowDequant<FMT, SplitBf16>;
+    using R = RowDequant<FMT, SingleF16>;
     extern __shared__ uint8_t smem_raw[];
     // The swizzled tiles need a 1024-byte aligned base.
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = a_tiles + G::kAbStages * G::kATileBytes;
-    uint8_t* raw = b_tiles + G::kAbStages * G::kBTileBytes;
+    uint8_t* raw = b_tiles + G::kAbStages * G::kBStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + G::kRawBytes);
     uint64_t* raw_full = bars;                       // [kRawStages], 32 producer lanes
     uint64_t* raw_empty = raw_full + G::kRawStages;  // [kRawStages], 8 dequant warps
@@ -128,7 +135,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBM;
-    const int m0 = blockIdx.y * NT;
+    const int m0 = blockIdx.y * (TT * NT);
     const int sb_begin = static_cast<int>(static_cast<long long>(p.nsb) * blockIdx.z / p.ksplit);
     const int sb_end = static_cast<int>(static_cast<long long>(p.nsb) * (blockIdx.z + 1) / p.ksplit);
     const int nsb_local = sb_end - sb_begin;
@@ -140,8 +147,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
             mbar_init(&raw_empty[s], kDequantWarps);
         }
         for (int s = 0; s < G::kAbStages; ++s) {
-            mbar_init(&ab_full[s], 4 + 1);   // the four warps of the step's slot + the activation tile
-            mbar_init(&ab_empty[s], 1);
+            mbar_init(&ab_full[s], (TT == 2 ? 8 : 4) + 1);   // the warps of the step's slot (two slots) + the activation tiles
+            mbar_init(&ab_empty[s], TT);                      // tcgen05.commit of every issuer that reads the stage
         }
         mbar_init(acc_full, 2);
         mbar_fence_init();
@@ -222,33 +229,37 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                     atomicExch(p.status, kDeviceWaitTimeout);
                     break;
                 }
-                mbar_arrive_expect_tx(&ab_full[as], G::kBTileBytes);
-                tma_load_2d(b_tiles + as * G::kBTileBytes, &xmap, sb_begin * kSuperBlock + j * kBK, m0, &ab_full[as]);
+                mbar_arrive_expect_tx(&ab_full[as], G::kBStageBytes);
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt)   // a token tile past the last token reads as zeros
+                    tma_load_2d(b_tiles + as * G::kBStageBytes + tt * G::kBTileBytes, &xmap, sb_begin * kSuperBlock + j * kBK, m0 + tt * NT,
+                                &ab_full[as]);
             }
         }
         __syncwarp();
     } else if (warp == 1 || warp == kSecondIssuerWarp) {
-        // ---------------- MMA issuers: one thread for the even steps, one for the odd ones ----------------
+        // ---------------- MMA issuers: one thread for the even tiles of the ring, one for the odd ones ----------------
+        // (a tile always belongs to the same issuer, so that its waits on the tile's barrier follow one another phase by
+        // phase, which the one-bit parity needs whether the ring has three tiles or four)
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_instr_desc(kBM, NT, /*A bf16*/ 1, /*B bf16*/ 1);
+            constexpr uint32_t idesc = umma_instr_desc(kBM, NT, /*A f16*/ 0, /*B f16*/ 0);
             const int first = warp == 1 ? 0 : 1;
             const uint32_t acc = tmem_base + first * NT;
-            for (int j = first; j < steps; j += 2) {
+            for (int j = TT == 2 ? 0 : first; j < steps; ++j) {
                 const int as = j % G::kAbStages;
+                if (TT == 1 && (as & 1) != first) continue;   // two token tiles: every step, this issuer's token tile
                 if (!mbar_wait_bounded(&ab_full[as], (j / G::kAbStages) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     break;
                 }
                 stamp(p, 0, j, 0);
                 tcgen05_fence_after_sync();
-                const uint64_t desc_high = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes));
-                const uint64_t desc_low = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes + G::kAPartBytes));
-                const uint64_t desc_b = umma_smem_desc_sw128(smem_addr(b_tiles + as * G::kBTileBytes));
+                const uint64_t desc_a = umma_smem_desc_sw128(smem_addr(a_tiles + as * G::kATileBytes));
+                const uint64_t desc_b = umma_smem_desc_sw128(smem_addr(b_tiles + as * G::kBStageBytes + (TT == 2 ? first * G::kBTileBytes : 0)));
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk) {
                     // 16 K elements = 32 bytes further along the swizzled row: +2 in the address field
-                    umma_f16(acc, desc_high + 2 * kk, desc_b + 2 * kk, idesc, j > first || kk > 0);
-                    umma_f16(acc, desc_low + 2 * kk, desc_b + 2 * kk, idesc, true);
+                    umma_f16(acc, desc_a + 2 * kk, desc_b + 2 * kk, idesc, j > (TT == 2 ? 0 : first) || kk > 0);
                 }
                 umma_commit(&ab_empty[as]);
                 stamp(p, 0, j, 1);
@@ -287,7 +298,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 // barriers then follow one another phase by phase, which the one-bit parity needs.
                 const int j = i * kSub + t;
                 const int as = j % G::kAbStages;
-                if (as != slot) continue;
+                if (as != (TT == 2 ? (slot & 1) : slot)) continue;
                 if (j >= G::kAbStages && !mbar_wait_bounded(&ab_empty[as], ((j / G::kAbStages) - 1) & 1)) {
                     atomicExch(p.status, kDeviceWaitTimeout);
                     ok = false;
@@ -297,18 +308,18 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
                 uint8_t* tile = a_tiles + as * G::kATileBytes + row_off;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    if (TT == 2 && h != (slot >> 1)) continue;   // two slots share the stage: one half of the K step each
                     typename R::Chunk out[4];
                     if (row_ok) {
                         R::step(blk, scales, t, h, out);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) out[c] = SplitBf16::zero();
+                        for (int c = 0; c < 4; ++c) out[c] = SingleF16::zero();
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint32_t chunk_off = (static_cast<uint32_t>(R::chunk_index(h, c)) ^ sw) << 4;
                         *reinterpret_cast<uint4*>(tile + chunk_off) = out[c].high;
-                        *reinterpret_cast<uint4*>(tile + G::kAPartBytes + chunk_off) = out[c].low;
                     }
                 }
                 if (r == 0) stamp(p, 1, j, 1);
@@ -333,21 +344,28 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         const bool split = p.ksplit > 1;
         float* part = split ? p.partial + static_cast<size_t>(blockIdx.z) * p.m * p.n : nullptr;
         if (ok) {
+            // One token tile: the two accumulators hold the even and the odd share of the K steps and are added.  Two token
+            // tiles: accumulator t holds token tile t, columns c0 run over both.
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 16) {
+            for (int c0 = 0; c0 < TT * NT; c0 += 16) {
                 if (m0 + c0 >= p.m) break;
-                uint32_t v[16], odd[16];
+                uint32_t v[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
-                tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + NT + c0, odd);
-                tmem_ld_wait();
+                if (TT == 1) {
+                    uint32_t odd[16];
+                    tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + NT + c0, odd);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) + __uint_as_float(odd[jj]));
+                    for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) + __uint_as_float(odd[jj]));
+                } else {
+                    tmem_ld_wait();
+                }
                 if (row < p.n) {
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj) {
                         const int m = m0 + c0 + jj;
                         if (m < p.m) {
-                            const float value = __uint_as_float(v[jj]);
+                            const float value = __uint_as_float(v[jj]) * __ldg(p.x_scale + m);   // the token row's factor, undone
                             const size_t o = static_cast<size_t>(m) * p.n + row;
                             if (split) {
                                 part[o] = value;
@@ -381,7 +399,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         if (*last_flag != 0 && row < p.n) {
             __threadfence();
             const size_t plane = static_cast<size_t>(p.m) * p.n;
-            const int m_end = min(m0 + NT, p.m);
+            const int m_end = min(m0 + TT * NT, p.m);
             // Four tokens at a time, so that four independent loads per K slice are in flight;
             // the slices are added in index order whatever the arrival order was.
             for (int m = m0 + 4 * (worker >> 7); m < m_end; m += 4 * kSlots) {
@@ -414,10 +432,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, G::kTmemColumns);
 }
 
-template <uint32_t FMT, int NT, bool RAWTMA>
+template <uint32_t FMT, int NT, bool RAWTMA, int TT = 1>
 cudaError_t launch_tile(const TcArgs& a) {
-    using G = TcGeometry<FMT, NT, RAWTMA>;
-    auto kernel = qgemm_tc_kernel<FMT, NT, RAWTMA>;
+    using G = TcGeometry<FMT, NT, RAWTMA, TT>;
+    auto kernel = qgemm_tc_kernel<FMT, NT, RAWTMA, TT>;
     static int configured_device = -1;
     int device = 0;
     cudaGetDevice(&device);
@@ -428,14 +446,25 @@ cudaError_t launch_tile(const TcArgs& a) {
     }
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return cudaErrorNotSupported;
+    // Scratch: [f16 activations][one factor per token row][split-K partial tiles].
+    const size_t x16_bytes = (static_cast<size_t>(a.m) * a.k * sizeof(__half) + 1023) & ~static_cast<size_t>(1023);
+    const size_t factor_bytes = (static_cast<size_t>(a.m) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+    if (x16_bytes + factor_bytes > a.scratch_bytes) return cudaErrorMemoryAllocation;
+    void* x16 = a.scratch;
+    float* factor = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + x16_bytes);
+    float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + x16_bytes + factor_bytes);
+    const size_t partial_bytes = a.scratch_bytes - x16_bytes - factor_bytes;
+    if (!a.skip_prepass) {
+        const cudaError_t converted = launch_convert_activations_f16(a.x, a.x_bf16, false, nullptr, 0.0f, x16, factor, a.m, a.k, a.stream);
+        if (converted != cudaSuccess) return converted;
+    }
     CUtensorMap map;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k) * 2};
     const cuuint32_t box[2] = {kBK, NT};
     const cuuint32_t elem[2] = {1, 1};
-    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x16, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     TcParams p;
     p.w = a.weights;
@@ -453,7 +482,8 @@ cudaError_t launch_tile(const TcArgs& a) {
             return cudaErrorInvalidValue;
     }
     p.y = a.y;
-    p.partial = static_cast<float*>(a.scratch);
+    p.partial = partial;
+    p.x_scale = factor;
     p.tickets = a.tickets;
     p.k = a.k;
     p.n = a.n;
@@ -464,11 +494,13 @@ cudaError_t launch_tile(const TcArgs& a) {
     p.status = a.device_status;
     p.trace = a.trace;
     const int n_tiles = (a.n + kBM - 1) / kBM;
-    const int m_tiles = (a.m + NT - 1) / NT;
-    p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, static_cast<size_t>(a.m) * a.n * sizeof(float),
-                             a.scratch_bytes, a.ticket_count);
+    const int m_tiles = (a.m + TT * NT - 1) / (TT * NT);
+    p.ksplit = choose_ksplit(n_tiles * m_tiles, p.nsb, a.sm_count, static_cast<size_t>(a.m) * a.n * sizeof(float), partial_bytes, a.ticket_count);
+    // Hundreds of tokens: a partial tile is megabytes, written and read once more per split (192 tiles of 512 tokens: 127 us
+    // unsplit, 160 us split in two).  K is split then only where the tiles leave more than half of the SMs idle.
+    if (a.m > 256 && 2 * n_tiles * m_tiles > a.sm_count) p.ksplit = 1;
     if (a.force_ksplit > 0 && a.force_ksplit <= p.nsb &&
-        static_cast<size_t>(a.m) * a.n * sizeof(float) * a.force_ksplit <= a.scratch_bytes && n_tiles * m_tiles <= a.ticket_count)
+        static_cast<size_t>(a.m) * a.n * sizeof(float) * a.force_ksplit <= partial_bytes && n_tiles * m_tiles <= a.ticket_count)
         p.ksplit = a.force_ksplit;
     const dim3 grid(n_tiles, m_tiles, p.ksplit);
     kernel<<<grid, kTcThreads, G::kSmemBytes, a.stream>>>(map, wmap, p);
@@ -481,7 +513,15 @@ cudaError_t launch_tokens(const TcArgs& a) {
     if (a.m <= 32) return launch_tile<FMT, 32, RAWTMA>(a);
     if (a.m <= 64) return launch_tile<FMT, 64, RAWTMA>(a);
     if (a.m <= 128) return launch_tile<FMT, 128, RAWTMA>(a);
-    return launch_tile<FMT, 256, RAWTMA>(a);
+    // From 257 tokens on a CTA takes two tiles of 256 (Q8_0's 272-byte super-blocks leave no room for the second).
+    if constexpr (FMT == kQ8_0) {
+        return launch_tile<FMT, 256, RAWTMA>(a);
+    } else {
+        // ... when CTAs of 512 tokens still cover most SMs (measured: 96 CTAs of two tiles lose to 192 of one, 128 win over 256)
+        const long long wide_ctas = static_cast<long long>((a.n + kBM - 1) / kBM) * ((a.m + 511) / 512);
+        if (a.m <= 256 || wide_ctas * 5 < static_cast<long long>(a.sm_count) * 4) return launch_tile<FMT, 256, RAWTMA>(a);
+        return launch_tile<FMT, 256, RAWTMA, 2>(a);
+    }
 }
 
 template <uint32_t FMT>

@@ -717,6 +717,12 @@ cudaError_t launch_format(const TcArgs& a) {
 
 }  // namespace
 
+cudaError_t launch_convert_activations_f16(const void* x, bool x_bf16, bool swiglu, const float* norm_weight, float eps, void* x16, float* factor,
+                                           int m, int k, cudaStream_t stream) {
+    return launch_kernel(convert_activations_f16, dim3(m), dim3(kConvertThreads), 0, stream, x, x_bf16 ? 1 : 0, swiglu ? 1 : 0, norm_weight, eps,
+                         static_cast<__half*>(x16), factor, k);
+}
+
 cudaError_t launch_qgemv_tc(const TcArgs& a) {
     if (a.m < 1 || a.m > 64) return cudaErrorInvalidValue;
     switch (a.value_type) {

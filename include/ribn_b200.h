@@ -122,8 +122,9 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "tc_four_row_bytes": where the mma kernel does not serve a shape, bf16 batches of exactly four rows use the
  *                   tcgen05 kernel when the encoded weights are at least this many bytes (default 8 MiB);
  *   "tc_f32_activations": 1 = f32 batches may use the tcgen05 kernel too (they are rounded to f16; default 0);
- *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the split-bf16-operand GEMM (the prefill
- *                   kernel) instead of the f16 decode kernel (default 0);
+ *   "tc_split_operands": 1 = bf16 batches of up to 64 rows use the prefill GEMM kernel (accumulation over the whole
+ *                   K range in tensor memory) instead of the f16 decode kernel (default 0; the name is from when that
+ *                   kernel split every weight into two bf16 operands);
  *   "dp4a_prepass": 0 = calls of 1..4 rows on the integer-dot kernel pack their activations inside it, every CTA
  *                   its own copy, instead of in a launch of their own (default 1);
  *   "pdl":          programmatic dependent launch, process-wide: 0 = off, 1 = every kernel of the path, 2 = the GEMV

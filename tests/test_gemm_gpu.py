@@ -18,10 +18,11 @@ TOL = 2e-3
 BF16_ROUNDOFF = 2.0 ** -8
 
 
-@pytest.fixture(params=[0, 1], ids=["f16-normalised", "split-operands"], autouse=True)
+@pytest.fixture(params=[0, 1], ids=["f16-normalised", "gemm-kernel"], autouse=True)
 def tc_kernel(request, ctx):
-    """Batches of up to 64 tokens have two tensor-core kernels (one f16 operand tile normalised per
-    super-block, and split bf16 operands); every test runs with each.  Larger batches always use the second."""
+    """Batches of up to 64 tokens have two tensor-core kernels (the decode kernel, whose f16 operand tile is normalised
+    per super-block, and the prefill GEMM, which accumulates over the whole K range in tensor memory); every test runs
+    with each.  Larger batches always use the second."""
     ctx.set_option("tc_split_operands", request.param)
     yield request.param
     ctx.set_option("tc_split_operands", 0)
