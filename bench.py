@@ -214,8 +214,7 @@ def attention_profile(spec: str) -> None:
 
 def prefill_leg(ctx, device, stream):
     """ribn_gemm on the two configuration-3 matrices, 512 and 2048 tokens, bf16 in and out: TFLOP/s and the fraction of
-    the measured dense bf16 throughput (the kernel issues two MMAs per weight -- high and low bf16 part -- so half of
-    the tensor peak is its ceiling)."""
+    the measured dense bf16 throughput (the call's f16 conversion pre-pass of the activations is inside the timed region)."""
     import torch
 
     import engine_b200
