@@ -754,7 +754,8 @@ def main() -> None:
     acts = {(k, m): torch.randn(m, k, device=device).to(torch.bfloat16) for _, k in SHAPES for m in MEMBERS}
     outs = {(n, m): torch.empty(m, n, dtype=torch.float32, device=device) for n, _ in SHAPES for m in MEMBERS}
     cursor = {key: 0 for key in rings}
-    cases = [(vt, n, k, m) for vt in FORMATS for n, k in SHAPES for m in MEMBERS]
+    # One batch size at a time through every matrix, the way a decode step meets them.
+    cases = [(vt, n, k, m) for m in MEMBERS for vt in FORMATS for n, k in SHAPES]
     step_bytes = sum(case_bytes(*c) for c in cases)
     # Launches per call: one for up to two member rows (the kernel converts its activations itself; two rows over more
     # than 24 super-blocks take the pre-pass too), otherwise an activation pre-pass and the GEMV kernel.
@@ -988,6 +989,7 @@ def main() -> None:
                        "formats": [synth.TYPE_NAMES[v] for v in FORMATS], "shapes_NxK": SHAPES,
                        "members": MEMBERS, "activations": "bf16", "outputs": "f32",
                        "l2": "ring of distinct weight copies > 2x L2 per (format, shape); inputs larger than L2",
+                       "order": "one member count at a time through all 12 (format, shape) matrices, as a decode step meets them",
                        "parallelism": "replicas" if world > 1 else "single", "gemv_variant": args.variant, "options": args.option,
                        "cuda_graph": step_graph is not None},
             "roofline": roofline(value / world, step_bytes, dominant_roofline, peak, peak_kind),
