@@ -165,9 +165,14 @@ def test_q8_0_input_sizes_that_are_not_multiples_of_256(ctx, k, n):
 # kernels, crates/nvidia/tests/cuda_reference.rs:5243-5337)
 @pytest.mark.parametrize("vt", [12, 13, 14])
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
-def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype):
+@pytest.mark.parametrize("integer_kernel", [1, 0], ids=["imma", "f16-mma"])
+def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype, integer_kernel):
+    """Q4_K / Q5_K run on the integer tensor-core kernel by default and on the f16 kernel (Q6_K's) with imma_gemv = 0."""
     if gemv_path != 0:
-        pytest.skip("the mma kernel is the default path only")
+        pytest.skip("the mma kernels are the default path only")
+    if vt == 14 and integer_kernel == 0:
+        pytest.skip("Q6_K has one narrow kernel")
+    ctx.set_option("imma_gemv", integer_kernel)
     k, n = 4096, 528
     w = synth.random_weight(vt, k, n, seed=vt)
     weight = upload(ctx, vt, w, k, n)
@@ -185,6 +190,7 @@ def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype):
                 results[(image_members, members)] = y
     finally:
         ctx.set_option("mma_image_members", 3)
+        ctx.set_option("imma_gemv", 1)
     full = results[(1, 8)]
     for (image_members, members), y in results.items():
         assert np.array_equal(y, full[:members]), (image_members, members)
