@@ -403,7 +403,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
         // ---------------- consumers ----------------
         const int g = lane >> 2, t = lane & 3;
         named_barrier_sync(2, kThreads);
-        reinterpret_cast<uint32_t*>(zeros)[threadIdx.x] = 0u;   // 256 consumers x 4 bytes = the zero area
+        // 256 consumers x 4 bytes = the zero area, in place (and visible to every warp) before the wait for the previous
+        // kernel ends: after that wait a warp only needs what it converts itself
+        reinterpret_cast<uint32_t*>(zeros)[threadIdx.x] = 0u;
+        named_barrier_sync(1, kConsumers);
         pdl_wait_prior();   // the activations may be the previous kernel's output, and y may still be read by it
         if (p.image == nullptr) {
             // norm[64 + m] = 1 / rms of member row m when RMSNorm is asked for
@@ -441,13 +444,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
                     store_slice(m1, sb1, lane, v1, planes + static_cast<size_t>(m1) * p.nsb * kSliceBytes, sums + static_cast<size_t>(m1) * p.nsb * 16,
                                 scale);
             }
+            __syncwarp();   // a warp reads only the super-blocks it converted itself
         } else if (!mbar_wait_bounded(image_bar, 0)) {
             atomicExch(p.status, kDeviceWaitTimeout);
             ok = false;
         }
-        // A warp reads only what it wrote itself (its own super-blocks) or what the bulk copy brought; the zero
-        // area was written by all consumers.
-        named_barrier_sync(1, kConsumers);
 
         LaneX<GROUPS> lx;
         {
