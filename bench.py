@@ -757,9 +757,9 @@ def main() -> None:
     # One batch size at a time through every matrix, the way a decode step meets them.
     cases = [(vt, n, k, m) for m in MEMBERS for vt in FORMATS for n, k in SHAPES]
     step_bytes = sum(case_bytes(*c) for c in cases)
-    # Launches per call: one for up to two member rows (the kernel converts its activations itself; two rows over more
-    # than 24 super-blocks take the pre-pass too), otherwise an activation pre-pass and the GEMV kernel.
-    launches_per_step = sum(1 if (m == 1 or (m == 2 and k // 256 <= 24)) else 2 for _, _, k, m in cases)
+    # Launches per call: one for up to two member rows over at most 24 super-blocks (the kernel converts its activations
+    # itself), otherwise an activation pre-pass and the GEMV kernel.
+    launches_per_step = sum(1 if (m <= 2 and k // 256 <= 24) else 2 for _, _, k, m in cases)
 
     def launch(vt, n, k, m):
         ring = rings[(vt, n, k)]

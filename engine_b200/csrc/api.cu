@@ -404,7 +404,7 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
             a.device_status = ctx->device_status;
             a.sm_count = ctx->sm_count;
             a.stream = ctx->stream;
-            const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
+            const bool wide = a.members >= ctx->mma_image_members || (a.members <= 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
                               (shared_image && a.members >= 2 && ctx->mma_image_members <= 8) || (mode == 2 && ctx->mma_image_members <= 8);
             const uint64_t image_bytes = ribn::gemv_imma_image_bytes(a.members, a.k);
             if (wide && offset + image_bytes <= ctx->workspace_bytes) {
@@ -449,10 +449,11 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
         a.stream = ctx->stream;
         const uint64_t image_bytes = ribn::gemv_mma_image_bytes(a.members, a.k, a.planes);
         // Narrow launches convert their activations inside the kernel (no second launch on the critical path); from
-        // about four slices per warp on, the conversion is worth a launch of its own (measured: two rows over K = 12288).
+        // about four slices per warp on, the conversion is worth a launch of its own (measured: one and two rows over
+        // K = 12288, where every CTA would otherwise convert 48 slices before its first multiply).
         // Several projections of one normalised or gated input of two rows or more share the image: the norm /
         // activation runs once (one row is cheaper converted by every CTA than waited for).
-        const bool wide = a.members >= ctx->mma_image_members || (a.members == 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
+        const bool wide = a.members >= ctx->mma_image_members || (a.members <= 2 && ctx->mma_image_members <= 3 && a.k / 256 > 24) ||
                           (shared_image && a.members >= 2 && ctx->mma_image_members <= 8) ||
                           (mode == 2 && ctx->mma_image_members <= 8);   // silu(gate) * up once, not once per CTA (measured: K = 12288, one row)
         if (wide && image_offset + image_bytes <= ctx->workspace_bytes) {

@@ -302,7 +302,7 @@ class CudaDenseDecode:
         # one launch per projection, plus the activation pre-pass where one runs (from three members on, for wide
         # two-member inputs, for gated inputs, and whenever several projections share a normalised input)
         shared = len(jobs) > 1 and norm is not None and self.members >= 2
-        prepass = self.members >= 3 or shared or swiglu or (self.members == 2 and x.shape[-1] // 256 > 24)
+        prepass = self.members >= 3 or shared or swiglu or x.shape[-1] // 256 > 24
         self.launches_per_step += len(jobs) + (1 if prepass else 0)
 
     def _all_reduce(self, t: torch.Tensor) -> None:

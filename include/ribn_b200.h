@@ -114,7 +114,8 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *                   activations as 22-bit integers per 256-value slice); 0 = on the half2-unpack f16 kernel that
  *                   serves Q6_K (default 1);  "imma_max_members": largest such call (1..8, default 8);
  *   "mma_image_members": launches of at least this many rows convert their activations in a pre-pass launch,
- *                   narrower ones inside the GEMV kernel (1..9, default 3);
+ *                   narrower ones inside the GEMV kernel unless K exceeds 24 super-blocks or the input is gated
+ *                   (1..9, default 3);
  *   "mma_stages":   ring depth of that kernel, 0 = as many stages as fit (default);
  *   "tc_min_members": smallest bf16 batch ribn_gemv sends to a tcgen05 batch kernel (default 9);
  *   "tmem_gemv":    1 = those batches (Q4_K / Q5_K / Q6_K, up to 64 rows) run on the kernel that unpacks the weights into
