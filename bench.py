@@ -646,10 +646,10 @@ def cpu_baseline_leg(ctx=None):
 
                 norms = oracle.row_norms(vt, w, k, n)
                 y, seen = gpu_gemv(vt, w, k, n, x, torch.float32)
-                observe("narrow kernels: integer mma Q4_K/Q5_K, f16 mma Q6_K (1 row, f32 in)", vt, n, k, w, seen, y, f32_reference=y32, norms=norms)
+                observe("integer mma (1 row, f32 in)", vt, n, k, w, seen, y, f32_reference=y32, norms=norms)
                 x4 = synth.random_activations(4, k, seed=4)
                 y, seen = gpu_gemv(vt, w, k, n, x4, torch.bfloat16)
-                observe("narrow kernels: integer mma Q4_K/Q5_K, f16 mma Q6_K (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
+                observe("integer mma (4 rows, bf16 in)", vt, n, k, w, seen, y, norms=norms)
                 y, seen = gpu_gemv(vt, w, k, n, x, torch.float32, options=(("imma_gemv", 0),))
                 observe("f16 mma, two planes (1 row, f32 in; imma_gemv = 0)", vt, n, k, w, seen, y, norms=norms)
                 x16 = synth.random_activations(16, k, seed=16)

@@ -46,7 +46,7 @@ struct ribn_ctx {
     int tc_min_members = 9;         // batches of at least this many rows go to the tcgen05 decode kernel
     int tmem_gemv = 1;              // 1 = Q4_K / Q5_K batches of nine or more rows use the kernel that unpacks the weights into tensor memory
     int mma_gemv = 1;               // 1 = batches of up to eight rows use the half2-unpack + mma.sync kernel where it serves the shape
-    int imma_gemv = 1;              // 1 = up to imma_max_members rows of Q4_K / Q5_K use the integer tensor-core kernel (gemv_imma.cu)
+    int imma_gemv = 1;              // 1 = up to imma_max_members rows of a K-quant use the integer tensor-core kernel (gemv_imma.cu)
     int imma_max_members = 8;
     int mma_image_members = 3;      // launches of at least this many rows convert their activations in a pre-pass, fewer inside the kernel
     int mma_stages = 0;             // ring depth of that kernel, 0 = as many stages as fit
@@ -377,7 +377,7 @@ int enqueue_mma(ribn_ctx* ctx, const ribn_qweight* w, uint64_t k, uint64_t n, co
     const uint64_t x_row_bytes = k * (mode == 2 ? 2 : 1) * dtype_bytes(x_dtype);
     unsigned none_made = 0;
     if (images_made == nullptr) images_made = &none_made;
-    // Q4_K / Q5_K: the integer tensor-core kernel, eight rows per launch (quants go to the instruction as they are).
+    // The integer tensor-core kernel, eight rows per launch (quants go to the instruction as 8-bit operands).
     const uint32_t per_launch = members < 8 ? members : 8;
     if (ctx->imma_gemv != 0 && (members <= static_cast<uint32_t>(ctx->imma_max_members) || members > 8) &&
         ribn::gemv_imma_supports(w->value_type, static_cast<int>(k), static_cast<int>(n), static_cast<int>(per_launch), w->data)) {

@@ -1,5 +1,5 @@
 // Dequant-fused GEMV for 1..8 activation rows per launch on the integer tensor-core instruction
-// (mma.sync m16n8k32 u8 x s8, s32 accumulate): Q4_K and Q5_K.
+// (mma.sync m16n8k32 u8 x s8 for Q4_K and Q5_K, m16n8k16 s8 x s8 for Q6_K; s32 accumulate).
 //
 //   y[m][n] = sum_k dequant(W[n][k]) * x[m][k]
 //
@@ -19,6 +19,11 @@
 //     sub-blocks stay exact; d * 2^-e is applied in f32 once per super-block and row;
 //   * the minima term (dmin * m_j * sum of the sub-block's activations) is one f16 mma per super-block, as in
 //     the f16 kernel: A = the eight minima, B = the block sums as f16 hi + lo.
+// Q6_K: scales cover 16 weights, so the instruction is the k16 one; a quant is six bits from two places
+// (a nibble and two bits, merged with three logic ops per four weights), and q - 32 is made a signed byte in two
+// more (set the top bit, subtract 32 without a borrow between bytes, clear the top bit again), which needs no
+// block sums.  Super-blocks are 210 bytes: every second one starts two bytes off a word boundary, and its words
+// are funnel-shifted out of two aligned loads.
 // Rounding: the weights are exact; an activation carries 2^-22 of its super-block's largest magnitude, all
 // integer sums are exact, and a row's result does not depend on the rows launched with it.
 //
@@ -48,16 +53,19 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxMembers = 8;                 // four column groups of two members
 constexpr int kSliceBytes = 768;               // image bytes per (member, super-block): 8 sub-blocks x 3 planes x 32
 constexpr int kZeroBytes = 1024;               // zeros the fourth column of every member (and absent members) read
-constexpr int kBoxSb = 2;                      // row pitch 288 B (Q4_K) / 352 B (Q5_K): 8 or 24 (mod 32) words, so the
-constexpr int kBoxes = kWarps / kBoxSb;        // 64-bit loads of four rows x four lanes fall on 32 different banks
 
 template <uint32_t FMT>
 struct ImmaPlan {
     static constexpr int kSbBytes = Format<FMT>::kBytes;
+    // Super-blocks per TMA box.  Q4_K / Q5_K: two, a row pitch of 288 / 352 bytes = 8 or 24 (mod 32) words, so that the
+    // 64-bit loads of four rows x four lanes fall on 32 different banks.  Q6_K: eight (1680 bytes, the smallest multiple of
+    // 210 that is a multiple of 16) = 4 (mod 32) words: the 32-bit loads of eight rows x four lanes fall on 32 banks.
+    static constexpr int kBoxSb = FMT == kQ6_K ? 8 : 2;
+    static constexpr int kBoxes = kWarps / kBoxSb;
     static constexpr int kRowPitch = kBoxSb * kSbBytes;
     static constexpr int kBoxBytes = kTileRows * kRowPitch;
     static constexpr int kStageBytes = kBoxes * kBoxBytes;
-    static constexpr uint32_t kQuantOffset = FMT == kQ4_K ? 16 : 48;   // Q5_K: 32 fifth-bit bytes after the header
+    [[maybe_unused]] static constexpr uint32_t kQuantOffset = FMT == kQ4_K ? 16 : 48;   // Q5_K: 32 fifth-bit bytes after the header
     static_assert(kRowPitch % 16 == 0 && kBoxBytes % 128 == 0, "TMA box: 16-byte rows, 128-byte aligned destination");
     static_assert((kSbBytes * kBoxSb / 8) % 2 == 0, "TMA x coordinate of every box on a 16-byte boundary");
 };
@@ -181,6 +189,20 @@ __device__ __forceinline__ void hmma_zero(float (&c)[4], uint32_t a0, uint32_t a
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// D = A(16x16, s8, row) * B(16x8, s8, col), s32.  Lane (g, t): a0 row g, a1 row g+8, K slots 4t..4t+3; b0 column g, the same slots.
+__device__ __forceinline__ void imma16_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+// A 32-bit word of shared memory at `address`, which is two bytes past a word boundary when ODD.
+template <bool ODD>
+__device__ __forceinline__ uint32_t lds32_shifted(uint32_t address) {
+    if (!ODD) return lds32(address);
+    return __funnelshift_r(lds32(address - 2), lds32(address + 2), 16);
 }
 
 // Per-lane shared addresses at the super-block the warp works on.  Column g of column group q is plane g & 3 of
@@ -308,6 +330,98 @@ __device__ __forceinline__ void superblock(uint32_t p0, uint32_t p1, const LaneX
     mins[3] = fmaf(dm1 * xb, cm[3], mins[3]);
 }
 
+// ---- Q6_K.  Block b = 8 n2 + 2 v + h of the sixteen 16-weight blocks: positions 128 n2 + 32 v + 16 h .. + 15, low nibbles
+// in ql byte 64 n2 + 32 (v & 1) + 16 h + l (the low half of the byte for v < 2, the high half above), two more bits in
+// qh byte 32 n2 + 16 h + l at bit 2 v; lane t takes l = 4t .. 4t + 3 of every block, one word of each.
+template <int V>
+__device__ __forceinline__ uint32_t q6_signed_bytes(uint32_t ql_word, uint32_t qh_word) {
+    // 128 + nibble in every byte, then bits 4..5 from qh: 128 + q; minus 32 without a borrow between bytes; top bit off again
+    const uint32_t nibbles = and_or(V < 2 ? ql_word : (ql_word >> 4), 0x0f0f0f0fu, 0x80808080u);
+    const uint32_t moved = V == 0 ? (qh_word << 4) : V == 1 ? (qh_word << 2) : V == 2 ? qh_word : (qh_word >> 2);
+    return (and_or(moved, 0x30303030u, nibbles) - 0x20202020u) ^ 0x80808080u;
+}
+
+// Byte I of `word` as a sign-extended integer: prmt with the replicate-sign bit of the selector set for the three upper
+// bytes (the __byte_perm intrinsic keeps only the byte index of a selector nibble).
+template <int I>
+__device__ __forceinline__ int signed_byte(uint32_t word) {
+    int value;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(value) : "r"(word), "r"(0u), "n"(I | ((I | 8) << 4) | ((I | 8) << 8) | ((I | 8) << 12)));
+    return value;
+}
+
+template <int B, int GROUPS>
+__device__ __forceinline__ void block_q6(uint32_t a0, uint32_t a1, const LaneX<GROUPS>& lx, uint32_t scales0, uint32_t scales1,
+                                         int (&total)[GROUPS][4]) {
+    const int s0 = signed_byte<B & 3>(scales0), s1 = signed_byte<B & 3>(scales1);
+#pragma unroll
+    for (int q = 0; q < GROUPS; ++q) {
+        uint32_t b0;
+        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(b0) : "r"(lx.x[q]), "n"(96 * (B >> 1) + 16 * (B & 1)));
+        int c[4];
+        imma16_zero(c, a0, a1, b0);
+        total[q][0] += s0 * c[0];
+        total[q][1] += s0 * c[1];
+        total[q][2] += s1 * c[2];
+        total[q][3] += s1 * c[3];
+    }
+}
+
+// The two blocks that share the ql word (N2, VLOW, H): block B = 8 N2 + 2 VLOW + H from its low nibbles, block B + 4 from
+// its high nibbles.
+template <int N2, int H, int VLOW, int GROUPS, bool ODD>
+__device__ __forceinline__ void blocks_q6(uint32_t p0, uint32_t p1, uint32_t qh0, uint32_t qh1, uint32_t lane_bytes, const LaneX<GROUPS>& lx,
+                                          const uint32_t (&sc0)[4], const uint32_t (&sc1)[4], int (&total)[GROUPS][4]) {
+    constexpr int B = 8 * N2 + 2 * VLOW + H;
+    const uint32_t ql0 = lds32_shifted<ODD>(p0 + 64 * N2 + 32 * VLOW + 16 * H + lane_bytes);
+    const uint32_t ql1 = lds32_shifted<ODD>(p1 + 64 * N2 + 32 * VLOW + 16 * H + lane_bytes);
+    block_q6<B, GROUPS>(q6_signed_bytes<VLOW>(ql0, qh0), q6_signed_bytes<VLOW>(ql1, qh1), lx, sc0[B >> 2], sc1[B >> 2], total);
+    block_q6<B + 4, GROUPS>(q6_signed_bytes<VLOW + 2>(ql0, qh0), q6_signed_bytes<VLOW + 2>(ql1, qh1), lx, sc0[(B + 4) >> 2], sc1[(B + 4) >> 2],
+                            total);
+}
+
+// The four blocks that share the qh word (N2, H).
+template <int N2, int H, int GROUPS, bool ODD>
+__device__ __forceinline__ void quarter_q6(uint32_t p0, uint32_t p1, uint32_t lane_bytes, const LaneX<GROUPS>& lx, const uint32_t (&sc0)[4],
+                                           const uint32_t (&sc1)[4], int (&total)[GROUPS][4]) {
+    const uint32_t qh0 = lds32_shifted<ODD>(p0 + 128 + 32 * N2 + 16 * H + lane_bytes);
+    const uint32_t qh1 = lds32_shifted<ODD>(p1 + 128 + 32 * N2 + 16 * H + lane_bytes);
+    blocks_q6<N2, H, 0, GROUPS, ODD>(p0, p1, qh0, qh1, lane_bytes, lx, sc0, sc1, total);
+    blocks_q6<N2, H, 1, GROUPS, ODD>(p0, p1, qh0, qh1, lane_bytes, lx, sc0, sc1, total);
+}
+
+// One Q6_K super-block of rows g (at p0) and g + 8 (at p1); ODD: the super-block starts two bytes past a word boundary.
+template <int GROUPS, bool ODD>
+__device__ __forceinline__ void superblock_q6(uint32_t p0, uint32_t p1, const LaneX<GROUPS>& lx, int t, float (&acc)[GROUPS][2]) {
+    int total[GROUPS][4];
+#pragma unroll
+    for (int q = 0; q < GROUPS; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total[q][i] = 0;
+    const uint32_t lane_bytes = 4u * static_cast<uint32_t>(t);
+    // the sixteen scale bytes of each row: word i holds blocks 4i .. 4i + 3
+    uint32_t sc0[4], sc1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sc0[i] = lds32_shifted<ODD>(p0 + 192 + 4 * i);
+        sc1[i] = lds32_shifted<ODD>(p1 + 192 + 4 * i);
+    }
+    quarter_q6<0, 0, GROUPS, ODD>(p0, p1, lane_bytes, lx, sc0, sc1, total);
+    quarter_q6<0, 1, GROUPS, ODD>(p0, p1, lane_bytes, lx, sc0, sc1, total);
+    quarter_q6<1, 0, GROUPS, ODD>(p0, p1, lane_bytes, lx, sc0, sc1, total);
+    quarter_q6<1, 1, GROUPS, ODD>(p0, p1, lane_bytes, lx, sc0, sc1, total);
+    const float d0 = f16_bits_to_f32(lds_u16(p0 + 208)), d1 = f16_bits_to_f32(lds_u16(p1 + 208));
+    const float weight = (t & 1) ? 16384.0f : 1.0f;
+#pragma unroll
+    for (int q = 0; q < GROUPS; ++q) {
+        const float xs = __uint_as_float(lds32(lx.scale + 8 * q + 4 * (t >> 1))) * weight;
+        const float v0 = fmaf(128.0f, static_cast<float>(total[q][1]), static_cast<float>(total[q][0]));
+        const float v1 = fmaf(128.0f, static_cast<float>(total[q][3]), static_cast<float>(total[q][2]));
+        acc[q][0] = fmaf(d0 * xs, v0, acc[q][0]);
+        acc[q][1] = fmaf(d1 * xs, v1, acc[q][1]);
+    }
+}
+
 // ---------------------------------------------------------------- the kernel
 // Shared-memory plan: [ring: stages x stage][zeros 1 KiB][image: planes | sums | scale][red: 2 x 8 warps x 128 f32]
 //                     [norm: 9 x 8 f32][barriers]
@@ -391,11 +505,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
                 const int chunk = it - tile * chunks;
                 const int row0 = (tile_begin + tile) * kTileRows;
                 const int sbs = min(kWarps, p.nsb - chunk * kWarps);
-                const int boxes = (sbs + kBoxSb - 1) / kBoxSb;
+                const int boxes = (sbs + P::kBoxSb - 1) / P::kBoxSb;
                 mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(boxes * P::kBoxBytes));
                 for (int b = 0; b < boxes; ++b)
                     tma_load_2d(ring + static_cast<size_t>(s) * P::kStageBytes + b * P::kBoxBytes, &wmap,
-                                (chunk * kWarps + b * kBoxSb) * P::kSbBytes / 8, row0, &full[s]);
+                                (chunk * kWarps + b * P::kBoxSb) * P::kSbBytes / 8, row0, &full[s]);
                 if (it == prefetch - 1 && !image_requested) request_image();
             }
         }
@@ -456,8 +570,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
             for (int q = 0; q < GROUPS; ++q) {
                 const int member = 2 * q + (g >> 2), plane = g & 3;
                 const bool real = member < p.members && plane < 3;
-                lx.x[q] = real ? smem_addr(planes) + static_cast<uint32_t>(member) * static_cast<uint32_t>(p.nsb) * kSliceBytes + plane * 32u + 8u * t
-                               : smem_addr(zeros) + 96u + 8u * t;
+                // the lane's share of a block: 8 bytes of a 32-weight sub-block (Q4_K / Q5_K), 4 bytes of a 16-weight block (Q6_K)
+                const uint32_t lane_bytes = (FMT == kQ6_K ? 4u : 8u) * t;
+                lx.x[q] = real ? smem_addr(planes) + static_cast<uint32_t>(member) * static_cast<uint32_t>(p.nsb) * kSliceBytes + plane * 32u + lane_bytes
+                               : smem_addr(zeros) + 96u + lane_bytes;
                 lx.step[q] = real ? static_cast<uint32_t>(kSliceBytes) : 0u;
             }
             const uint32_t sums_member = g < p.members ? static_cast<uint32_t>(g) : 0u;
@@ -467,7 +583,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
         }
         const uint32_t ring_addr = smem_addr(ring);
         // This warp's super-block inside a stage: box warp / kBoxSb, position warp % kBoxSb, rows g and g + 8.
-        const uint32_t lane_off = static_cast<uint32_t>((warp / kBoxSb) * P::kBoxBytes + (warp % kBoxSb) * P::kSbBytes + g * P::kRowPitch);
+        const uint32_t lane_off = static_cast<uint32_t>((warp / P::kBoxSb) * P::kBoxBytes + (warp % P::kBoxSb) * P::kSbBytes + g * P::kRowPitch);
 
 #pragma unroll 1
         for (int tile = 0; tile < tiles; ++tile) {
@@ -485,7 +601,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
                 const int sb = chunk * kWarps + warp;
                 if (sb < p.nsb) {
                     const uint32_t p0 = ring_addr + static_cast<uint32_t>(s) * P::kStageBytes + lane_off;
-                    superblock<FMT, GROUPS>(p0, p0 + 8 * P::kRowPitch, lx, t, acc, mins);
+                    if constexpr (FMT == kQ6_K) {
+                        // 210-byte super-blocks: the warp's one starts on a word boundary when its position in the box is even
+                        if (warp & 1) superblock_q6<GROUPS, true>(p0, p0 + 8 * P::kRowPitch, lx, t, acc);
+                        else superblock_q6<GROUPS, false>(p0, p0 + 8 * P::kRowPitch, lx, t, acc);
+                    } else {
+                        superblock<FMT, GROUPS>(p0, p0 + 8 * P::kRowPitch, lx, t, acc, mins);
+                    }
                 }
                 lx.advance(kWarps);
                 __syncwarp();
@@ -644,12 +766,13 @@ cudaError_t launch_format(const MmaGemvArgs& a) {
 }  // namespace
 
 bool gemv_imma_supports(uint32_t value_type, int k, int n, int members, const void* weights) {
-    if (value_type != kQ4_K && value_type != kQ5_K) return false;
+    if (value_type != kQ4_K && value_type != kQ5_K && value_type != kQ6_K) return false;
     if (members < 1 || members > kMaxMembers || k <= 0 || k % kSuperBlock != 0 || n < kTileRows) return false;
-    const int block_bytes = value_type == kQ4_K ? 144 : 176;
+    const int block_bytes = value_type == kQ4_K ? 144 : value_type == kQ5_K ? 176 : 210;
     const unsigned long long row_bytes = static_cast<unsigned long long>(k / kSuperBlock) * block_bytes;
-    if (row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(weights) % 16 != 0) return false;
-    const size_t stage = value_type == kQ4_K ? ImmaPlan<kQ4_K>::kStageBytes : ImmaPlan<kQ5_K>::kStageBytes;
+    if (row_bytes % 16 != 0 || reinterpret_cast<uintptr_t>(weights) % 16 != 0) return false;   // Q6_K: K / 256 a multiple of eight
+    const size_t stage = value_type == kQ4_K ? ImmaPlan<kQ4_K>::kStageBytes : value_type == kQ5_K ? ImmaPlan<kQ5_K>::kStageBytes
+                                                                                                  : ImmaPlan<kQ6_K>::kStageBytes;
     return imma_fixed_bytes(members, k / kSuperBlock) + 2 * stage <= kSmemLimit - 1024;
 }
 
@@ -672,6 +795,7 @@ cudaError_t launch_gemv_imma(const MmaGemvArgs& a) {
     switch (a.value_type) {
         case kQ4_K: return launch_format<kQ4_K>(a);
         case kQ5_K: return launch_format<kQ5_K>(a);
+        case kQ6_K: return launch_format<kQ6_K>(a);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -124,7 +124,7 @@ size_t gemv_mma_image_bytes(int members, int k, int planes);
 cudaError_t launch_gemv_mma_image(const MmaGemvArgs& args, void* image);
 cudaError_t launch_gemv_mma(const MmaGemvArgs& args);
 
-// The same call on the integer tensor-core instruction (gemv_imma.cu): Q4_K / Q5_K, 1..8 member rows; `planes` is unused.
+// The same call on the integer tensor-core instruction (gemv_imma.cu): K-quants, 1..8 member rows; `planes` is unused.
 bool gemv_imma_supports(uint32_t value_type, int k, int n, int members, const void* weights);
 size_t gemv_imma_image_bytes(int members, int k);
 cudaError_t launch_gemv_imma_image(const MmaGemvArgs& args, void* image);

@@ -110,9 +110,9 @@ void ribn_last_error_detail(const ribn_ctx *ctx, uint64_t *expected, uint64_t *a
  *   "mma_gemv":     1 = calls of up to eight rows per launch (and wider f32 batches, in groups of eight) use the
  *                   mma.sync kernels where they serve the shape (Q4_K / Q5_K / Q6_K, 16-byte aligned rows, at least
  *                   16 output rows); 0 = leave them to the integer-dot kernel (default 1);
- *   "imma_gemv":    1 = of those calls, Q4_K and Q5_K run on the integer instruction (nibbles as u8 operands,
- *                   activations as 22-bit integers per 256-value slice); 0 = on the half2-unpack f16 kernel that
- *                   serves Q6_K (default 1);  "imma_max_members": largest such call (1..8, default 8);
+ *   "imma_gemv":    1 = those calls run on the integer instruction (quants as 8-bit operands, activations as
+ *                   22-bit integers per 256-value slice); 0 = on the half2-unpack f16 kernel (default 1);
+ *                   "imma_max_members": largest such call (1..8, default 8);
  *   "mma_image_members": launches of at least this many rows convert their activations in a pre-pass launch,
  *                   narrower ones inside the GEMV kernel unless K exceeds 24 super-blocks or the input is gated
  *                   (1..9, default 3);

@@ -167,11 +167,9 @@ def test_q8_0_input_sizes_that_are_not_multiples_of_256(ctx, k, n):
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("integer_kernel", [1, 0], ids=["imma", "f16-mma"])
 def test_mma_kernel_modes_and_batch_identity(ctx, gemv_path, vt, x_dtype, integer_kernel):
-    """Q4_K / Q5_K run on the integer tensor-core kernel by default and on the f16 kernel (Q6_K's) with imma_gemv = 0."""
+    """The K-quants run on the integer tensor-core kernel by default and on the f16 kernel with imma_gemv = 0."""
     if gemv_path != 0:
         pytest.skip("the mma kernels are the default path only")
-    if vt == 14 and integer_kernel == 0:
-        pytest.skip("Q6_K has one narrow kernel")
     ctx.set_option("imma_gemv", integer_kernel)
     k, n = 4096, 528
     w = synth.random_weight(vt, k, n, seed=vt)
