@@ -257,14 +257,16 @@ __device__ __forceinline__ void umma_f16_tmem_a_elected(uint32_t tmem_d, uint32_
 constexpr int kImageCacheFloats = 50 * 1024;   // 200 KB
 
 template <int NT>
-__global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int cached) {
+// 8 to 32 warps per CTA (chosen by the launcher from the row length): a warp owns the super-blocks sb = warp (mod warps)
+// and has two of them in flight per trip, so up to 64 super-blocks are read in one round trip to memory.
+__global__ void __launch_bounds__(1024) tmem_image_kernel(const TmemParams p, int cached) {
     using I = ImagePlan<NT, 5>;
     extern __shared__ __align__(16) float row_copy[];
-    __shared__ float red[8];
-    __shared__ uint32_t red_bits[8];
+    __shared__ float red[32];
+    __shared__ uint32_t red_bits[32];
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = static_cast<int>(blockDim.x >> 5);
     const int m = blockIdx.x;
     const size_t row_elements = static_cast<size_t>(p.k) * (p.mode == 2 ? 2 : 1);
     const AnyRow row{static_cast<const uint8_t*>(p.x) + static_cast<size_t>(m) * row_elements * (p.x_bf16 ? 2 : 4), p.x_bf16};
@@ -292,11 +294,11 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int
     // non-negative floats order like their bit patterns; infinities and NaNs (0x7f800000 and above) come out on top
     uint32_t biggest = 0u;
     float part = 0.0f;
-    for (int sb = warp; sb < p.nsb; sb += 16) {   // two slices per trip: their loads are in flight together
+    for (int sb = warp; sb < p.nsb; sb += 2 * warps) {   // two slices per trip: their loads are in flight together
         float v0[8], v1[8];
-        const bool second = sb + 8 < p.nsb;
+        const bool second = sb + warps < p.nsb;
         read_slice(sb, v0);
-        if (second) read_slice(sb + 8, v1);
+        if (second) read_slice(sb + warps, v1);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             part = fmaf(v0[j], v0[j], part);
@@ -309,7 +311,7 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int
                 part = fmaf(v1[j], v1[j], part);
                 biggest = max(biggest, __float_as_uint(fabsf(v1[j])));
             }
-            if (cached) keep(sb + 8, v1);
+            if (cached) keep(sb + warps, v1);
         }
     }
     float inv_rms = 1.0f;
@@ -319,12 +321,11 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int
         if (lane == 0) red[warp] = part;
         __syncthreads();
         float total = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) total += red[w];
+        for (int w = 0; w < warps; ++w) total += red[w];
         inv_rms = 1.0f / sqrtf(total / static_cast<float>(p.k) + p.eps);
         // the normalised values, in the order of operations of rms_norm (x * inv_rms * weight), and their largest magnitude
         biggest = 0u;
-        for (int sb = warp; sb < p.nsb; sb += 8) {
+        for (int sb = warp; sb < p.nsb; sb += warps) {
             float v[8], g[8];
             if (cached) kept(sb, v);
             else read_slice(sb, v);
@@ -340,8 +341,7 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int
     biggest = __reduce_max_sync(0xffffffffu, biggest);
     if (lane == 0) red_bits[warp] = biggest;
     __syncthreads();
-#pragma unroll
-    for (int w = 0; w < 8; ++w) biggest = max(biggest, red_bits[w]);
+    for (int w = 0; w < warps; ++w) biggest = max(biggest, red_bits[w]);
     const bool bad = biggest >= 0x7f800000u;
     const float amax = __uint_as_float(biggest);
     int e = 9 - (static_cast<int>(biggest >> 23) - 127);
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(256) tmem_image_kernel(const TmemParams p, int
         up = __int_as_float(0x7fc00000);
     }
     float* scales = reinterpret_cast<float*>(p.image + I::scales_offset(p.nsb));
-    for (int sb = warp; sb < p.nsb; sb += 8) {
+    for (int sb = warp; sb < p.nsb; sb += warps) {
         float v[8];
         if (cached) {
             kept(sb, v);   // a warp reads back what it wrote itself
@@ -1025,7 +1025,10 @@ cudaError_t launch_format(const TmemGemvArgs& a) {
             if (attribute != cudaSuccess) return attribute;
             image_device = device;
         }
-        const cudaError_t e = launch_kernel(tmem_image_kernel<NT>, dim3(a.members), dim3(256), cached ? static_cast<size_t>(a.k) * sizeof(float) : 0,
+        // two super-blocks per warp and trip: as many warps as that takes, between 8 and 32
+        int image_warps = (nsb + 1) / 2;
+        image_warps = image_warps < 8 ? 8 : image_warps > 32 ? 32 : image_warps;
+        const cudaError_t e = launch_kernel(tmem_image_kernel<NT>, dim3(a.members), dim3(32 * image_warps), cached ? static_cast<size_t>(a.k) * sizeof(float) : 0,
                                             a.stream, p, cached);
         if (e != cudaSuccess) return e;
     }
