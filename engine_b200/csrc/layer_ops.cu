@@ -361,21 +361,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_split_kernel(con
     }
 }
 
-// grid (q_heads, members), 128 threads: merges the splits of one query head.
+// grid (q_heads, members), 128 threads: merges the splits of one query head.  Lane s of every warp holds split s (at most 32
+// splits): the maximum, the sum and the weights come out of two warp reductions, and a thread then has eight partial rows of
+// its output dimension in flight at a time.
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                          void* __restrict__ out, int q_heads, int splits) {
     pdl_launch_dependents();
     pdl_wait_prior();   // inputs come from the kernels before this one in the stream
+    const int lane = threadIdx.x & 31;
     const size_t base = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * splits;
-    float global_max = -INFINITY;
-    for (int s = 0; s < splits; ++s) global_max = fmaxf(global_max, part_ml[(base + s) * 2]);
-    float total = 0.0f, value = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = part_ml[(base + s) * 2];
-        const float weight = m == -INFINITY ? 0.0f : expf(m - global_max);
-        total = fmaf(part_ml[(base + s) * 2 + 1], weight, total);
-        value = fmaf(part_o[(base + s) * kAttnHeadDim + threadIdx.x], weight, value);
+    float m = -INFINITY, l = 0.0f;
+    if (lane < splits) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + lane) * 2);
+        m = ml.x;
+        l = ml.y;
+    }
+    float global_max = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) global_max = fmaxf(global_max, __shfl_xor_sync(0xffffffffu, global_max, o));
+    const float weight = m == -INFINITY ? 0.0f : expf(m - global_max);
+    float total = l * weight;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    const float* column = part_o + base * kAttnHeadDim + threadIdx.x;
+    float value = 0.0f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+        float part[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) part[u] = s0 + u < splits ? column[static_cast<size_t>(s0 + u) * kAttnHeadDim] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) value = fmaf(part[u], __shfl_sync(0xffffffffu, weight, (s0 + u) & 31), value);
     }
     const size_t index = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * kAttnHeadDim + threadIdx.x;
     if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value / total);
