@@ -201,24 +201,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_split_kernel(con
     const int begin = split * chunk;
     const int end = min(tokens, begin + chunk);
 
-    // The group's queries as A fragments, times scale * log2(e) (the softmax runs on exp2), hi and lo parts: rows = heads
-    // (rows from `group` on are zero), eight K steps of 16 dims.
-    uint32_t q_hi[8][4], q_lo[8][4];
-    {
-        const float factor = scale * 1.4426950408889634f;
-        const float* q_group = q + (static_cast<size_t>(member) * q_heads + static_cast<size_t>(kv_head) * group) * kAttnHeadDim;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-#pragma unroll
-            for (int part = 0; part < 4; ++part) {
-                const int row = g + 8 * (part & 1), column = 16 * ks + 2 * t + 8 * (part >> 1);
-                float2 v = make_float2(0.0f, 0.0f);
-                if (row < group) v = *reinterpret_cast<const float2*>(q_group + row * kAttnHeadDim + column);
-                split_half2(v.x * factor, v.y * factor, q_hi[ks][part], q_lo[ks][part]);
-            }
-        }
-    }
-
     const long long sequence = shared_cache ? 0 : member;
     const __half* k_base = k_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
     const __half* v_base = v_cache + (sequence * kv_heads + kv_head) * max_context * kAttnHeadDim;
@@ -244,7 +226,25 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_split_kernel(con
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (begin < end) request_tile(0, begin);
+    if (begin < end) request_tile(0, begin);   // in flight while the queries are fetched and split below
+
+    // The group's queries as A fragments, times scale * log2(e) (the softmax runs on exp2), hi and lo parts: rows = heads
+    // (rows from `group` on are zero), eight K steps of 16 dims.
+    uint32_t q_hi[8][4], q_lo[8][4];
+    {
+        const float factor = scale * 1.4426950408889634f;
+        const float* q_group = q + (static_cast<size_t>(member) * q_heads + static_cast<size_t>(kv_head) * group) * kAttnHeadDim;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                const int row = g + 8 * (part & 1), column = 16 * ks + 2 * t + 8 * (part >> 1);
+                float2 v = make_float2(0.0f, 0.0f);
+                if (row < group) v = *reinterpret_cast<const float2*>(q_group + row * kAttnHeadDim + column);
+                split_half2(v.x * factor, v.y * factor, q_hi[ks][part], q_lo[ks][part]);
+            }
+        }
+    }
 
     float out[16][4];   // rows g, g + 8; dims 8 n + 2 t, + 1
 #pragma unroll
@@ -362,8 +362,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_split_kernel(con
 }
 
 // grid (q_heads, members), 128 threads: merges the splits of one query head.  Lane s of every warp holds split s (at most 32
-// splits): the maximum, the sum and the weights come out of two warp reductions, and a thread then has eight partial rows of
-// its output dimension in flight at a time.
+// splits): the maximum, the sum and the weights come out of two warp reductions, and a thread then has sixteen partial rows
+// of its output dimension in flight at a time.
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                          void* __restrict__ out, int q_heads, int splits) {
@@ -386,12 +386,12 @@ __global__ void __launch_bounds__(kAttnHeadDim) attention_combine_kernel(const f
     for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
     const float* column = part_o + base * kAttnHeadDim + threadIdx.x;
     float value = 0.0f;
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-        float part[8];
+    for (int s0 = 0; s0 < splits; s0 += 16) {
+        float part[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) part[u] = s0 + u < splits ? column[static_cast<size_t>(s0 + u) * kAttnHeadDim] : 0.0f;
+        for (int u = 0; u < 16; ++u) part[u] = s0 + u < splits ? column[static_cast<size_t>(s0 + u) * kAttnHeadDim] : 0.0f;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) value = fmaf(part[u], __shfl_sync(0xffffffffu, weight, (s0 + u) & 31), value);
+        for (int u = 0; u < 16; ++u) value = fmaf(part[u], __shfl_sync(0xffffffffu, weight, (s0 + u) & 31), value);
     }
     const size_t index = (static_cast<size_t>(blockIdx.y) * q_heads + blockIdx.x) * kAttnHeadDim + threadIdx.x;
     if constexpr (OUT_BF16) static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value / total);
