@@ -522,7 +522,45 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
         reinterpret_cast<uint32_t*>(zeros)[threadIdx.x] = 0u;
         named_barrier_sync(1, kConsumers);
         pdl_wait_prior();   // the activations may be the previous kernel's output, and y may still be read by it
-        if (p.image == nullptr) {
+        const int owned_slices = p.nsb > warp ? (p.nsb - warp + kWarps - 1) / kWarps : 0;
+        if (p.image == nullptr && p.mode == 1 && p.members == 1 && p.nsb <= 2 * kWarps) {
+            // One row of at most sixteen super-blocks to normalise (a decode step's projections): every lane keeps its
+            // share of the warp's one or two slices in registers, so the row and the norm weights are read once -- one
+            // round trip to memory instead of three.  Sums run in the order of the general path below (same bits).
+            const AnyRow row{static_cast<const uint8_t*>(p.x), p.x_bf16};
+            float v[2][8], gain[2][8];
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (i < owned_slices) {
+                    const int k0 = (warp + i * kWarps) * kSuperBlock + lane * 8;
+                    load_row8(row + k0, v[i]);
+                    load_x8<float>(p.norm_weight + k0, gain[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                if (i < owned_slices)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) part = fmaf(v[i][j], v[i][j], part);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0) norm[warp * kMaxMembers] = part;
+            named_barrier_sync(1, kConsumers);
+            float totalsq = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) totalsq += norm[w * kMaxMembers];
+            const float inv_rms = 1.0f / sqrtf(totalsq / static_cast<float>(p.k) + p.eps);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (i < owned_slices) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * inv_rms * gain[i][j];
+                    store_slice(0, warp + i * kWarps, lane, v[i], planes, sums, scale);
+                }
+            }
+            __syncwarp();   // a warp reads only the super-blocks it converted itself
+        } else if (p.image == nullptr) {
             // norm[64 + m] = 1 / rms of member row m when RMSNorm is asked for
             if (p.mode == 1) {
                 for (int m = 0; m < p.members; ++m) {
@@ -542,8 +580,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_imma_kernel(const __grid_con
             }
             // The warp's slices (super-blocks warp, warp + 8, ... of every member), two loads in flight.
             const float* inv_rms = norm + kWarps * kMaxMembers;
-            const int owned = p.nsb > warp ? (p.nsb - warp + kWarps - 1) / kWarps : 0;
-            const int slices = owned * p.members;
+            const int slices = owned_slices * p.members;
 #pragma unroll 1
             for (int i = 0; i < slices; i += 2) {
                 const int sb0 = warp + (i / p.members) * kWarps, m0 = i % p.members;
