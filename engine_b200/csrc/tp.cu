@@ -422,8 +422,10 @@ int ribn_tp_allreduce_residual(ribn_ctx* ctx, ribn_tp* tp, uint32_t slot, float*
     int previous = 0;
     cudaGetDevice(&previous);
     cudaSetDevice(device);
+    // One group of four values per thread where the grid allows it: all of a rank's loads from its peers are then in flight
+    // in one round trip over NVLink (no CTA waits for another CTA of this launch, so the grid may exceed what is resident).
     unsigned long long ctas = (total / 4 + 255) / 256;
-    if (ctas > static_cast<unsigned long long>(sm_count)) ctas = static_cast<unsigned long long>(sm_count);
+    if (ctas > 4ull * static_cast<unsigned long long>(sm_count)) ctas = 4ull * static_cast<unsigned long long>(sm_count);
     const dim3 grid(static_cast<unsigned>(ctas));
     const uint64_t slot_offset = static_cast<uint64_t>(slot) * tp->slot_bytes, tail_offset = 2 * tp->slot_bytes;
     cudaError_t e;
