@@ -65,7 +65,6 @@ struct ImmaPlan {
     static constexpr int kRowPitch = kBoxSb * kSbBytes;
     static constexpr int kBoxBytes = kTileRows * kRowPitch;
     static constexpr int kStageBytes = kBoxes * kBoxBytes;
-    [[maybe_unused]] static constexpr uint32_t kQuantOffset = FMT == kQ4_K ? 16 : 48;   // Q5_K: 32 fifth-bit bytes after the header
     static_assert(kRowPitch % 16 == 0 && kBoxBytes % 128 == 0, "TMA box: 16-byte rows, 128-byte aligned destination");
     static_assert((kSbBytes * kBoxSb / 8) % 2 == 0, "TMA x coordinate of every box on a 16-byte boundary");
 };
@@ -256,7 +255,7 @@ __device__ __forceinline__ void subblock(uint32_t a0, uint32_t a1, uint32_t a2, 
 //   mins[0..3]: the minima term of members 2t, 2t + 1 for row g, then for row g + 8.
 template <uint32_t FMT, int GROUPS>
 __device__ __forceinline__ void superblock(uint32_t p0, uint32_t p1, const LaneX<GROUPS>& lx, int t, float (&acc)[GROUPS][2], float (&mins)[4]) {
-    using P = ImmaPlan<FMT>;
+    constexpr uint32_t kQuantOffset = FMT == kQ4_K ? 16 : 48;   // Q5_K: 32 fifth-bit bytes between the header and the nibbles
     const uint4 h0 = lds128(p0), h1 = lds128(p1);   // d | dmin, 12 scale bytes
     uint32_t sc_lo0, sc_hi0, m_lo0, m_hi0, sc_lo1, sc_hi1, m_lo1, m_hi1;
     unpack_k_scales(h0.y, h0.z, h0.w, sc_lo0, sc_hi0, m_lo0, m_hi0);
@@ -283,7 +282,7 @@ __device__ __forceinline__ void superblock(uint32_t p0, uint32_t p1, const LaneX
         for (int i = 0; i < 4; ++i) total[q][i] = 0;
 #define RIBN_IMMA_PAIR(G)                                                                                                      \
     {                                                                                                                          \
-        const uint2 q0 = lds64(p0 + P::kQuantOffset + 32 * (G) + 8 * t), q1 = lds64(p1 + P::kQuantOffset + 32 * (G) + 8 * t);  \
+        const uint2 q0 = lds64(p0 + kQuantOffset + 32 * (G) + 8 * t), q1 = lds64(p1 + kQuantOffset + 32 * (G) + 8 * t);  \
         uint32_t a0 = q0.x & 0x0f0f0f0fu, a1 = q1.x & 0x0f0f0f0fu, a2 = q0.y & 0x0f0f0f0fu, a3 = q1.y & 0x0f0f0f0fu;           \
         if (FMT == kQ5_K) {                                                                                                    \
             a0 = with_fifth<2 * (G)>(a0, f0.x);                                                                                \
