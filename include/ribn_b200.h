@@ -251,9 +251,9 @@ int ribn_noalloc_status(int device, void *cuda_stream);
  *   silu_mul -> down GEMV              RIBN_FUSED_SWIGLU: x is [members][2K], rows [gate | up], the operand is
  *                                      silu(gate) * up (model_ops.rs:316-328)
  *   q and k (any two projections of one format) stored as one matrix: one launch, two outputs (split_rows)
- * All jobs share K; each is validated like ribn_gemv before anything is launched.  Served by the integer-dot
- * kernel (1..4 member rows per launch) and the tensor-core decode kernel; shapes that only the f32 kernel
- * serves are refused with RIBN_E_INVALID_ARGUMENT (use the separate calls). */
+ * All jobs share K; each is validated like ribn_gemv before anything is launched.  Served by the kernels ribn_gemv
+ * uses (the integer tensor-core kernel for up to eight rows, the batch kernel from nine, the integer-dot kernel for
+ * Q8_0); shapes that only the f32 kernel serves are refused with RIBN_E_INVALID_ARGUMENT (use the separate calls). */
 typedef struct ribn_gemv_job {
     uint32_t expected_type;      /* 0 = the weight's own type */
     const ribn_qweight* weight;
